@@ -1,0 +1,77 @@
+"""TP=2 / PP=2 over gloo on CPU must emit the token IDs of the single-process run."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from vade_b200.config import tiny_config
+from vade_b200.runtime.build import build_engine
+
+
+def _prompt(n=128, vocab=4096, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab - 8, (n,), generator=g).tolist()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, tp, pp, n_new, draft, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vade_b200.parallel.groups import make_parallel
+    par = make_parallel(tp=tp, pp=pp)
+    eng = build_engine(tiny_config(), seed=0, tp=tp, tp_rank=par.tp_rank, pp=pp, pp_rank=par.pp_rank,
+                       comm=par.comm, pp_comm=par.pp_comm, max_seq=512)
+    seq = eng.generate(_prompt(), n_new, draft_depth=draft)
+    q.put((rank, seq.generated))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _launch(tp, pp, n_new=24, draft=0):
+    world = tp * pp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, tp, pp, n_new, draft, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    return outs
+
+
+def _single(n_new=24):
+    eng = build_engine(tiny_config(), seed=0, max_seq=512)
+    return eng.generate(_prompt(), n_new).generated
+
+
+def test_tp2_matches_single():
+    ref = _single()
+    outs = _launch(2, 1)
+    assert outs[0] == ref and outs[1] == ref
+
+
+def test_pp2_matches_single():
+    ref = _single()
+    outs = _launch(1, 2)
+    assert outs[1] == ref and outs[0] == ref
+
+
+def test_tp2_pp2_speculative_matches_single():
+    ref = _single()
+    outs = _launch(2, 2, draft=2)
+    assert all(o == ref for o in outs.values())

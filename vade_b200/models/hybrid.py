@@ -1,0 +1,84 @@
+"""Hybrid Gated-DeltaNet + gated-attention MoE decoder (Qwen3-Next style) with an MTP head.
+
+Layer i is full attention when (i + 1) % interval == 0, else Gated DeltaNet; every layer is
+followed by a top-k MoE with a sigmoid-gated shared expert.  The residual stream is fp32;
+inputs of every matrix product are ``act`` (bf16 on GPU); row-parallel products (o_proj, GDN
+out_proj) are produced as canonical-range partial sums and folded in one fixed tree after the
+exchange, so any tensor-parallel size gives the same bits.  The same class runs on CPU with
+``RefOps`` and on B200 with ``CudaOps``.
+
+Layer order follows the reference decoder (engine/crates/model/src/flash/refcpu.rs:946-993,
+without its hyper-connection and n-gram-embedding extras); the MTP block follows
+engine/crates/engine/src/flash/next_mtp.rs:285-335.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig, RANGES
+from ..ops.api import Batch
+from ..parallel.plan import ShardPlan
+from .weights import ModelWeights, LayerWeights
+
+
+class HybridModel:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, plan: ShardPlan, ops, comm):
+        self.cfg, self.w, self.plan, self.ops, self.comm = cfg, weights, plan, ops, comm
+        self.r_local = plan.ranges[1] - plan.ranges[0]
+
+    # ------------------------------------------------------------------ one layer
+    def _layer(self, lw: LayerWeights, key, x, h, batch: Batch, cache, next_norm):
+        ops, comm = self.ops, self.comm
+        ph = batch.phase
+        if lw.attention:
+            qkv = ops.linear(h, lw.qkv, phase=ph)
+            mixed = ops.attn_mix(lw, qkv, batch, cache, key)
+            parts = ops.linear_ranges(mixed, lw.o_proj, self.r_local, phase=ph)
+        else:
+            proj = ops.linear(h, lw.in_proj, phase=ph)
+            mixed = ops.gdn_mix(lw, proj, batch, cache, key)
+            parts = ops.linear_ranges(mixed, lw.out_proj, self.r_local, phase=ph)
+        parts = comm.gather_partials(parts)
+        x, h2 = ops.fold_add_norm(parts, x, lw.post_norm)
+        logits = ops.linear(h2, lw.moe.router, out_fp32=True, phase=ph)
+        ids, wts, sg = ops.route(logits)
+        pair_out, owned = ops.moe_experts(lw.moe, h2, ids, phase=ph)
+        pair_out = comm.gather_pairs(pair_out, owned)
+        return ops.combine_add_norm(pair_out, ids, wts, sg, x, next_norm)
+
+    # ------------------------------------------------------------------ trunk
+    def forward(self, batch: Batch, cache, hidden_in: torch.Tensor | None = None):
+        """Runs this stage's layers.  Returns (x, h): the fp32 residual rows and, on the last stage,
+        their final-norm rows; on other stages h is None and x goes to the next stage."""
+        ops, plan = self.ops, self.plan
+        x = ops.embed(self.w.embed, batch.tokens) if plan.first_stage else hidden_in
+        layers = list(range(*plan.layers))
+        h = ops.rmsnorm(x, self.w.layers[layers[0]].input_norm)
+        for n, i in enumerate(layers):
+            if n + 1 < len(layers):
+                nxt = self.w.layers[layers[n + 1]].input_norm
+            else:
+                nxt = self.w.final_norm if plan.last_stage else None
+            x, h = self._layer(self.w.layers[i], i, x, h, batch, cache, nxt)
+        return x, h
+
+    # ------------------------------------------------------------------ heads
+    def greedy(self, h: torch.Tensor) -> torch.Tensor:
+        """argmax over the sharded vocabulary: ties to the lower id, identical on every rank."""
+        val, idx = self.ops.head_argmax(h, self.w.lm_head, self.plan.vocab[0])
+        _, idx = self.comm.merge_argmax(val, idx)
+        return idx
+
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        return self.comm.gather_cols(self.ops.head_logits(h, self.w.lm_head))
+
+    # ------------------------------------------------------------------ MTP draft block
+    def mtp_forward(self, batch: Batch, cache, hidden: torch.Tensor):
+        """One multi-token-prediction step: row t gets token id t+1 (batch.tokens) and the trunk's
+        residual row t (``hidden``); returns (x, h) of the draft block, h ready for the shared head."""
+        m, ops = self.w.mtp, self.ops
+        e = ops.embed(self.w.embed, batch.tokens)
+        cat = torch.cat([ops.rmsnorm(e, m.norm_emb).float(), ops.rmsnorm(hidden, m.norm_hidden).float()], -1)
+        x = ops.linear(cat.to(ops.act), m.fc, out_fp32=True, phase=batch.phase)
+        h = ops.rmsnorm(x, m.layer.input_norm)
+        return self._layer(m.layer, "mtp", x, h, batch, cache, m.final_norm)

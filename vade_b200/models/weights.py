@@ -1,0 +1,462 @@
+"""Per-rank runtime weights: fused, sharded, and (on GPU) repacked into kernel tiles.
+
+A checkpoint stores one tensor per projection; the engine wants few large matrices per layer
+so a decode step is few launches.  This module reads exactly the rows/columns a rank owns
+(parallel/plan.py), concatenates them into fused matrices
+
+    GDN        in_proj  = [q | k | v | z | b | a] rows          out_proj (K split in ranges)
+    attention  qkv      = [q+gate per head | k | v] rows        o_proj   (K split in ranges)
+    MoE        router   = [experts | shared gate] rows (plain)  gate_up (gate/up rows interleaved), down
+    shared expert = ``s`` virtual experts of the routed width appended after the routed ones
+
+and keeps per-tensor NVFP4 scales as a per-row fp32 vector so fused matrices keep each source
+tensor's own scale.  Parity: the reference's resident arena and load-time repack
+(engine/crates/engine/src/flash/next_batched.rs:161-640, engine/crates/gpu/src/load.rs).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config import ModelConfig, RANGES
+from ..parallel.plan import ShardPlan
+from ..quant import codecs
+
+TILE_M = 128          # weight rows per kernel tile
+TILE_K = 64           # K columns per kernel block (one 128-byte swizzle atom of bf16)
+TILE_BYTES = TILE_M * TILE_K // 2 + TILE_M * (TILE_K // 16)     # 4096 nibble bytes + 512 scale bytes
+
+
+@dataclass
+class QLinear:
+    """One [n, k] matrix (or a stack of ``e`` of them) in plain or NVFP4 storage."""
+    n: int
+    k: int
+    kind: str                                   # "plain" | "nvfp4"
+    w: torch.Tensor | None = None               # plain: [e?, n, k]
+    packed: torch.Tensor | None = None          # nvfp4: [e?, n, k/2] uint8, low nibble = even column
+    scale: torch.Tensor | None = None           # nvfp4: [e?, n, k/16] uint8 (e4m3 bits)
+    row_scale: torch.Tensor | None = None       # fp32 [e?, n]; 1.0 for plain
+    tiles: torch.Tensor | None = None           # kernel layout, see pack_tiles()
+    e: int = 0                                  # 0 = single matrix, else stack size
+
+    def dense(self, idx: int | None = None) -> torch.Tensor:
+        """fp32 values WITHOUT the row scale (e2m1*e4m3 for nvfp4)."""
+        if self.kind == "plain":
+            w = self.w if idx is None else self.w[idx]
+            return w.float()
+        p = self.packed if idx is None else self.packed[idx]
+        s = self.scale if idx is None else self.scale[idx]
+        return codecs.nvfp4_block_values(p, s)
+
+    def rs(self, idx: int | None = None) -> torch.Tensor:
+        return self.row_scale if idx is None else self.row_scale[idx]
+
+    def to(self, device) -> "QLinear":
+        mv = lambda t: None if t is None else t.to(device)
+        return QLinear(self.n, self.k, self.kind, mv(self.w), mv(self.packed), mv(self.scale),
+                       mv(self.row_scale), mv(self.tiles), self.e)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w, self.tiles, self.row_scale) if t is not None) \
+            + (0 if self.tiles is not None else sum(t.numel() for t in (self.packed, self.scale) if t is not None))
+
+
+def pack_tiles(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Row-major NVFP4 ([..., n, k/2] nibble bytes, [..., n, k/16] scale bytes) -> kernel tiles
+    [..., n_pad/128, k/64, 4608]: per (row tile, K block) 128 rows x 16 B of columns 0..31, then
+    128 rows x 16 B of columns 32..63, then 128 rows x 4 scale bytes.  One block is one
+    contiguous 4608-byte bulk copy; a thread that owns row r reads r*16 in each plane, which is
+    bank-conflict free.  Rows are zero-padded to a multiple of 128."""
+    *lead, n, kh = packed.shape
+    k = kh * 2
+    assert k % TILE_K == 0, "K must be a multiple of 64"
+    n_pad = -(-n // TILE_M) * TILE_M
+    if n_pad != n:
+        packed = torch.cat([packed, packed.new_zeros(*lead, n_pad - n, kh)], -2)
+        scale = torch.cat([scale, scale.new_zeros(*lead, n_pad - n, k // 16)], -2)
+    mt, kb = n_pad // TILE_M, k // TILE_K
+    nib = packed.reshape(*lead, mt, TILE_M, kb, 2, 16)          # [.., mt, row, kb, half, 16B]
+    nib = nib.movedim(-3, -4).movedim(-2, -3)                   # [.., mt, kb, half, row, 16B]
+    nib = nib.reshape(*lead, mt, kb, 2 * TILE_M * 16)
+    sc = scale.reshape(*lead, mt, TILE_M, kb, 4).movedim(-2, -3).reshape(*lead, mt, kb, TILE_M * 4)
+    return torch.cat([nib, sc], -1).contiguous()
+
+
+def unpack_tiles(tiles: torch.Tensor, n: int):
+    """Inverse of pack_tiles (used by tests and by synthetic weights to recover row-major form)."""
+    *lead, mt, kb, _ = tiles.shape
+    nib = tiles[..., :2 * TILE_M * 16].reshape(*lead, mt, kb, 2, TILE_M, 16)
+    nib = nib.movedim(-3, -2).movedim(-4, -3)                   # [.., mt, row, kb, half, 16]
+    packed = nib.reshape(*lead, mt * TILE_M, kb * 32)[..., :n, :]
+    sc = tiles[..., 2 * TILE_M * 16:].reshape(*lead, mt, kb, TILE_M, 4).movedim(-2, -3)
+    scale = sc.reshape(*lead, mt * TILE_M, kb * 4)[..., :n, :]
+    return packed.contiguous(), scale.contiguous()
+
+
+# --------------------------------------------------------------------------- reading + fusing
+class _Reader:
+    def __init__(self, cfg: ModelConfig, source, act: torch.dtype):
+        self.cfg, self.src, self.act = cfg, source, act
+
+    def kind(self, name: str) -> str:
+        return "nvfp4" if self.src.has(name + "_scale_2") else ("fp8" if self.src.has(name + "_scale_inv") else "plain")
+
+    def rows(self, name: str, r0: int, r1: int, c0: int = 0, c1: int | None = None):
+        """Rows [r0,r1) and logical columns [c0,c1) of a linear weight -> (kind, parts)."""
+        kind = self.kind(name)
+        if kind == "plain":
+            w = self.src.read(name, r0, r1)
+            return kind, (w[:, c0:c1].to(self.act),)
+        if kind == "nvfp4":
+            p = self.src.read(name, r0, r1).view(torch.uint8)
+            s = self.src.read(name + "_scale", r0, r1).view(torch.uint8)
+            g = self.src.read(name + "_scale_2").float().reshape(())
+            k = p.shape[1] * 2
+            c1 = k if c1 is None else c1
+            assert c0 % 16 == 0 and c1 % 16 == 0
+            return kind, (p[:, c0 // 2:c1 // 2], s[:, c0 // 16:c1 // 16], g)
+        # block fp8 is expanded to plain storage at load (exact: e4m3 * fp32 scale)
+        q = self.src.read(name).view(torch.uint8)
+        sc = self.src.read(name + "_scale_inv").float()
+        w = codecs.fp8_block_dequantize_weight(q, sc)[r0:r1]
+        return "plain", (w[:, c0:c1].to(self.act),)
+
+    def vec(self, name: str, r0: int = 0, r1: int | None = None) -> torch.Tensor:
+        return self.src.read(name, r0, r1).float()
+
+
+def fuse(segments: list) -> QLinear:
+    """Concatenate row segments [(kind, parts), ...] of equal K and equal kind into one QLinear."""
+    kinds = {k for k, _ in segments}
+    if len(kinds) != 1:
+        raise ValueError(f"cannot fuse segments of different storage classes: {sorted(kinds)}")
+    kind = kinds.pop()
+    if kind == "plain":
+        w = torch.cat([p[0] for _, p in segments], 0).contiguous()
+        return QLinear(w.shape[0], w.shape[1], "plain", w=w,
+                       row_scale=torch.ones(w.shape[0], dtype=torch.float32))
+    packed = torch.cat([p[0] for _, p in segments], 0).contiguous()
+    scale = torch.cat([p[1] for _, p in segments], 0).contiguous()
+    rs = torch.cat([p[2].expand(p[0].shape[0]) for _, p in segments], 0).contiguous().float()
+    return QLinear(packed.shape[0], packed.shape[1] * 2, "nvfp4", packed=packed, scale=scale, row_scale=rs)
+
+
+def stack(mats: list) -> QLinear:
+    a = mats[0]
+    if a.kind == "plain":
+        return QLinear(a.n, a.k, "plain", w=torch.stack([m.w for m in mats]),
+                       row_scale=torch.stack([m.row_scale for m in mats]), e=len(mats))
+    return QLinear(a.n, a.k, "nvfp4", packed=torch.stack([m.packed for m in mats]),
+                   scale=torch.stack([m.scale for m in mats]),
+                   row_scale=torch.stack([m.row_scale for m in mats]), e=len(mats))
+
+
+def interleave_rows(g: QLinear, u: QLinear) -> QLinear:
+    """Rows g0,u0,g1,u1,... so a gate value and its up value land in adjacent accumulator lanes."""
+    def il(a, b):
+        return torch.stack([a, b], 1).reshape(a.shape[0] * 2, *a.shape[1:]).contiguous()
+    if g.kind == "plain":
+        return QLinear(2 * g.n, g.k, "plain", w=il(g.w, u.w), row_scale=il(g.row_scale, u.row_scale))
+    return QLinear(2 * g.n, g.k, "nvfp4", packed=il(g.packed, u.packed), scale=il(g.scale, u.scale),
+                   row_scale=il(g.row_scale, u.row_scale))
+
+
+@dataclass
+class MoEWeights:
+    router: QLinear                 # [E + 1, H] plain; last row = shared-expert gate
+    gate_up: QLinear                # stack of local routed + shared virtual experts, [2I, H] each
+    down: QLinear                   # stack, [H, I] each
+    n_local: int                    # routed experts held by this rank
+    n_shared: int                   # virtual shared experts (replicated), stored after the routed ones
+    expert0: int                    # global id of the first local routed expert
+
+
+@dataclass
+class LayerWeights:
+    attention: bool
+    input_norm: torch.Tensor
+    post_norm: torch.Tensor
+    moe: MoEWeights
+    # attention
+    qkv: QLinear | None = None
+    o_proj: QLinear | None = None
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+    # gdn
+    in_proj: QLinear | None = None
+    out_proj: QLinear | None = None
+    conv_w: torch.Tensor | None = None      # [C_local, 4]
+    a_log: torch.Tensor | None = None
+    dt_bias: torch.Tensor | None = None
+    gdn_norm: torch.Tensor | None = None
+
+
+@dataclass
+class MTPWeights:
+    fc: QLinear                     # [H, 2H] over [norm(emb) | norm(hidden)]
+    norm_emb: torch.Tensor
+    norm_hidden: torch.Tensor
+    layer: LayerWeights
+    final_norm: torch.Tensor
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor | None              # [V, H] (first stage and MTP)
+    final_norm: torch.Tensor | None
+    lm_head: QLinear | None                 # [V / tp, H]
+    layers: dict = field(default_factory=dict)     # global layer index -> LayerWeights
+    mtp: MTPWeights | None = None
+
+    def all_linears(self):
+        for lw in list(self.layers.values()) + ([self.mtp.layer] if self.mtp else []):
+            for q in (lw.qkv, lw.o_proj, lw.in_proj, lw.out_proj, lw.moe.router, lw.moe.gate_up, lw.moe.down):
+                if q is not None:
+                    yield q
+        if self.lm_head is not None:
+            yield self.lm_head
+        if self.mtp is not None:
+            yield self.mtp.fc
+
+    def nbytes(self) -> int:
+        n = sum(q.nbytes() for q in self.all_linears())
+        if self.embed is not None:
+            n += self.embed.numel() * self.embed.element_size()
+        return n
+
+
+def _load_layer(rd: _Reader, plan: ShardPlan, base: str, attention: bool) -> LayerWeights:
+    cfg = rd.cfg
+    H, hd = cfg.hidden_size, cfg.head_dim
+    lw = LayerWeights(attention, rd.vec(base + "input_layernorm.weight"),
+                      rd.vec(base + "post_attention_layernorm.weight"), moe=None)
+    if attention:
+        q0, q1 = plan.q_heads
+        k0, k1 = plan.kv_heads
+        segs = [rd.rows(base + "self_attn.q_proj.weight", q0 * 2 * hd, q1 * 2 * hd),
+                rd.rows(base + "self_attn.k_proj.weight", k0 * hd, k1 * hd),
+                rd.rows(base + "self_attn.v_proj.weight", k0 * hd, k1 * hd)]
+        lw.qkv = fuse(segs)
+        lw.o_proj = fuse([rd.rows(base + "self_attn.o_proj.weight", 0, H, q0 * hd, q1 * hd)])
+        lw.q_norm = rd.vec(base + "self_attn.q_norm.weight")
+        lw.k_norm = rd.vec(base + "self_attn.k_norm.weight")
+    else:
+        kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        g0, g1 = plan.gdn_k_heads
+        v0, v1 = plan.gdn_v_heads
+        kdim = cfg.gdn_key_dim
+        qkv = base + "linear_attn.in_proj_qkv.weight"
+        sel = [(g0 * kd, g1 * kd), (kdim + g0 * kd, kdim + g1 * kd), (2 * kdim + v0 * vd, 2 * kdim + v1 * vd)]
+        segs = [rd.rows(qkv, a, b) for a, b in sel]
+        segs.append(rd.rows(base + "linear_attn.in_proj_z.weight", v0 * vd, v1 * vd))
+        segs.append(rd.rows(base + "linear_attn.in_proj_b.weight", v0, v1))
+        segs.append(rd.rows(base + "linear_attn.in_proj_a.weight", v0, v1))
+        lw.in_proj = fuse(segs)
+        lw.out_proj = fuse([rd.rows(base + "linear_attn.out_proj.weight", 0, H, v0 * vd, v1 * vd)])
+        cw = rd.src.read(base + "linear_attn.conv1d.weight").float().reshape(cfg.gdn_conv_dim, -1)
+        lw.conv_w = torch.cat([cw[a:b] for a, b in sel], 0).contiguous()
+        lw.a_log = rd.vec(base + "linear_attn.A_log", v0, v1)
+        lw.dt_bias = rd.vec(base + "linear_attn.dt_bias", v0, v1)
+        lw.gdn_norm = rd.vec(base + "linear_attn.norm.weight")
+    # ---- MoE
+    I, S = cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    if S % I != 0:
+        raise ValueError("shared expert width must be a multiple of the routed expert width")
+    router = fuse([rd.rows(base + "mlp.gate.weight", 0, cfg.num_experts),
+                   rd.rows(base + "mlp.shared_expert_gate.weight", 0, 1)])
+    gu, dn = [], []
+    e0, e1 = plan.experts
+    for e in range(e0, e1):
+        p = base + f"mlp.experts.{e}."
+        gu.append(interleave_rows(fuse([rd.rows(p + "gate_proj.weight", 0, I)]), fuse([rd.rows(p + "up_proj.weight", 0, I)])))
+        dn.append(fuse([rd.rows(p + "down_proj.weight", 0, H)]))
+    p = base + "mlp.shared_expert."
+    for j in range(S // I):
+        gu.append(interleave_rows(fuse([rd.rows(p + "gate_proj.weight", j * I, (j + 1) * I)]),
+                                  fuse([rd.rows(p + "up_proj.weight", j * I, (j + 1) * I)])))
+        dn.append(fuse([rd.rows(p + "down_proj.weight", 0, H, j * I, (j + 1) * I)]))
+    lw.moe = MoEWeights(router, stack(gu), stack(dn), e1 - e0, S // I, e0)
+    return lw
+
+
+def load_weights(cfg: ModelConfig, source, plan: ShardPlan, act: torch.dtype = torch.float32,
+                 device: str | torch.device = "cpu", with_mtp: bool = True, keep_rowmajor: bool = True) -> ModelWeights:
+    """Read, shard, fuse and (for CUDA devices) tile-pack the weights this rank owns."""
+    rd = _Reader(cfg, source, act)
+    mw = ModelWeights(None, None, None)
+    pre = "model.language_model."
+    want_mtp = with_mtp and cfg.mtp_num_hidden_layers > 0 and plan.last_stage
+    if plan.first_stage or want_mtp:
+        mw.embed = source.read(pre + "embed_tokens.weight").to(act)
+    if plan.last_stage:
+        mw.final_norm = rd.vec(pre + "norm.weight")
+        head = pre + "embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"
+        mw.lm_head = fuse([rd.rows(head, plan.vocab[0], plan.vocab[1])])
+    for i in range(*plan.layers):
+        mw.layers[i] = _load_layer(rd, plan, f"{pre}layers.{i}.", cfg.is_attention_layer(i))
+    if want_mtp:
+        fc = fuse([(k, p) for k, p in [_hcat(rd, "mtp.fc_embedding.weight", "mtp.fc_hidden.weight")]])
+        mw.mtp = MTPWeights(fc, rd.vec("mtp.pre_fc_norm_embedding.weight"), rd.vec("mtp.pre_fc_norm_hidden.weight"),
+                            _load_layer(rd, plan, "mtp.layers.0.", True), rd.vec("mtp.norm.weight"))
+    return finalize(mw, device, keep_rowmajor)
+
+
+def _hcat(rd: _Reader, a: str, b: str):
+    """[A | B] along K for two [H, H] matrices (the MTP input projection over [emb | hidden])."""
+    ka, pa = rd.rows(a, 0, rd.cfg.hidden_size)
+    kb, pb = rd.rows(b, 0, rd.cfg.hidden_size)
+    if ka != kb:
+        raise ValueError("MTP fc matrices use different storage classes")
+    if ka == "plain":
+        return ka, (torch.cat([pa[0], pb[0]], 1),)
+    # two tensor scales over one row: fold the ratio into the block scales is not exact, so keep
+    # plain storage for this small matrix
+    wa = codecs.nvfp4_dequantize(pa[0], pa[1], pa[2])
+    wb = codecs.nvfp4_dequantize(pb[0], pb[1], pb[2])
+    return "plain", (torch.cat([wa, wb], 1).to(rd.act),)
+
+
+def finalize(mw: ModelWeights, device, keep_rowmajor: bool = True) -> ModelWeights:
+    """Move to ``device``; on CUDA build the kernel tiles (and drop row-major copies if asked)."""
+    dev = torch.device(device)
+    def mv(t):
+        return None if t is None else t.to(dev)
+    def lin(q: QLinear | None):
+        if q is None:
+            return None
+        q = q.to(dev)
+        if dev.type == "cuda" and q.kind == "nvfp4" and q.tiles is None:
+            q.tiles = pack_tiles(q.packed, q.scale)
+            if not keep_rowmajor:
+                q.packed = q.scale = None
+        if dev.type == "cuda" and q.kind == "plain" and q.w.dtype != torch.bfloat16:
+            q.w = q.w.to(torch.bfloat16)
+        return q
+    def layer(lw: LayerWeights) -> LayerWeights:
+        m = lw.moe
+        return LayerWeights(lw.attention, mv(lw.input_norm), mv(lw.post_norm),
+                            MoEWeights(lin(m.router), lin(m.gate_up), lin(m.down), m.n_local, m.n_shared, m.expert0),
+                            lin(lw.qkv), lin(lw.o_proj), mv(lw.q_norm), mv(lw.k_norm), lin(lw.in_proj),
+                            lin(lw.out_proj), mv(lw.conv_w), mv(lw.a_log), mv(lw.dt_bias), mv(lw.gdn_norm))
+    out = ModelWeights(mv(mw.embed), mv(mw.final_norm), lin(mw.lm_head))
+    if dev.type == "cuda" and out.embed is not None:
+        out.embed = out.embed.to(torch.bfloat16)
+    out.layers = {i: layer(lw) for i, lw in mw.layers.items()}
+    if mw.mtp is not None:
+        out.mtp = MTPWeights(lin(mw.mtp.fc), mv(mw.mtp.norm_emb), mv(mw.mtp.norm_hidden), layer(mw.mtp.layer),
+                             mv(mw.mtp.final_norm))
+    return out
+
+
+# --------------------------------------------------------------------------- synthetic device weights
+class _UnitRandom:
+    """Random tensors keyed by GLOBAL coordinates (layer, tensor, head/expert/chunk), so a rank of
+    any TP/PP layout generates exactly the bytes a single-GPU run generates for the same unit."""
+
+    def __init__(self, seed: int, device):
+        self.seed, self.dev = seed, torch.device(device)
+        self.gen = torch.Generator(device=self.dev)
+
+    def _g(self, key: tuple) -> torch.Generator:
+        h = self.seed & 0xFFFFFFFF
+        for v in key:
+            h = (h * 1000003 + (int(v) + 0x9E3779B1)) % (1 << 61)
+        self.gen.manual_seed(h)
+        return self.gen
+
+    def nvfp4(self, n: int, k: int, key: tuple):
+        """Row-major NVFP4 unit: uniform e2m1 codes, block scales in [0.25, 1)."""
+        g = self._g(key)
+        packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=self.dev, generator=g)
+        scale = torch.randint(0x28, 0x38, (n, k // 16), dtype=torch.uint8, device=self.dev, generator=g)
+        return packed, scale
+
+    def normal(self, shape, key: tuple, std: float = 0.02, mean: float = 0.0) -> torch.Tensor:
+        return mean + std * torch.randn(shape, device=self.dev, generator=self._g(key), dtype=torch.float32)
+
+    def uniform(self, shape, key: tuple) -> torch.Tensor:
+        return torch.rand(shape, device=self.dev, generator=self._g(key), dtype=torch.float32)
+
+
+_NVFP4_ROW_SCALE = 0.02 / 1.7        # e2m1 codes (rms 2.9) x block scale (~0.58) x this ~ N(0, 0.02)
+
+
+def _q_from_units(units_rows: list, cols: bool = False) -> QLinear:
+    """Fuse generated units along rows (or along K when ``cols``) and tile-pack them."""
+    packed = torch.cat([u[0] for u in units_rows], 1 if cols else 0)
+    scale = torch.cat([u[1] for u in units_rows], 1 if cols else 0)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    rs = torch.full((n,), _NVFP4_ROW_SCALE, dtype=torch.float32, device=packed.device)
+    return QLinear(n, k, "nvfp4", row_scale=rs, tiles=pack_tiles(packed, scale))
+
+
+def synth_device_weights(cfg: ModelConfig, plan: ShardPlan, device, seed: int = 0, with_mtp: bool = True) -> ModelWeights:
+    """Random-init weights of the configured architecture created directly on the GPU in the
+    kernel's storage (no host copy, no checkpoint files): what a benchmark of a model too large
+    to materialise in fp32 uses.  Every tensor is a function of (seed, global coordinates) only,
+    so all parallel layouts serve the same model.  Row-major copies are not kept."""
+    if cfg.quant.method != "nvfp4":
+        raise ValueError("synthetic device weights are generated for NVFP4 configurations")
+    dev = torch.device(device)
+    R = _UnitRandom(seed, dev)
+    H, hd, I = cfg.hidden_size, cfg.head_dim, cfg.moe_intermediate_size
+    kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    bf = lambda t: t.to(torch.bfloat16)
+
+    def plain(n, k, key) -> QLinear:
+        return QLinear(n, k, "plain", w=bf(R.normal((n, k), key)),
+                       row_scale=torch.ones(n, dtype=torch.float32, device=dev))
+
+    def layer(L: int, attention: bool) -> LayerWeights:
+        lw = LayerWeights(attention, R.normal((H,), (L, 1)), R.normal((H,), (L, 2)), moe=None)
+        if attention:
+            rows = [R.nvfp4(2 * hd, H, (L, 10, h)) for h in range(*plan.q_heads)]
+            rows += [R.nvfp4(hd, H, (L, 11, h)) for h in range(*plan.kv_heads)]
+            rows += [R.nvfp4(hd, H, (L, 12, h)) for h in range(*plan.kv_heads)]
+            lw.qkv = _q_from_units(rows)
+            lw.o_proj = _q_from_units([R.nvfp4(H, hd, (L, 13, h)) for h in range(*plan.q_heads)], cols=True)
+            lw.q_norm, lw.k_norm = R.normal((hd,), (L, 14)), R.normal((hd,), (L, 15))
+        else:
+            kh, vh = range(*plan.gdn_k_heads), range(*plan.gdn_v_heads)
+            rows = [R.nvfp4(kd, H, (L, 20, h)) for h in kh] + [R.nvfp4(kd, H, (L, 21, h)) for h in kh]
+            rows += [R.nvfp4(vd, H, (L, 22, h)) for h in vh] + [R.nvfp4(vd, H, (L, 23, h)) for h in vh]
+            rows += [R.nvfp4(1, H, (L, 24, h)) for h in vh] + [R.nvfp4(1, H, (L, 25, h)) for h in vh]
+            lw.in_proj = _q_from_units(rows)
+            lw.out_proj = _q_from_units([R.nvfp4(H, vd, (L, 26, h)) for h in vh], cols=True)
+            conv = [R.normal((kd, 4), (L, 27, h), 0.3) for h in kh] + [R.normal((kd, 4), (L, 28, h), 0.3) for h in kh]
+            conv += [R.normal((vd, 4), (L, 29, h), 0.3) for h in vh]
+            lw.conv_w = torch.cat(conv, 0).contiguous()
+            lw.a_log = torch.cat([torch.log(1.0 + 15.0 * R.uniform((1,), (L, 30, h))) for h in vh])
+            lw.dt_bias = torch.cat([R.normal((1,), (L, 31, h), 0.5) for h in vh])
+            lw.gdn_norm = R.normal((vd,), (L, 32), mean=1.0)
+        ns = cfg.shared_expert_intermediate_size // I
+        ids = list(range(*plan.experts)) + [cfg.num_experts + j for j in range(ns)]
+        gu = [R.nvfp4(2 * I, H, (L, 40, e)) for e in ids]
+        dn = [R.nvfp4(H, I, (L, 41, e)) for e in ids]
+        ne = len(ids)
+        gate_up = QLinear(2 * I, H, "nvfp4", tiles=pack_tiles(torch.stack([u[0] for u in gu]), torch.stack([u[1] for u in gu])),
+                          row_scale=torch.full((ne, 2 * I), _NVFP4_ROW_SCALE, dtype=torch.float32, device=dev), e=ne)
+        down = QLinear(H, I, "nvfp4", tiles=pack_tiles(torch.stack([u[0] for u in dn]), torch.stack([u[1] for u in dn])),
+                       row_scale=torch.full((ne, H), _NVFP4_ROW_SCALE, dtype=torch.float32, device=dev), e=ne)
+        lw.moe = MoEWeights(plain(cfg.num_experts + 1, H, (L, 42)), gate_up, down,
+                            plan.experts[1] - plan.experts[0], ns, plan.experts[0])
+        return lw
+
+    mw = ModelWeights(None, None, None)
+    want_mtp = with_mtp and cfg.mtp_num_hidden_layers > 0 and plan.last_stage
+    if plan.first_stage or want_mtp:
+        mw.embed = bf(R.normal((cfg.vocab_size, H), (9000,)))
+    if plan.last_stage:
+        mw.final_norm = R.normal((H,), (9001,))
+        chunk = cfg.vocab_size // RANGES
+        c0, c1 = plan.vocab[0] // chunk, plan.vocab[1] // chunk
+        w = torch.cat([bf(R.normal((chunk, H), (9002, c))) for c in range(c0, c1)], 0)
+        mw.lm_head = QLinear(w.shape[0], H, "plain", w=w, row_scale=torch.ones(w.shape[0], dtype=torch.float32, device=dev))
+    for i in range(*plan.layers):
+        mw.layers[i] = layer(i, cfg.is_attention_layer(i))
+    if want_mtp:
+        mw.mtp = MTPWeights(plain(H, 2 * H, (9003,)), R.normal((H,), (9004,)), R.normal((H,), (9005,)),
+                            layer(100000, True), R.normal((H,), (9006,)))
+    return mw

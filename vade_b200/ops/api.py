@@ -1,0 +1,169 @@
+"""The op set the model is written against, and its plain-PyTorch implementation.
+
+``RefOps`` runs every op with ops/reference.py on whatever device the tensors live on (fp32
+math, activations rounded to ``act`` between ops).  It is the CPU execution path and the
+oracle of ``CudaOps`` (ops/cuda.py), which implements the same methods with the sm_100a
+kernels.  A method either returns new tensors or mutates the cache it is handed; no method
+keeps hidden state, so a step is a pure function of (weights, cache, batch).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config import ModelConfig, RANGES
+from . import reference as R
+
+
+@dataclass
+class Batch:
+    """Ragged rows of one engine step.  Rows of a sequence are contiguous and in position order."""
+    tokens: torch.Tensor            # int64 [T]
+    positions: torch.Tensor         # int64 [T] absolute positions
+    row_slot: torch.Tensor          # int64 [T] cache slot of each row
+    seq_slots: list                 # [B] slot per sequence
+    seq_start: list                 # [B+1] row offsets
+    seq_pos0: list                  # [B] absolute position of each sequence's first row
+    phase: str = "prefill"          # arithmetic class: "prefill" (prompt tiles) or "decode" (step / verify rows)
+    dev: dict = field(default_factory=dict)   # device copies of the sequence arrays (CUDA path)
+
+    @property
+    def rows(self) -> int:
+        return int(self.tokens.shape[0])
+
+    @staticmethod
+    def make(seqs: list, device="cpu", phase: str = "prefill") -> "Batch":
+        """seqs: [(slot, pos0, [token ids])]."""
+        toks, pos, slot, start, slots, pos0 = [], [], [], [0], [], []
+        for s, p0, ids in seqs:
+            toks += list(ids)
+            pos += list(range(p0, p0 + len(ids)))
+            slot += [s] * len(ids)
+            start.append(start[-1] + len(ids))
+            slots.append(s)
+            pos0.append(p0)
+        mk = lambda v: torch.tensor(v, dtype=torch.int64, device=device)
+        return Batch(mk(toks), mk(pos), mk(slot), slots, start, pos0, phase)
+
+
+class RefOps:
+    name = "reference"
+
+    def __init__(self, cfg: ModelConfig, act: torch.dtype = torch.float32):
+        self.cfg, self.act = cfg, act
+
+    # ---- basic
+    def embed(self, w: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        return w[tokens.long()].float()
+
+    def rmsnorm(self, x, w):
+        return R.rmsnorm(x, w, self.cfg.rms_norm_eps, True, self.act)
+
+    def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
+        y = R.dot_rows(h.float(), q.dense()) * q.row_scale
+        return y if out_fp32 else R._round(y, self.act)
+
+    def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
+        return R.linear_ranges(h.float(), q.dense(), n_ranges, 0, n_ranges) * q.row_scale
+
+    def fold_add_norm(self, parts, x, w):
+        x = x + R.fold_tree(parts)
+        return x, (self.rmsnorm(x, w) if w is not None else None)
+
+    # ---- token mixers
+    def gdn_mix(self, lw, proj, batch: Batch, cache, layer):
+        cfg = self.cfg
+        kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        vh = lw.a_log.shape[0]
+        kh = vh * cfg.linear_num_key_heads // cfg.linear_num_value_heads
+        C = 2 * kh * kd + vh * vd
+        p = proj.float()
+        raw, z = p[:, :C], p[:, C:C + vh * vd]
+        b, a = p[:, C + vh * vd:C + vh * vd + vh], p[:, C + vh * vd + vh:C + vh * vd + 2 * vh]
+        conv = R.gdn_conv(raw, lw.conv_w, cache.conv_hist[layer], batch.seq_slots, batch.seq_start, torch.float32)
+        T = p.shape[0]
+        q = R.l2norm(conv[:, :kh * kd].reshape(T, kh, kd)) * (kd ** -0.5)
+        k = R.l2norm(conv[:, kh * kd:2 * kh * kd].reshape(T, kh, kd))
+        v = conv[:, 2 * kh * kd:].reshape(T, vh, vd)
+        beta, g = R.gdn_gates(a, b, lw.a_log, lw.dt_bias)
+        state = cache.gdn_state[layer]
+        if batch.phase == "prefill":
+            o = R.gdn_chunked(q, k, v, beta, g, state, batch.seq_slots, batch.seq_start, batch.seq_pos0)
+        else:
+            o = R.gdn_recurrent(q, k, v, beta, g, state, batch.seq_slots, batch.seq_start)
+        return R.gdn_gated_norm(o, z.reshape(T, vh, vd), lw.gdn_norm, cfg.rms_norm_eps, self.act)
+
+    def attn_mix(self, lw, qkv, batch: Batch, cache, layer):
+        cfg = self.cfg
+        hd, rot = cfg.head_dim, cfg.rotary_dim
+        T = qkv.shape[0]
+        kp, vp = cache.k_pages[layer], cache.v_pages[layer]
+        nkv = kp.shape[2]
+        nq = (qkv.shape[1] - 2 * nkv * hd) // (2 * hd)
+        p = qkv.float()
+        qg = p[:, :nq * 2 * hd].reshape(T, nq, 2, hd)
+        q, gate = qg[:, :, 0], qg[:, :, 1]
+        k = p[:, nq * 2 * hd:nq * 2 * hd + nkv * hd].reshape(T, nkv, hd)
+        v = p[:, nq * 2 * hd + nkv * hd:].reshape(T, nkv, hd)
+        eps = cfg.rms_norm_eps
+        q = R.rmsnorm(q, lw.q_norm, eps, True, torch.float32)
+        k = R.rmsnorm(k, lw.k_norm, eps, True, torch.float32)
+        cos, sin = R.rope_tables(batch.positions, rot, cfg.rope_theta)
+        q = R._round(R.apply_rope(q, cos, sin, rot), self.act)
+        k = R._round(R.apply_rope(k, cos, sin, rot), self.act)
+        R.kv_append(k, v, kp, vp, cache.block_table, batch.row_slot, batch.positions)
+        o = R.attention_paged(q, kp, vp, cache.block_table, batch.seq_slots, batch.seq_start, batch.seq_pos0, hd ** -0.5)
+        return R._round((o * torch.sigmoid(gate)).reshape(T, nq * hd), self.act)
+
+    # ---- MoE
+    def route(self, logits):
+        cfg = self.cfg
+        E = cfg.num_experts
+        ids, w = R.route_topk(logits[:, :E], cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        return ids, w, torch.sigmoid(logits[:, E].float())
+
+    def moe_experts(self, mw, h, ids, phase: str = "prefill"):
+        """Outputs of the experts this rank holds: pair_out [T, k + ns, H] (rounded to ``act``),
+        owned bool [T, k + ns]."""
+        T, k = ids.shape
+        ns = mw.n_shared
+        H = mw.down.n
+        pair_out = torch.zeros(T, k + ns, H, dtype=torch.float32, device=h.device)
+        owned = torch.zeros(T, k + ns, dtype=torch.bool, device=h.device)
+        hf = h.float()
+
+        def expert(le, rows):
+            gu = R._round(R.dot_rows(hf[rows], mw.gate_up.dense(le)) * mw.gate_up.rs(le), self.act)
+            mid = R.swiglu(gu[:, 0::2], gu[:, 1::2], self.act)
+            return R._round(R.dot_rows(mid, mw.down.dense(le)) * mw.down.rs(le), self.act)
+
+        for le in range(mw.n_local):
+            t, j = torch.nonzero(ids == mw.expert0 + le, as_tuple=True)
+            if t.numel():
+                pair_out[t, j] = expert(le, t)
+                owned[t, j] = True
+        allrows = torch.arange(T, device=h.device)
+        for s in range(ns):
+            pair_out[:, k + s] = expert(mw.n_local + s, allrows)
+            owned[:, k + s] = True
+        return pair_out, owned
+
+    def combine_add_norm(self, pair_out, ids, w, sg, x, norm_w):
+        T, k = ids.shape
+        ns = pair_out.shape[1] - k
+        E = self.cfg.num_experts
+        ids_full = torch.cat([ids.long(), E + torch.arange(ns, device=ids.device).expand(T, ns)], 1)
+        w_full = torch.cat([w, sg.unsqueeze(1).expand(T, ns)], 1)
+        x = x + R.moe_combine(pair_out, ids_full, w_full)
+        return x, (self.rmsnorm(x, norm_w) if norm_w is not None else None)
+
+    # ---- head
+    def head_argmax(self, h, lm_head, vocab0: int):
+        logits = R.dot_rows(h.float(), lm_head.dense()) * lm_head.row_scale
+        idx = R.argmax_lowest(logits)
+        val = logits.gather(1, idx.unsqueeze(1)).squeeze(1)
+        return val, idx + vocab0
+
+    def head_logits(self, h, lm_head):
+        return R.dot_rows(h.float(), lm_head.dense()) * lm_head.row_scale

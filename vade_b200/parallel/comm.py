@@ -1,0 +1,102 @@
+"""Collectives of the tensor/expert-parallel group, all exact (bits move, sums never split).
+
+Only four exchanges exist in a forward pass, and none of them adds numbers across ranks in an
+arrival- or topology-dependent order:
+
+* ``gather_partials``  all-gather of fp32 canonical-range partial sums; every rank then folds
+  all ranges in the one fixed pair tree (ops.fold_tree), so the result does not depend on
+  how many ranks computed the partials.
+* ``gather_pairs``     all-gather of per-(token, expert) outputs, each produced by exactly one
+  rank; the ordered expert fold happens after the exchange.
+* ``merge_argmax``     12 bytes per row (value, id): larger logit wins, ties to the lower id.
+* ``gather_cols``      concatenation of column-parallel outputs (full logits for sampling).
+
+``LocalComm`` is the world-1 no-op, ``TorchComm`` the baseline over torch.distributed (gloo on
+CPU, NCCL on GPU).  The fused device-initiated versions live in parallel/symm.py and replace
+these calls on the GPU hot path.  Parity: the reference's ``Exchange`` trait and its no-op
+``LocalExchange`` (engine/crates/fabric/src/exchange.rs:7-33,
+engine/crates/engine/src/hybrid/tp_group.rs:20-25).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class LocalComm:
+    tp = 1
+    rank = 0
+
+    def gather_partials(self, parts: torch.Tensor) -> torch.Tensor:
+        return parts
+
+    def gather_pairs(self, pair_out: torch.Tensor, owned: torch.Tensor) -> torch.Tensor:
+        return pair_out
+
+    def merge_argmax(self, val: torch.Tensor, idx: torch.Tensor):
+        return val, idx
+
+    def gather_cols(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def broadcast(self, t: torch.Tensor, src: int = 0) -> torch.Tensor:
+        return t
+
+    def barrier(self) -> None:
+        pass
+
+
+class TorchComm(LocalComm):
+    """Baseline collectives through a torch.distributed process group."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.calls = {"gather_partials": 0, "gather_pairs": 0, "merge_argmax": 0, "gather_cols": 0}
+
+    def _all_gather(self, t: torch.Tensor) -> list:
+        t = t.contiguous()
+        outs = [torch.empty_like(t) for _ in range(self.tp)]
+        dist.all_gather(outs, t, group=self.group)
+        return outs
+
+    def gather_partials(self, parts: torch.Tensor) -> torch.Tensor:
+        self.calls["gather_partials"] += 1
+        return torch.cat(self._all_gather(parts), 0)
+
+    def gather_pairs(self, pair_out: torch.Tensor, owned: torch.Tensor) -> torch.Tensor:
+        """pair_out [T, slots, H] holds valid rows where ``owned`` [T, slots] is true on this rank
+        (exactly one rank owns each routed slot; replicated slots are owned by every rank)."""
+        self.calls["gather_pairs"] += 1
+        outs = self._all_gather(pair_out)
+        masks = self._all_gather(owned.to(torch.uint8))
+        full = pair_out.clone()
+        for r in range(self.tp):
+            if r == self.rank:
+                continue
+            take = masks[r].bool() & ~owned
+            full = torch.where(take.unsqueeze(-1), outs[r], full)
+        return full
+
+    def merge_argmax(self, val: torch.Tensor, idx: torch.Tensor):
+        self.calls["merge_argmax"] += 1
+        vals = torch.stack(self._all_gather(val.float()))
+        ids = torch.stack(self._all_gather(idx.to(torch.int64)))
+        best_v, best_i = vals[0], ids[0]
+        for r in range(1, self.tp):
+            better = (vals[r] > best_v) | ((vals[r] == best_v) & (ids[r] < best_i))
+            best_v = torch.where(better, vals[r], best_v)
+            best_i = torch.where(better, ids[r], best_i)
+        return best_v, best_i
+
+    def gather_cols(self, x: torch.Tensor) -> torch.Tensor:
+        self.calls["gather_cols"] += 1
+        return torch.cat(self._all_gather(x), -1)
+
+    def broadcast(self, t: torch.Tensor, src: int = 0) -> torch.Tensor:
+        dist.broadcast(t, dist.get_global_rank(self.group, src) if self.group is not None else src, group=self.group)
+        return t
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group)

@@ -1,0 +1,55 @@
+"""Process-group layout of one job: world = pp stages x tp ranks (one process per GPU).
+
+Global rank r sits in pipeline stage r // tp at tensor-parallel rank r % tp.  Expert
+parallelism uses the tensor-parallel group (whole experts per rank).  Data-parallel replicas
+are separate jobs behind the gateway (serve/gateway.py).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .comm import LocalComm, TorchComm
+from .pipeline import PipelineComm
+
+
+@dataclass
+class Parallel:
+    tp: int
+    pp: int
+    tp_rank: int
+    pp_rank: int
+    comm: object
+    pp_comm: object
+    tp_group: object = None
+
+
+def make_parallel(tp: int = 1, pp: int = 1, int_device="cpu") -> Parallel:
+    if tp * pp == 1 or not dist.is_initialized():
+        if tp * pp != 1:
+            raise RuntimeError("torch.distributed must be initialised for tp*pp > 1")
+        return Parallel(1, 1, 0, 0, LocalComm(), None)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if world != tp * pp:
+        raise ValueError(f"world size {world} != tp {tp} x pp {pp}")
+    stage, tr = divmod(rank, tp)
+    tp_group = None
+    pp_group = None
+    # every rank must create every group, in the same order
+    for s in range(pp):
+        g = dist.new_group([s * tp + i for i in range(tp)])
+        if s == stage:
+            tp_group = g
+    for i in range(tp):
+        g = dist.new_group([s * tp + i for s in range(pp)])
+        if i == tr:
+            pp_group = g
+    comm = TorchComm(tp_group) if tp > 1 else LocalComm()
+    pp_comm = None
+    if pp > 1:
+        prev = (stage - 1) * tp + tr if stage > 0 else None
+        nxt = (stage + 1) * tp + tr if stage < pp - 1 else None
+        pp_comm = PipelineComm(stage, pp, prev, nxt, (pp - 1) * tp + tr, pp_group, int_device)
+    return Parallel(tp, pp, tr, stage, comm, pp_comm, tp_group)

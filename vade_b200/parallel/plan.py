@@ -1,0 +1,102 @@
+"""Ownership of every tensor under tensor/expert/pipeline parallelism, in checkpoint coordinates.
+
+Column-parallel matrices (QKV+gate, GDN in-projections, expert gate/up, lm_head) are split by
+whole heads / whole experts / vocabulary rows and their outputs are concatenated, never summed.
+Row-parallel matrices (o_proj, GDN out_proj) are split along K at canonical-range boundaries:
+K is cut into ``RANGES`` equal ranges at every world size, a rank owns ``RANGES / tp``
+consecutive ranges, and the partial sums are joined in one fixed pair tree, so TP=1/2/4/8
+produce the same bits.  Routed experts are owned whole (expert parallel over the same group);
+the shared expert, router, embeddings and norms are replicated.
+Parity: engine/crates/model/src/flash/plan.rs:165-317 (RankPlan), shard.rs:71-205 (ShardPlan).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from ..config import ModelConfig, RANGES
+
+
+def partition(total: int, parts: int, index: int) -> tuple:
+    """Contiguous uneven partition [begin, end) of ``total`` items (first ranks get the extra)."""
+    base, extra = divmod(total, parts)
+    begin = index * base + min(index, extra)
+    return begin, begin + base + (1 if index < extra else 0)
+
+
+@dataclass(frozen=True)
+class ShardPlan:
+    tp: int = 1
+    tp_rank: int = 0
+    pp: int = 1
+    pp_rank: int = 0
+    # derived, filled by make_plan
+    q_heads: tuple = (0, 0)
+    kv_heads: tuple = (0, 0)
+    gdn_k_heads: tuple = (0, 0)
+    gdn_v_heads: tuple = (0, 0)
+    experts: tuple = (0, 0)
+    vocab: tuple = (0, 0)
+    ranges: tuple = (0, RANGES)
+    layers: tuple = (0, 0)
+
+    @property
+    def first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def last_stage(self) -> bool:
+        return self.pp_rank == self.pp - 1
+
+    def owns_expert(self, e: int) -> bool:
+        return self.experts[0] <= e < self.experts[1]
+
+
+def make_plan(cfg: ModelConfig, tp: int = 1, tp_rank: int = 0, pp: int = 1, pp_rank: int = 0) -> ShardPlan:
+    def need(ok, msg):
+        if not ok:
+            raise ValueError(f"cannot shard: {msg}")
+    need(tp >= 1 and 0 <= tp_rank < tp and pp >= 1 and 0 <= pp_rank < pp, "bad rank")
+    need(RANGES % tp == 0, f"tensor parallel size {tp} must divide {RANGES} canonical ranges")
+    need(cfg.num_attention_heads % tp == 0, "attention heads not divisible by tp")
+    need(cfg.linear_num_key_heads % tp == 0 and cfg.linear_num_value_heads % tp == 0, "GDN heads not divisible by tp")
+    need(cfg.num_experts % tp == 0, "experts not divisible by tp")
+    need(cfg.vocab_size % tp == 0, "vocabulary not divisible by tp")
+    need(cfg.num_hidden_layers >= pp, "more pipeline stages than layers")
+    nh = cfg.num_attention_heads // tp
+    q = (tp_rank * nh, (tp_rank + 1) * nh)
+    kvh = cfg.num_key_value_heads
+    if kvh % tp == 0:
+        kv = (tp_rank * (kvh // tp), (tp_rank + 1) * (kvh // tp))
+    else:
+        # a KV head is replicated on every rank that holds one of its query heads
+        need(tp % kvh == 0, "kv heads and tp must divide one another")
+        group = cfg.num_attention_heads // kvh
+        first = q[0] // group
+        last = (q[1] - 1) // group
+        need(first == last, "a rank's query heads straddle KV heads")
+        kv = (first, first + 1)
+    gk = cfg.linear_num_key_heads // tp
+    gv = cfg.linear_num_value_heads // tp
+    ne = cfg.num_experts // tp
+    nv = cfg.vocab_size // tp
+    rl = RANGES // tp
+    layers = partition(cfg.num_hidden_layers, pp, pp_rank)
+    return ShardPlan(tp, tp_rank, pp, pp_rank, q, kv, (tp_rank * gk, (tp_rank + 1) * gk),
+                     (tp_rank * gv, (tp_rank + 1) * gv), (tp_rank * ne, (tp_rank + 1) * ne),
+                     (tp_rank * nv, (tp_rank + 1) * nv), (tp_rank * rl, (tp_rank + 1) * rl), layers)
+
+
+def cache_bytes_per_token(cfg: ModelConfig, plan: ShardPlan, kv_itemsize: int = 2) -> int:
+    """KV bytes one token costs on this rank (attention layers of this stage only)."""
+    n_attn = sum(1 for i in range(*plan.layers) if cfg.is_attention_layer(i))
+    kvh = plan.kv_heads[1] - plan.kv_heads[0]
+    return n_attn * 2 * kvh * cfg.head_dim * kv_itemsize
+
+
+def state_bytes_per_sequence(cfg: ModelConfig, plan: ShardPlan) -> int:
+    """Recurrent-state bytes one sequence costs on this rank: S[vh][kd][vd] fp32 + 3 conv rows."""
+    n_gdn = sum(1 for i in range(*plan.layers) if not cfg.is_attention_layer(i))
+    vh = plan.gdn_v_heads[1] - plan.gdn_v_heads[0]
+    kh = plan.gdn_k_heads[1] - plan.gdn_k_heads[0]
+    conv = 2 * kh * cfg.linear_key_head_dim + vh * cfg.linear_value_head_dim
+    return n_gdn * (vh * cfg.linear_key_head_dim * cfg.linear_value_head_dim * 4 + 3 * conv * 4)

@@ -1,0 +1,47 @@
+"""Assembles an Engine for one rank from a config + weight source (the call every entry point uses)."""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..models.hybrid import HybridModel
+from ..models import weights as W
+from ..ops.api import RefOps
+from ..parallel.comm import LocalComm
+from ..parallel.plan import make_plan
+from .cache import Cache
+from .engine import Engine
+
+
+def make_ops(cfg: ModelConfig, device, act: torch.dtype, reference: bool = False):
+    dev = torch.device(device)
+    if dev.type == "cuda" and not reference:
+        from ..ops.cuda import CudaOps
+        return CudaOps(cfg, dev)
+    return RefOps(cfg, act)
+
+
+def build_engine(cfg: ModelConfig, source=None, *, device="cpu", act: torch.dtype | None = None,
+                 tp: int = 1, tp_rank: int = 0, pp: int = 1, pp_rank: int = 0, comm=None, pp_comm=None,
+                 slots: int = 4, max_seq: int = 4096, pages: int | None = None, seed: int = 0,
+                 prefill_chunk: int = 2048, reference_ops: bool = False, synth_on_device: bool = False,
+                 with_mtp: bool = True, keep_rowmajor: bool = True) -> Engine:
+    """source: a tensor source (checkpoint.synth.DictSource / IndexSource) or None for random init."""
+    dev = torch.device(device)
+    if act is None:
+        act = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    plan = make_plan(cfg, tp, tp_rank, pp, pp_rank)
+    if synth_on_device:
+        weights = W.synth_device_weights(cfg, plan, dev, seed, with_mtp)
+    else:
+        if source is None:
+            from ..checkpoint.synth import synth_state_dict, DictSource
+            source = DictSource(synth_state_dict(cfg, seed))
+        weights = W.load_weights(cfg, source, plan, act, dev, with_mtp, keep_rowmajor)
+    ops = make_ops(cfg, dev, act, reference_ops)
+    comm = comm or LocalComm()
+    model = HybridModel(cfg, weights, plan, ops, comm)
+    if pages is None:
+        pages = slots * (-(-max_seq // 64))
+    cache = Cache(cfg, plan, slots, pages, max_seq, act, dev, mtp=with_mtp)
+    return Engine(model, cache, prefill_chunk, pp_comm)

@@ -1,0 +1,167 @@
+"""Paged KV cache + Gated-DeltaNet recurrent-state cache, one instance per rank.
+
+* KV: per attention layer two page pools ``[pages, 64, kv_heads_local, head_dim]``; a sequence
+  slot owns a row of the block table.  Pages are 64 tokens, the alignment every exactness rule
+  of the engine uses (prompt tiles, GDN chunks, prefix checkpoints).
+* GDN: per linear-attention layer ``S[slots, v_heads_local, kd, vd]`` fp32 plus the last three
+  raw in-projection rows ``[slots, 3, conv_dim_local]`` for the causal conv.
+* Snapshots copy a slot's recurrent state (and remember its length) so speculative decoding can
+  roll back and the prefix cache can resume; KV needs no copy because positions are truncated.
+
+Parity: the reference's VMM-paged KV arenas and per-chat state
+(engine/crates/gpu/src/segments.rs:15,529; engine/crates/serve/src/kv_pages.rs), prefix
+checkpoints at 64-token boundaries (engine/crates/engine/src/flash/next_prefix.rs:1-60).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..config import ModelConfig
+from ..parallel.plan import ShardPlan
+
+PAGE = 64
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PageAllocator:
+    """LIFO free list with reference counts (shared prefix pages are counted, not copied)."""
+
+    def __init__(self, pages: int):
+        self.total = pages
+        self.free = list(range(pages - 1, -1, -1))
+        self.refs = [0] * pages
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise OutOfPages("KV page pool exhausted")
+        p = self.free.pop()
+        self.refs[p] = 1
+        return p
+
+    def retain(self, p: int) -> None:
+        assert self.refs[p] > 0
+        self.refs[p] += 1
+
+    def release(self, p: int) -> None:
+        assert self.refs[p] > 0
+        self.refs[p] -= 1
+        if self.refs[p] == 0:
+            self.free.append(p)
+
+    @property
+    def available(self) -> int:
+        return len(self.free)
+
+
+@dataclass
+class StateSnapshot:
+    length: int
+    gdn: dict
+    conv: dict
+
+
+class Cache:
+    def __init__(self, cfg: ModelConfig, plan: ShardPlan, slots: int, pages: int, max_seq: int,
+                 act: torch.dtype = torch.float32, device="cpu", mtp: bool = True):
+        self.cfg, self.plan = cfg, plan
+        self.slots, self.max_pages = slots, -(-max_seq // PAGE)
+        self.device = torch.device(device)
+        kvh = plan.kv_heads[1] - plan.kv_heads[0]
+        vh = plan.gdn_v_heads[1] - plan.gdn_v_heads[0]
+        kh = plan.gdn_k_heads[1] - plan.gdn_k_heads[0]
+        kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        conv = 2 * kh * kd + vh * vd
+        self.k_pages, self.v_pages, self.gdn_state, self.conv_hist = {}, {}, {}, {}
+        keys = list(range(*plan.layers))
+        if mtp and cfg.mtp_num_hidden_layers and plan.last_stage:
+            keys.append("mtp")
+        for i in keys:
+            if i == "mtp" or cfg.is_attention_layer(i):
+                self.k_pages[i] = torch.zeros(pages, PAGE, kvh, cfg.head_dim, dtype=act, device=self.device)
+                self.v_pages[i] = torch.zeros(pages, PAGE, kvh, cfg.head_dim, dtype=act, device=self.device)
+            else:
+                self.gdn_state[i] = torch.zeros(slots, vh, kd, vd, dtype=torch.float32, device=self.device)
+                self.conv_hist[i] = torch.zeros(slots, 3, conv, dtype=torch.float32, device=self.device)
+        self.block_table = torch.zeros(slots, self.max_pages, dtype=torch.int32, device=self.device)
+        self._table_host = [[-1] * self.max_pages for _ in range(slots)]
+        self.alloc = PageAllocator(pages)
+        self.free_slots = list(range(slots - 1, -1, -1))
+        self.length = [0] * slots
+
+    # ---- slots
+    def new_slot(self) -> int:
+        if not self.free_slots:
+            raise OutOfPages("no free sequence slot")
+        s = self.free_slots.pop()
+        self.length[s] = 0
+        for st in self.gdn_state.values():
+            st[s].zero_()
+        for h in self.conv_hist.values():
+            h[s].zero_()
+        return s
+
+    def free_slot(self, s: int) -> None:
+        for i, p in enumerate(self._table_host[s]):
+            if p >= 0:
+                self.alloc.release(p)
+                self._table_host[s][i] = -1
+        self.length[s] = 0
+        self.free_slots.append(s)
+
+    def ensure(self, s: int, length: int) -> None:
+        """Map pages so that positions < length are backed (done before any kernel of the step)."""
+        need = -(-length // PAGE)
+        if need > self.max_pages:
+            raise OutOfPages(f"sequence of {length} tokens exceeds the context limit")
+        changed = False
+        for i in range(need):
+            if self._table_host[s][i] < 0:
+                self._table_host[s][i] = self.alloc.alloc()
+                changed = True
+        if changed:
+            row = [p if p >= 0 else 0 for p in self._table_host[s]]
+            self.block_table[s] = torch.tensor(row, dtype=torch.int32, device=self.device)
+
+    def truncate(self, s: int, length: int) -> None:
+        """Drop KV positions >= length (pages wholly beyond it go back to the pool)."""
+        keep = -(-length // PAGE)
+        for i in range(keep, self.max_pages):
+            p = self._table_host[s][i]
+            if p >= 0:
+                self.alloc.release(p)
+                self._table_host[s][i] = -1
+        self.length[s] = length
+
+    def share_prefix(self, src: int, dst: int, length: int) -> None:
+        """dst adopts src's first ``length`` tokens (a multiple of the page size): pages are shared."""
+        assert length % PAGE == 0
+        for i in range(length // PAGE):
+            p = self._table_host[src][i]
+            self.alloc.retain(p)
+            self._table_host[dst][i] = p
+        row = [p if p >= 0 else 0 for p in self._table_host[dst]]
+        self.block_table[dst] = torch.tensor(row, dtype=torch.int32, device=self.device)
+        self.length[dst] = length
+
+    # ---- recurrent-state snapshots
+    def snapshot(self, s: int) -> StateSnapshot:
+        return StateSnapshot(self.length[s], {i: st[s].clone() for i, st in self.gdn_state.items()},
+                             {i: h[s].clone() for i, h in self.conv_hist.items()})
+
+    def restore(self, s: int, snap: StateSnapshot) -> None:
+        for i, st in snap.gdn.items():
+            self.gdn_state[i][s].copy_(st)
+        for i, h in snap.conv.items():
+            self.conv_hist[i][s].copy_(h)
+        self.truncate(s, snap.length)
+
+    def state_bytes(self) -> int:
+        n = 0
+        for d in (self.k_pages, self.v_pages, self.gdn_state, self.conv_hist):
+            n += sum(t.numel() * t.element_size() for t in d.values())
+        return n

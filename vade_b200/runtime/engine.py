@@ -1,0 +1,240 @@
+"""Model execution engine of one rank: prompt tiles, decode steps, MTP drafting and verification.
+
+``Engine`` owns the model, its cache and the arithmetic-class rules that make tokens
+reproducible:
+
+* prompt rows always run in the "prefill" class, in tiles that start on absolute multiples of
+  64 tokens (so GDN chunks, KV pages and prefix checkpoints see the same cuts however a prompt
+  is sliced);
+* generated tokens always run in the "decode" class, whether alone, batched with other chats,
+  or as the rows of a speculative verify pass, and every row's arithmetic is independent of
+  the rows beside it.
+
+Speculative decoding is exact: the target verifies the draft rows itself and keeps a draft
+token only while it equals the target's own choice for that position.
+Parity: engine/crates/engine/src/flash/next_batched.rs:1094-1296 (sessions, prefill/step),
+next_execution.rs:676-790 (run_rows), next_mtp.rs:779-1053 (propose/verify/commit),
+draft.rs:822-828 (greedy acceptance).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config import ModelConfig
+from ..models.hybrid import HybridModel
+from ..ops.api import Batch
+from .cache import Cache, PAGE
+from .sampler import Sampling, sample
+
+
+@dataclass
+class Sequence:
+    slot: int
+    tokens: list = field(default_factory=list)      # prompt + generated so far
+    n_prompt: int = 0
+    sampling: Sampling = field(default_factory=Sampling)
+    last_x: torch.Tensor | None = None               # residual row of the last processed position (MTP input)
+    next_token: int | None = None                    # token chosen for position len(tokens), not yet processed
+    drafted: int = 0
+    accepted: int = 0
+    generated: list = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, model: HybridModel, cache: Cache, prefill_chunk: int = 2048, pp_comm=None):
+        assert prefill_chunk % PAGE == 0
+        self.model, self.cache = model, cache
+        self.cfg: ModelConfig = model.cfg
+        self.prefill_chunk = prefill_chunk
+        self.pp = pp_comm
+        self.device = cache.device
+        self.steps = 0
+
+    # ------------------------------------------------------------------ stage plumbing
+    def _run(self, batch: Batch):
+        """One pass over this rank's layers, with pipeline hand-over when pp > 1."""
+        plan = self.model.plan
+        hidden = None
+        if self.pp is not None and not plan.first_stage:
+            hidden = self.pp.recv_rows(batch.rows, self.cfg.hidden_size, self.device)
+        x, h = self.model.forward(batch, self.cache, hidden)
+        if self.pp is not None and not plan.last_stage:
+            self.pp.send_rows(x)
+        self.steps += 1
+        return x, h
+
+    # ------------------------------------------------------------------ prompt
+    def prefill(self, seq: Sequence, ids: list):
+        """Append prompt tokens ``ids`` to the sequence in 64-aligned tiles; returns (x, h) of the
+        LAST row only (None on non-final pipeline stages)."""
+        pos = len(seq.tokens)
+        x = h = None
+        done = 0
+        while done < len(ids):
+            room = self.prefill_chunk - (pos % self.prefill_chunk)
+            n = min(room, len(ids) - done)
+            self.cache.ensure(seq.slot, pos + n)
+            batch = Batch.make([(seq.slot, pos, ids[done:done + n])], self.device, "prefill")
+            x, h = self._run(batch)
+            pos += n
+            done += n
+        seq.tokens += list(ids)
+        self.cache.length[seq.slot] = pos
+        if h is None:
+            return None, None
+        seq.last_x = x[-1:].clone()
+        return x[-1:], h[-1:]
+
+    # ------------------------------------------------------------------ decode rows
+    def step(self, seqs: list, rows: list):
+        """Decode-class pass: ``rows[i]`` are the tokens sequence i appends (1 for a plain step,
+        1 + depth for a verify pass).  Returns (x, h) for all rows in order."""
+        items = []
+        for seq, toks in zip(seqs, rows):
+            pos = len(seq.tokens)
+            self.cache.ensure(seq.slot, pos + len(toks))
+            items.append((seq.slot, pos, toks))
+        batch = Batch.make(items, self.device, "decode")
+        return self._run(batch)
+
+    def choose(self, seq: Sequence, h_row: torch.Tensor, position: int, history: list | None = None) -> int:
+        """The target's token for ``position`` from final-norm row ``h_row`` [1, H]."""
+        if seq.sampling.plain_greedy:
+            return int(self.model.greedy(h_row)[0])
+        logits = self.model.logits(h_row)[0]
+        return sample(logits, seq.sampling, position, seq.tokens if history is None else history)
+
+    # ------------------------------------------------------------------ MTP
+    def propose(self, seq: Sequence, first: int, depth: int) -> list:
+        """Draft ``depth`` tokens after ``first`` (the already chosen next token) with the MTP block.
+        The draft block keeps its own KV under cache key "mtp"; its position p holds the pair
+        (token p+1, trunk residual p).  Draft rows are never trusted: verify decides."""
+        m = self.model
+        drafts, tok, hid = [], first, seq.last_x
+        base = len(seq.tokens) - 1                       # trunk position whose residual we hold
+        snap_len = self.cache.length[seq.slot]
+        self.cache.ensure(seq.slot, base + depth + 1)
+        for d in range(depth):
+            batch = Batch.make([(seq.slot, base + d, [tok])], self.device, "decode")
+            x, h = m.mtp_forward(batch, self.cache, hid)
+            tok = int(m.greedy(h)[0])
+            drafts.append(tok)
+            hid = x
+        self.cache.length[seq.slot] = snap_len
+        return drafts
+
+    def mtp_prefill(self, seq: Sequence, ids: list, xs: torch.Tensor, pos0: int):
+        """Feed prompt pairs (token p+1, residual p) to the draft block so its KV covers the prompt."""
+        batch = Batch.make([(seq.slot, pos0, ids)], self.device, "prefill")
+        self.model.mtp_forward(batch, self.cache, xs)
+
+    # ------------------------------------------------------------------ generation of one chat
+    def generate(self, prompt: list, max_new: int, sampling: Sampling | None = None, draft_depth: int = 0,
+                 eos: int | None = None, on_token=None) -> Sequence:
+        """Greedy/sampled generation of one sequence; with ``draft_depth`` > 0 the MTP block drafts
+        and the trunk verifies, emitting exactly the tokens of the undrafted run.  With pipeline
+        stages the last stage owns every decision and tells the others (row lists, accept counts)."""
+        cache = self.cache
+        seq = Sequence(cache.new_slot(), [], len(prompt), sampling or Sampling())
+        last = self.model.plan.last_stage
+        can_draft = draft_depth > 0 and seq.sampling.plain_greedy and self.cfg.mtp_num_hidden_layers > 0
+        use_mtp = can_draft and last and self.model.w.mtp is not None
+        if use_mtp:
+            x_last, h_last = self._prefill_with_mtp(seq, prompt)
+        else:
+            x_last, h_last = self.prefill(seq, prompt)
+        out = []
+        nxt = self.choose(seq, h_last, len(seq.tokens)) if last else 0
+        done = False
+        while not done:
+            # ---- rows of this pass: the chosen token plus (optionally) draft tokens after it
+            depth = min(draft_depth, max_new - len(out) - 1) if can_draft else 0
+            drafts = self.propose(seq, nxt, depth) if (use_mtp and depth > 0) else []
+            rows = self._bcast([nxt] + drafts)
+            if len(rows) == 1:
+                out.append(rows[0])
+                if on_token:
+                    on_token(rows[0])
+                if (eos is not None and rows[0] == eos) or len(out) >= max_new:
+                    seq.tokens.append(rows[0])
+                    break
+            snap = cache.snapshot(seq.slot) if len(rows) > 1 else None
+            x, h = self.step([seq], [rows])
+            keep, targets = 1, [0]
+            if last:
+                if len(rows) > 1 or seq.sampling.plain_greedy:
+                    targets = [int(t) for t in self.model.greedy(h)]
+                else:
+                    targets = [self.choose(seq, h[-1:], len(seq.tokens) + 1, seq.tokens + rows)]
+                while keep < len(rows) and rows[keep] == targets[keep - 1]:
+                    keep += 1
+            keep, nxt = self._bcast([keep, targets[keep - 1]])
+            if keep < len(rows):
+                # a draft row was wrong: rewind the recurrent state and replay the kept rows
+                cache.restore(seq.slot, snap)
+                x, h = self.step([seq], [rows[:keep]])
+            if len(rows) > 1:
+                seq.drafted += len(rows) - 1
+                seq.accepted += keep - 1
+            prev_x = seq.last_x
+            seq.tokens += rows[:keep]
+            cache.length[seq.slot] = len(seq.tokens)
+            if last:
+                if use_mtp:
+                    self._mtp_catch_up(seq, rows[:keep], prev_x, x[:keep])
+                seq.last_x = x[keep - 1:keep].clone()
+            if len(rows) > 1:
+                for t in rows[:keep]:
+                    out.append(t)
+                    if on_token:
+                        on_token(t)
+                    if (eos is not None and t == eos) or len(out) >= max_new:
+                        done = True
+                        break
+        seq.generated = out[:max_new]
+        return seq
+
+    # ---- helpers
+    def _bcast(self, values: list) -> list:
+        """Every pipeline stage needs the decisions of the last stage (tokens, accept counts)."""
+        if self.pp is None:
+            return list(values)
+        return self.pp.broadcast_ints(values)
+
+    def _prefill_with_mtp(self, seq: Sequence, prompt: list):
+        """Prompt pass that also fills the draft block's KV with (token p+1, residual p) pairs."""
+        pos = 0
+        x = h = None
+        pend_x = None            # residual of the last row of the previous tile
+        done = 0
+        while done < len(prompt):
+            room = self.prefill_chunk - (pos % self.prefill_chunk)
+            n = min(room, len(prompt) - done)
+            self.cache.ensure(seq.slot, pos + n)
+            batch = Batch.make([(seq.slot, pos, prompt[done:done + n])], self.device, "prefill")
+            x, h = self._run(batch)
+            # pairs inside this tile: positions pos..pos+n-2 get token at p+1; plus the pending one
+            xs, ids, p0 = x[:n - 1], prompt[done + 1:done + n], pos
+            if pend_x is not None:
+                xs, ids, p0 = torch.cat([pend_x, xs], 0), [prompt[done]] + ids, pos - 1
+            if ids:
+                self.mtp_prefill(seq, ids, xs, p0)
+            pend_x = x[n - 1:n].clone()
+            pos += n
+            done += n
+        seq.tokens += list(prompt)
+        self.cache.length[seq.slot] = pos
+        seq.last_x = pend_x
+        return x[-1:], h[-1:]
+
+    def _mtp_catch_up(self, seq: Sequence, rows: list, prev_x: torch.Tensor, xs: torch.Tensor) -> None:
+        """After accepting ``rows`` the draft block must hold the true pair of every trunk position
+        except the newest: write (rows[i], residual of the position before it) for the accepted rows.
+        ``prev_x`` is the residual of the position before rows[0]; seq.tokens already ends with rows."""
+        n = len(rows)
+        base = len(seq.tokens) - n - 1                  # trunk position of prev_x
+        hid = torch.cat([prev_x, xs[:n - 1]], 0) if n > 1 else prev_x
+        batch = Batch.make([(seq.slot, base, rows)], self.device, "decode")
+        self.model.mtp_forward(batch, self.cache, hid)
