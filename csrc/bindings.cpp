@@ -1,0 +1,164 @@
+// Python bindings of the sm_100a kernels: thin argument checks, then the C++ launchers.
+// Every function launches on the current PyTorch CUDA stream and allocates nothing.
+#include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "attn/attn.h"
+#include "gdn/gdn_scan.h"
+#include "gemm/umma_gemm.h"
+#include "head/head.h"
+#include "moe/route.h"
+#include "norm/rows.h"
+
+namespace {
+
+cudaStream_t stream_of(const torch::Tensor& t) { return c10::cuda::getCurrentCUDAStream(t.device().index()).stream(); }
+
+void check(const char* err) {
+    if (err != nullptr) throw std::runtime_error(std::string("vade_b200 kernel: ") + err);
+}
+
+void need(bool ok, const char* msg) {
+    if (!ok) throw std::runtime_error(std::string("vade_b200 kernel: ") + msg);
+}
+
+template <typename T>
+T* ptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? static_cast<T*>(t->data_ptr()) : nullptr; }
+
+// D = W X^T on tcgen05.  w: NVFP4 tile blocks (uint8) or bf16 [n_out, k]; x: bf16 [rows, ldx].
+void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tensor out, int64_t k, int64_t n_out, bool nvfp4,
+          int64_t epilogue, int64_t bn, int64_t ranges, int64_t tokens, int64_t ldo, int64_t out_range_stride,
+          c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
+          c10::optional<torch::Tensor> status) {
+    need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows on the GPU");
+    need(w.is_cuda() && w.is_contiguous() && row_scale.is_cuda() && row_scale.scalar_type() == torch::kFloat32, "bad weights");
+    need(out.is_cuda(), "bad output");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::GemmArgs a;
+    a.x = x.data_ptr(); a.x_rows = static_cast<int>(x.size(0)); a.ldx = static_cast<int>(x.stride(0)); a.k = static_cast<int>(k);
+    a.w = w.data_ptr(); a.nvfp4 = nvfp4; a.row_scale = row_scale.data_ptr<float>(); a.n_out = static_cast<int>(n_out);
+    a.out = out.data_ptr(); a.ldo = static_cast<int>(ldo); a.out_range_stride = out_range_stride; a.epilogue = static_cast<int>(epilogue);
+    a.tokens = static_cast<int>(tokens); a.bn = static_cast<int>(bn); a.ranges = static_cast<int>(ranges);
+    if (tasks.has_value()) {
+        need(meta.has_value(), "grouped GEMM needs the task count");
+        a.tasks = tasks->data_ptr<int>(); a.num_tasks = meta->data_ptr<int>(); a.max_tasks = static_cast<int>(max_tasks);
+    }
+    a.status = status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+    check(vade::umma_gemm(a, stream_of(x)));
+}
+
+void embed(torch::Tensor table, torch::Tensor tokens, torch::Tensor x) {
+    need(table.scalar_type() == torch::kBFloat16 && tokens.scalar_type() == torch::kInt64 && x.scalar_type() == torch::kFloat32, "embed dtypes");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::embed(table.data_ptr(), tokens.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()) : nullptr,
+                x.data_ptr<float>(), static_cast<int>(tokens.numel()), static_cast<int>(table.size(1)), stream_of(x));
+}
+
+void rmsnorm(torch::Tensor x, torch::Tensor w, torch::Tensor h, double eps, int64_t ldh, int64_t h_off) {
+    need(x.is_contiguous() && w.scalar_type() == torch::kFloat32 && h.scalar_type() == torch::kBFloat16, "rmsnorm dtypes");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::rmsnorm(x.data_ptr(), x.scalar_type() == torch::kBFloat16, w.data_ptr<float>(), h.data_ptr(), static_cast<int>(x.size(0)),
+                  static_cast<int>(x.size(1)), static_cast<float>(eps), static_cast<int>(ldh), static_cast<int>(h_off), stream_of(x));
+}
+
+void fold_add_norm(torch::Tensor parts, int64_t n_parts, int64_t part_stride, torch::Tensor x, c10::optional<torch::Tensor> w,
+                   c10::optional<torch::Tensor> h, double eps) {
+    need(parts.scalar_type() == torch::kFloat32 && x.scalar_type() == torch::kFloat32 && x.is_contiguous(), "fold dtypes");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::fold_add_norm(parts.data_ptr<float>(), part_stride, static_cast<int>(n_parts), x.data_ptr<float>(), ptr<float>(w),
+                        h.has_value() ? h->data_ptr() : nullptr, static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                        static_cast<float>(eps), stream_of(x));
+}
+
+void combine_add_norm(torch::Tensor y, torch::Tensor slot_row, torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, int64_t k,
+                      int64_t ns, torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> h, double eps) {
+    need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 64, "combine arguments");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::combine_add_norm(y.data_ptr(), slot_row.data_ptr<int>(), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
+                           static_cast<int>(k), static_cast<int>(ns), x.data_ptr<float>(), ptr<float>(w),
+                           h.has_value() ? h->data_ptr() : nullptr, static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                           static_cast<float>(eps), stream_of(x));
+}
+
+void gather_rows(torch::Tensor x, torch::Tensor row_token, torch::Tensor meta, torch::Tensor xs, int64_t max_rows) {
+    need(x.scalar_type() == torch::kBFloat16 && xs.scalar_type() == torch::kBFloat16 && x.size(1) % 8 == 0, "gather arguments");
+    c10::cuda::CUDAGuard guard(x.device());
+    vade::gather_rows(x.data_ptr(), row_token.data_ptr<int>(), meta.data_ptr<int>() + 1, xs.data_ptr(), static_cast<int>(max_rows),
+                      static_cast<int>(x.size(1)), stream_of(x));
+}
+
+void moe_route(torch::Tensor logits, int64_t E, int64_t k, bool renorm, int64_t e0, int64_t n_local, int64_t ns, int64_t bn,
+               torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, torch::Tensor counts, torch::Tensor pos, torch::Tensor offsets,
+               torch::Tensor tasks, torch::Tensor meta, int64_t max_tasks, torch::Tensor row_token, torch::Tensor slot_row) {
+    need(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 && E <= 1024 && k <= 32, "route arguments");
+    c10::cuda::CUDAGuard guard(logits.device());
+    vade::moe_route(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), static_cast<int>(logits.size(0)), static_cast<int>(E),
+                    static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local), static_cast<int>(ns), static_cast<int>(bn),
+                    ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(), counts.data_ptr<int>(), pos.data_ptr<int>(),
+                    offsets.data_ptr<int>(), tasks.data_ptr<int>(), meta.data_ptr<int>(), static_cast<int>(max_tasks),
+                    row_token.data_ptr<int>(), slot_row.data_ptr<int>(), stream_of(logits));
+}
+
+void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
+              torch::Tensor dt_bias, torch::Tensor norm_w, torch::Tensor seq_slot, torch::Tensor seq_start, int64_t n_seq,
+              torch::Tensor out, int64_t kh, int64_t vh, int64_t kd, int64_t vd, double eps, bool gate_silu) {
+    need(proj.scalar_type() == torch::kBFloat16 && proj.stride(1) == 1 && state.scalar_type() == torch::kFloat32 &&
+         hist.scalar_type() == torch::kFloat32 && out.scalar_type() == torch::kBFloat16 && out.is_contiguous(), "gdn arguments");
+    c10::cuda::CUDAGuard guard(proj.device());
+    check(vade::gdn_scan(proj.data_ptr(), static_cast<int>(proj.stride(0)), conv_w.data_ptr<float>(), hist.data_ptr<float>(),
+                         state.data_ptr<float>(), a_log.data_ptr<float>(), dt_bias.data_ptr<float>(), norm_w.data_ptr<float>(),
+                         seq_slot.data_ptr<int>(), seq_start.data_ptr<int>(), static_cast<int>(n_seq), out.data_ptr(),
+                         static_cast<int>(kh), static_cast<int>(vh), static_cast<int>(kd), static_cast<int>(vd),
+                         static_cast<float>(eps), gate_silu, stream_of(proj)));
+}
+
+void attn_prep(torch::Tensor qkv, int64_t nq, int64_t nkv, int64_t hd, torch::Tensor q_norm, torch::Tensor k_norm,
+               torch::Tensor positions, torch::Tensor row_slot, torch::Tensor block_table, torch::Tensor q_out,
+               torch::Tensor k_pages, torch::Tensor v_pages, int64_t rot, double theta, double eps) {
+    need(qkv.scalar_type() == torch::kBFloat16 && qkv.stride(1) == 1 && k_pages.scalar_type() == torch::kBFloat16 &&
+         positions.scalar_type() == torch::kInt32 && block_table.scalar_type() == torch::kInt32, "attn_prep arguments");
+    c10::cuda::CUDAGuard guard(qkv.device());
+    check(vade::attn_prep(qkv.data_ptr(), static_cast<int>(qkv.stride(0)), static_cast<int>(qkv.size(0)), static_cast<int>(nq),
+                          static_cast<int>(nkv), static_cast<int>(hd), q_norm.data_ptr<float>(), k_norm.data_ptr<float>(),
+                          positions.data_ptr<int>(), row_slot.data_ptr<int>(), block_table.data_ptr<int>(),
+                          static_cast<int>(block_table.size(1)), q_out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                          static_cast<int>(rot), theta, static_cast<float>(eps), stream_of(qkv)));
+}
+
+void attn_rows(torch::Tensor q, torch::Tensor qkv, torch::Tensor k_pages, torch::Tensor v_pages, torch::Tensor positions,
+               torch::Tensor row_slot, torch::Tensor block_table, int64_t nq, int64_t nkv, int64_t hd, bool split,
+               c10::optional<torch::Tensor> partial, int64_t n_split, torch::Tensor out) {
+    need(q.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16, "attn_rows arguments");
+    need(!split || (partial.has_value() && partial->numel() >= q.size(0) * nq * n_split * (hd + 2)), "attention scratch too small");
+    c10::cuda::CUDAGuard guard(q.device());
+    check(vade::attn_rows(q.data_ptr(), qkv.data_ptr(), static_cast<int>(qkv.stride(0)), k_pages.data_ptr(), v_pages.data_ptr(),
+                          positions.data_ptr<int>(), row_slot.data_ptr<int>(), block_table.data_ptr<int>(),
+                          static_cast<int>(block_table.size(1)), static_cast<int>(q.size(0)), static_cast<int>(nq), static_cast<int>(nkv),
+                          static_cast<int>(hd), split, ptr<float>(partial), static_cast<int>(n_split), out.data_ptr(), stream_of(q)));
+}
+
+void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id) {
+    need(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 && best_id.scalar_type() == torch::kInt64, "argmax arguments");
+    c10::cuda::CUDAGuard guard(logits.device());
+    vade::argmax_rows(logits.data_ptr<float>(), logits.stride(0), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                      static_cast<int>(id0), best_val.data_ptr<float>(), reinterpret_cast<long long*>(best_id.data_ptr<int64_t>()),
+                      stream_of(logits));
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("gemm", &gemm);
+    m.def("embed", &embed);
+    m.def("rmsnorm", &rmsnorm);
+    m.def("fold_add_norm", &fold_add_norm);
+    m.def("combine_add_norm", &combine_add_norm);
+    m.def("gather_rows", &gather_rows);
+    m.def("moe_route", &moe_route);
+    m.def("gdn_scan", &gdn_scan);
+    m.def("attn_prep", &attn_prep);
+    m.def("attn_rows", &attn_rows);
+    m.def("argmax_rows", &argmax_rows);
+    m.def("attn_split_keys", &vade::attn_split_keys);
+}

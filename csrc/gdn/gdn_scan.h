@@ -1,0 +1,13 @@
+// Host interface of the Gated DeltaNet token mixer (see gdn_scan.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace vade {
+
+// proj: bf16 [rows][ld] = [q | k | v | z | b | a] of the local heads; out: bf16 [rows][vh * vd].
+// hist fp32 [slots][3][conv channels]; state fp32 [slots][vh][kd][vd]; both updated in place.
+const char* gdn_scan(const void* proj, int ld, const float* conv_w, float* hist, float* state, const float* a_log,
+                     const float* dt_bias, const float* norm_w, const int* seq_slot, const int* seq_start, int n_seq,
+                     void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu, cudaStream_t s);
+
+}  // namespace vade

@@ -1,0 +1,338 @@
+// Swap-AB projection GEMM on 5th-generation tensor cores (tcgen05 + TMEM), sm_100a only.
+//
+//   D[m, n] = sum_k W[m, k] * X[n, k]        W = weight rows (the M = 128 operand), X = token rows
+//
+// Weights are either NVFP4 (packed e2m1 nibbles + one e4m3 scale per 16 columns, stored as
+// 4608-byte tile blocks, see pack_tiles) or plain bf16.  Token rows are the N operand (16..256
+// per CTA), so the per-output accumulation never depends on how many rows share a pass.
+//
+// One CTA computes one 128 x BN output tile over one K range:
+//   warp 0      producer: one bulk copy (NVFP4 block) or tiled TMA load (bf16 weights) plus one
+//               tiled TMA load of the X tile per 64-column K block, STAGES deep
+//   warps 2..5  NVFP4 only: expand nibbles to bf16 (e2m1 * e4m3, exact) into the 128-byte
+//               swizzled A tile; afterwards the epilogue: tcgen05.ld, row scale, store
+//   warp 1      one thread issues tcgen05.mma (4 x K16 per block) and commits to mbarriers
+// grid = (row tiles, token tiles or grouped tasks, K ranges).  With more than one range each
+// CTA writes an fp32 partial [range][token][row]; the caller folds ranges in a fixed tree.
+//
+// Every mbarrier wait is bounded; on a timeout the kernel writes a status word and exits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include "../common/ptx.cuh"
+#include "umma_gemm.h"
+
+namespace vade {
+
+constexpr int kTileM = 128;
+constexpr int kTileK = 64;
+constexpr int kWBlockBytes = 4608;
+constexpr int kAStageBytes = kTileM * kTileK * 2;
+constexpr int kThreads = 192;
+
+struct GemmDev {
+    const uint8_t* w_tiles;
+    const float* row_scale;
+    void* out;
+    const int4* tasks;
+    const int* num_tasks;
+    uint32_t* status;
+    long long w_expert_stride;      // bytes between stacked matrices (NVFP4 tiles)
+    long long out_range_stride;     // elements between range partials
+    int rs_expert_stride;
+    int n_out;
+    int kb_total;                   // K / 64 of one matrix
+    int kb_per_range;
+    int tokens;
+    int ldo;
+};
+
+template <int BN, int STAGES, bool NVFP4, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmDev a) {
+    constexpr int kBStageBytes = BN * kTileK * 2;
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kTxBytes = (NVFP4 ? kWBlockBytes : kAStageBytes) + kBStageBytes;
+
+    int expert = 0, row0, nrows;
+    if (a.tasks != nullptr) {
+        if (static_cast<int>(blockIdx.y) >= *a.num_tasks) return;
+        const int4 t = a.tasks[blockIdx.y];
+        expert = t.x; row0 = t.y; nrows = t.z;
+    } else {
+        row0 = blockIdx.y * BN;
+        nrows = min(BN, a.tokens - row0);
+    }
+    const int mtile = blockIdx.x;
+    const int range = blockIdx.z;
+    const int kb0 = range * a.kb_per_range;
+    const int nkb = a.kb_per_range;
+
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = sA + STAGES * kAStageBytes;
+    uint8_t* sW = sB + STAGES * kBStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sW + (NVFP4 ? STAGES * kWBlockBytes : 0));
+    uint64_t* full = bars;
+    uint64_t* aready = bars + STAGES;
+    uint64_t* empty = bars + 2 * STAGES;
+    uint64_t* tmem_full = bars + 3 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&aready[s], 128);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tmem_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_x);
+        if (!NVFP4) tma_prefetch_desc(&tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_d = *tmem_slot;
+
+    auto fail = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (a.status != nullptr) atomicMax(a.status, code);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint8_t* wbase = a.w_tiles + static_cast<long long>(expert) * a.w_expert_stride
+                                 + (static_cast<long long>(mtile) * a.kb_total + kb0) * kWBlockBytes;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1)) { fail(1); break; }
+                mbar_expect_tx(&full[s], kTxBytes);
+                if (NVFP4) bulk_load(sW + s * kWBlockBytes, wbase + static_cast<long long>(i) * kWBlockBytes, kWBlockBytes, &full[s]);
+                else tma_load_2d(sA + s * kAStageBytes, &tmap_w, (kb0 + i) * kTileK, mtile * kTileM, &full[s]);
+                tma_load_2d(sB + s * kBStageBytes, &tmap_x, (kb0 + i) * kTileK, row0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(kTileM, BN);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (NVFP4 && !mbar_wait(&aready[s], ph)) { fail(2); break; }
+                if (!mbar_wait(&full[s], ph)) { fail(3); break; }
+                tc_fence_after_sync();
+                const uint64_t adesc = umma_desc_sw128(smem_u32(sA + s * kAStageBytes));
+                const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + s * kBStageBytes));
+#pragma unroll
+                for (int kk = 0; kk < kTileK / 16; ++kk)
+                    umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i | kk) != 0 ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const int t = threadIdx.x - 64;          // 0..127: weight row inside the tile (dequant role)
+        if (NVFP4) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(&full[s], ph)) { fail(4); break; }
+                const uint8_t* raw = sW + s * kWBlockBytes;
+                const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 4096 + t * 4);
+                // four e4m3 block scales -> bf16x2 multipliers (scale * 2^112), see below
+                uint32_t mult[4];
+                {
+                    uint32_t h01, h23;
+                    const uint16_t lo16 = static_cast<uint16_t>(sc4 & 0xFFFF), hi16 = static_cast<uint16_t>(sc4 >> 16);
+                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(lo16));
+                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(hi16));
+                    const __half2 a01 = *reinterpret_cast<const __half2*>(&h01);
+                    const __half2 a23 = *reinterpret_cast<const __half2*>(&h23);
+                    const float f[4] = {__low2float(a01), __high2float(a01), __low2float(a23), __high2float(a23)};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t b = __float_as_uint(f[j] * 0x1p112f) >> 16;   // exact: <= 4 significant bits
+                        mult[j] = b | (b << 16);
+                    }
+                }
+                uint8_t* arow = sA + s * kAStageBytes + t * 128;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(raw + half * 2048 + t * 16);
+                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        // 8 nibbles of one word = columns 32*half + 8*w .. +7; block scale index 2*half + w/2
+                        const uint32_t m2 = mult[2 * half + (w >> 1)];
+                        uint32_t o[4];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            uint32_t h2;
+                            const uint16_t byte = static_cast<uint16_t>((words[w] >> (8 * b)) & 0xFF);
+                            asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(byte));
+                            // f16 bits >> 3 read as bf16 equal value * 2^-112 (normal for |v| >= 0.5, zero stays zero)
+                            const uint32_t p = ((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u);
+                            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[b]) : "r"(p), "r"(m2));
+                        }
+                        const int chunk = half * 4 + w;
+                        *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&aready[s]);
+            }
+        }
+        // ---------------- epilogue
+        const int q = warp & 3;                   // TMEM lane quadrant this warp may read
+        const int m = mtile * kTileM + q * 32 + lane;
+        const bool ok = mbar_wait(tmem_full, 0) && (*abort_flag == 0);
+        if (!ok) fail(5);
+        tc_fence_after_sync();
+        if (ok) {
+            const float rs = (m < a.n_out) ? a.row_scale[static_cast<long long>(expert) * a.rs_expert_stride + m] : 0.f;
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= nrows) break;
+                float v[16];
+                tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float y = v[j] * rs;
+                    const long long tok = row0 + c + j;
+                    if (EPI == 2) {
+                        const float yb = bf16_round(y);
+                        const float other = __shfl_xor_sync(0xffffffffu, yb, 1);
+                        if ((lane & 1) == 0 && c + j < nrows && m < a.n_out)
+                            reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + (m >> 1)] = __float2bfloat16_rn(siluf_(yb) * other);
+                    } else if (c + j < nrows && m < a.n_out) {
+                        if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
+                        else reinterpret_cast<float*>(a.out)[range * a.out_range_stride + tok * a.ldo + m] = y;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D bf16 tensor [rows][inner] with a {64, box_rows} box and the 128-byte swizzle.
+static bool make_tmap(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool NVFP4, int EPI>
+static const char* launch_one(const GemmArgs& h, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, dim3 grid, cudaStream_t stream) {
+    constexpr int smem = STAGES * (kAStageBytes + BN * kTileK * 2 + (NVFP4 ? kWBlockBytes : 0)) + (3 * STAGES + 2) * 8 + 1024;
+    static bool configured = false;
+    auto kern = umma_gemm_kernel<BN, STAGES, NVFP4, EPI>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return "cannot raise shared memory limit";
+        configured = true;
+    }
+    kern<<<grid, kThreads, smem, stream>>>(tx, tw, d);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "kernel launch failed";
+}
+
+template <bool NVFP4, int EPI>
+static const char* launch_bn(const GemmArgs& h, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, dim3 grid, cudaStream_t s) {
+    switch (h.bn) {
+        case 16:  return launch_one<16, 8, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 32:  return launch_one<32, 8, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 64:  return launch_one<64, 6, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 128: return launch_one<128, 5, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 256: return launch_one<256, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        default:  return "token tile must be 16, 32, 64, 128 or 256";
+    }
+}
+
+const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
+    if (h.k % kTileK != 0 || h.k <= 0) return "K must be a positive multiple of 64";
+    if (h.ranges < 1 || (h.k / kTileK) % h.ranges != 0) return "K blocks must divide evenly into ranges";
+    if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
+    if ((reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
+    if (h.x_rows <= 0 || h.n_out <= 0) return "empty problem";
+    CUtensorMap tx, tw;
+    if (!make_tmap(&tx, h.x, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.x_rows), static_cast<uint64_t>(h.ldx) * 2, h.bn))
+        return "cuTensorMapEncodeTiled failed for the activation tensor";
+    const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
+    if (h.nvfp4) {
+        if ((reinterpret_cast<uintptr_t>(h.w) & 15) != 0) return "weight tiles must be 16-byte aligned";
+        tw = tx;
+    } else {
+        if (!make_tmap(&tw, h.w, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.n_out), static_cast<uint64_t>(h.k) * 2, kTileM))
+            return "cuTensorMapEncodeTiled failed for the weight tensor";
+    }
+    GemmDev d;
+    d.w_tiles = static_cast<const uint8_t*>(h.w);
+    d.row_scale = h.row_scale;
+    d.out = h.out;
+    d.tasks = reinterpret_cast<const int4*>(h.tasks);
+    d.num_tasks = h.num_tasks;
+    d.status = h.status;
+    d.w_expert_stride = static_cast<long long>(m_tiles) * (h.k / kTileK) * kWBlockBytes;
+    d.out_range_stride = h.out_range_stride;
+    d.rs_expert_stride = h.n_out;
+    d.n_out = h.n_out;
+    d.kb_total = h.k / kTileK;
+    d.kb_per_range = d.kb_total / h.ranges;
+    d.tokens = h.tokens;
+    d.ldo = h.ldo;
+    const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + h.bn - 1) / h.bn;
+    if (y <= 0) return "empty grid";
+    dim3 grid(m_tiles, y, h.ranges);
+    if (h.nvfp4) {
+        switch (h.epilogue) {
+            case 0: return launch_bn<true, 0>(h, tx, tw, d, grid, stream);
+            case 1: return launch_bn<true, 1>(h, tx, tw, d, grid, stream);
+            case 2: return launch_bn<true, 2>(h, tx, tw, d, grid, stream);
+        }
+    } else {
+        switch (h.epilogue) {
+            case 0: return launch_bn<false, 0>(h, tx, tw, d, grid, stream);
+            case 1: return launch_bn<false, 1>(h, tx, tw, d, grid, stream);
+        }
+    }
+    return "unsupported epilogue";
+}
+
+}  // namespace vade

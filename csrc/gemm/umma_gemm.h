@@ -1,0 +1,38 @@
+// Host interface of the tcgen05 projection GEMM (see umma_gemm.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace vade {
+
+struct GemmArgs {
+    // activations: bf16 rows [x_rows][ldx], K = logical columns used (multiple of 64)
+    const void* x = nullptr;
+    int x_rows = 0;
+    int ldx = 0;
+    int k = 0;
+    // weights: NVFP4 tile blocks (nvfp4 = true) or row-major bf16 [n_out][k]
+    const void* w = nullptr;
+    bool nvfp4 = true;
+    const float* row_scale = nullptr;       // [experts?][n_out]
+    int n_out = 0;
+    // output: epilogue 0 = bf16 [tokens][ldo]; 1 = fp32 [ranges][tokens][ldo]; 2 = SwiGLU of
+    // interleaved gate/up rows, bf16 [tokens][ldo] with n_out / 2 columns
+    void* out = nullptr;
+    int ldo = 0;
+    long long out_range_stride = 0;
+    int epilogue = 0;
+    int tokens = 0;                         // dense: number of token rows
+    int bn = 16;                            // token tile (16, 32, 64, 128, 256)
+    int ranges = 1;                         // K ranges (grid.z); > 1 requires epilogue 1
+    // grouped (MoE): tasks[i] = {expert, first row, rows (<= bn), 0}; CTAs with blockIdx.y >= *num_tasks exit
+    const int* tasks = nullptr;
+    const int* num_tasks = nullptr;
+    int max_tasks = 0;
+    uint32_t* status = nullptr;             // device word, raised (atomicMax) on a wait timeout
+};
+
+// Returns nullptr on success or a static error text.
+const char* umma_gemm(const GemmArgs& args, cudaStream_t stream);
+
+}  // namespace vade

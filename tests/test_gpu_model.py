@@ -1,0 +1,65 @@
+"""Whole-model checks on a B200: kernels vs the PyTorch statement, determinism, batch invariance."""
+import pytest
+import torch
+
+from vade_b200.config import small_gpu_config
+from vade_b200.ops.api import Batch
+from vade_b200.runtime.build import build_engine
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompt(n, vocab=8192, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab - 8, (n,), generator=g).tolist()
+
+
+def test_forward_matches_reference_ops():
+    cfg = small_gpu_config()
+    a = build_engine(cfg, device="cuda", seed=0, max_seq=512)
+    b = build_engine(cfg, device="cuda", seed=0, max_seq=512, reference_ops=True)
+    ids = _prompt(96)
+    outs = []
+    for eng in (a, b):
+        s = eng.cache.new_slot()
+        eng.cache.ensure(s, len(ids))
+        x, h = eng.model.forward(Batch.make([(s, 0, ids)], "cuda", "prefill"), eng.cache)
+        outs.append((x, eng.model.logits(h[-1:])))
+    a.model.ops.check_status()
+    rel = (outs[0][0] - outs[1][0]).norm() / outs[1][0].norm()
+    assert rel < 6e-2, f"residual stream differs: rel {rel}"
+    la, lb = outs[0][1], outs[1][1]
+    assert (la - lb).abs().max() < 0.05 * lb.abs().max()
+
+
+def test_generation_is_deterministic_and_batch_invariant():
+    cfg = small_gpu_config()
+    eng = build_engine(cfg, device="cuda", seed=0, max_seq=512, slots=4)
+    p1, p2 = _prompt(70, seed=1), _prompt(33, seed=2)
+    a = eng.generate(p1, 24).generated
+    b = eng.generate(p1, 24).generated
+    assert a == b
+    # the same chat decoded beside another chat in one batch emits the same ids
+    from vade_b200.runtime.engine import Sequence
+    s1, s2 = Sequence(eng.cache.new_slot()), Sequence(eng.cache.new_slot())
+    _, h1 = eng.prefill(s1, p1)
+    _, h2 = eng.prefill(s2, p2)
+    t1, t2 = int(eng.model.greedy(h1)[0]), int(eng.model.greedy(h2)[0])
+    got = [t1]
+    for _ in range(23):
+        x, h = eng.step([s1, s2], [[t1], [t2]])
+        s1.tokens.append(t1), s2.tokens.append(t2)
+        nxt = eng.model.greedy(h)
+        t1, t2 = int(nxt[0]), int(nxt[1])
+        got.append(t1)
+    eng.model.ops.check_status()
+    assert got == a
+
+
+def test_speculative_decoding_is_exact():
+    cfg = small_gpu_config()
+    eng = build_engine(cfg, device="cuda", seed=0, max_seq=512)
+    p = _prompt(80, seed=3)
+    plain = eng.generate(p, 32)
+    spec = eng.generate(p, 32, draft_depth=3)
+    assert plain.generated == spec.generated and spec.drafted > 0

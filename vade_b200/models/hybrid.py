@@ -41,10 +41,10 @@ class HybridModel:
         parts = comm.gather_partials(parts)
         x, h2 = ops.fold_add_norm(parts, x, lw.post_norm)
         logits = ops.linear(h2, lw.moe.router, out_fp32=True, phase=ph)
-        ids, wts, sg = ops.route(logits)
-        pair_out, owned = ops.moe_experts(lw.moe, h2, ids, phase=ph)
+        routing = ops.route(logits, lw.moe)
+        pair_out, owned = ops.moe_experts(lw.moe, h2, routing, phase=ph)
         pair_out = comm.gather_pairs(pair_out, owned)
-        return ops.combine_add_norm(pair_out, ids, wts, sg, x, next_norm)
+        return ops.combine_add_norm(pair_out, routing, x, next_norm)
 
     # ------------------------------------------------------------------ trunk
     def forward(self, batch: Batch, cache, hidden_in: torch.Tensor | None = None):

@@ -1,0 +1,80 @@
+"""Builds and loads the sm_100a extension (csrc/) in-tree.
+
+The shared object is kept under ``vade_b200/_ext`` so it travels with the source tree; it is
+compiled for ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a``).  ``load()`` imports a
+prebuilt object when one is present and its source stamp matches, otherwise it compiles with ninja
+through torch.utils.cpp_extension.  On a machine with a GPU the ops fail loudly when the extension
+cannot be loaded; there is no silent fallback.
+"""
+from __future__ import annotations
+
+import hashlib
+import importlib.util
+import os
+import sys
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_CSRC = os.path.join(_ROOT, "csrc")
+_OUT = os.path.join(_ROOT, "vade_b200", "_ext")
+_NAME = "_vade_cuda"
+_mod = None
+
+SOURCES = ["bindings.cpp", "gemm/umma_gemm.cu", "norm/rows.cu", "moe/route.cu", "gdn/gdn_scan.cu",
+           "attn/attn.cu", "head/head.cu"]
+
+CUDA_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+
+
+def _stamp() -> str:
+    h = hashlib.sha256()
+    for root, _, files in sorted(os.walk(_CSRC)):
+        for f in sorted(files):
+            if f.endswith((".cu", ".cuh", ".h", ".cpp")):
+                with open(os.path.join(root, f), "rb") as fh:
+                    h.update(f.encode())
+                    h.update(fh.read())
+    h.update(" ".join(CUDA_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _import_so(path: str):
+    spec = importlib.util.spec_from_file_location(_NAME, path)
+    mod = importlib.util.module_from_spec(spec)
+    import torch  # noqa: F401  (libtorch symbols must be loaded first)
+    spec.loader.exec_module(mod)
+    sys.modules[_NAME] = mod
+    return mod
+
+
+def build(verbose: bool = False):
+    """Compile (if stale) and import the extension.  Works without a GPU (nvcc cross-compiles)."""
+    global _mod
+    from torch.utils import cpp_extension
+    os.makedirs(_OUT, exist_ok=True)
+    os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 1)))
+    mod = cpp_extension.load(
+        name=_NAME, sources=[os.path.join(_CSRC, s) for s in SOURCES],
+        extra_cflags=["-O2", "-std=c++17"], extra_cuda_cflags=CUDA_FLAGS,
+        extra_include_paths=[_CSRC], build_directory=_OUT, with_cuda=True, verbose=verbose)
+    with open(os.path.join(_OUT, "stamp.txt"), "w") as f:
+        f.write(_stamp())
+    _mod = mod
+    return mod
+
+
+def load():
+    """The extension module; builds it when no current prebuilt object exists."""
+    global _mod
+    if _mod is not None:
+        return _mod
+    so = os.path.join(_OUT, _NAME + ".so")
+    stamp = os.path.join(_OUT, "stamp.txt")
+    if os.path.exists(so) and os.path.exists(stamp) and open(stamp).read().strip() == _stamp():
+        _mod = _import_so(so)
+        return _mod
+    return build()
+
+
+def so_path() -> str:
+    return os.path.join(_OUT, _NAME + ".so")

@@ -9,6 +9,7 @@ keeps hidden state, so a step is a pure function of (weights, cache, batch).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from types import SimpleNamespace
 
 import torch
 
@@ -117,15 +118,17 @@ class RefOps:
         return R._round((o * torch.sigmoid(gate)).reshape(T, nq * hd), self.act)
 
     # ---- MoE
-    def route(self, logits):
+    def route(self, logits, mw):
+        """Routing of every row: ids [T, k] (descending probability), weights, shared-expert gate."""
         cfg = self.cfg
         E = cfg.num_experts
         ids, w = R.route_topk(logits[:, :E], cfg.num_experts_per_tok, cfg.norm_topk_prob)
-        return ids, w, torch.sigmoid(logits[:, E].float())
+        return SimpleNamespace(ids=ids, wts=w, sg=torch.sigmoid(logits[:, E].float()))
 
-    def moe_experts(self, mw, h, ids, phase: str = "prefill"):
+    def moe_experts(self, mw, h, routing, phase: str = "prefill"):
         """Outputs of the experts this rank holds: pair_out [T, k + ns, H] (rounded to ``act``),
         owned bool [T, k + ns]."""
+        ids = routing.ids
         T, k = ids.shape
         ns = mw.n_shared
         H = mw.down.n
@@ -149,7 +152,9 @@ class RefOps:
             owned[:, k + s] = True
         return pair_out, owned
 
-    def combine_add_norm(self, pair_out, ids, w, sg, x, norm_w):
+    def combine_add_norm(self, pair_out, routing, x, norm_w):
+        ids, w, sg = routing.ids, routing.wts, routing.sg
+        pair_out = pair_out.float()
         T, k = ids.shape
         ns = pair_out.shape[1] - k
         E = self.cfg.num_experts

@@ -1,0 +1,188 @@
+"""``CudaOps``: the model's op set on the hand-written sm_100a kernels (csrc/).
+
+Same methods as ``RefOps`` (ops/api.py).  Matrix products run on the tcgen05 GEMM
+(csrc/gemm/umma_gemm.cu) with NVFP4 or bf16 weights; token mixers, routing, folds and the head
+run on the row kernels.  Nothing here falls back to a library kernel: if the extension cannot
+be loaded on a GPU machine the constructor raises.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+
+from ..config import ModelConfig
+from . import _ext
+from .api import Batch
+
+
+def _bn_for(rows: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if rows <= bn:
+            return bn
+    return 256
+
+
+class CudaOps:
+    name = "cuda"
+    act = torch.bfloat16
+
+    def __init__(self, cfg: ModelConfig, device, tp: int = 1):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.tp = tp
+        self.ext = _ext.load()
+        if cfg.head_dim != 256 or cfg.linear_key_head_dim != 128 or cfg.linear_value_head_dim != 128:
+            raise ValueError("the sm_100a kernels handle attention head_dim 256 and GDN head dims 128")
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+        self._moe_ws = {}
+
+    # ---- helpers
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"a device wait timed out (status {code}); the pass is invalid")
+
+    def _dev(self, batch: Batch) -> dict:
+        if not batch.dev:
+            mk = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+            batch.dev = {"positions": batch.positions.to(torch.int32), "row_slot": batch.row_slot.to(torch.int32),
+                         "seq_slot": mk(batch.seq_slots), "seq_start": mk(batch.seq_start),
+                         "max_len": max(p + (e - s) for p, s, e in zip(batch.seq_pos0, batch.seq_start, batch.seq_start[1:]))}
+        return batch.dev
+
+    def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0):
+        nv = q.kind == "nvfp4"
+        self.launches += 1
+        self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
+                      range_stride, tasks, meta, max_tasks, self.status)
+
+    # ---- basic
+    def embed(self, w, tokens):
+        x = torch.empty(tokens.shape[0], w.shape[1], dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.ext.embed(w, tokens.to(torch.int64), x)
+        return x
+
+    def rmsnorm(self, x, w, out=None, off: int = 0):
+        x = x.contiguous()
+        if out is None:
+            out = torch.empty(x.shape[0], x.shape[1], dtype=torch.bfloat16, device=self.device)
+        self.launches += 1
+        self.ext.rmsnorm(x, w, out, self.cfg.rms_norm_eps, out.stride(0), off)
+        return out
+
+    def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
+        T = h.shape[0]
+        out = torch.empty(T, q.n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=self.device)
+        self._gemm(h, q, out, 1 if out_fp32 else 0, _bn_for(T), 1, T, q.n, 0)
+        return out
+
+    def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
+        T = h.shape[0]
+        out = torch.empty(n_ranges, T, q.n, dtype=torch.float32, device=self.device)
+        self._gemm(h, q, out, 1, _bn_for(T), n_ranges, T, q.n, T * q.n)
+        return out
+
+    def fold_add_norm(self, parts, x, w):
+        h = torch.empty(x.shape[0], x.shape[1], dtype=torch.bfloat16, device=self.device) if w is not None else None
+        self.launches += 1
+        self.ext.fold_add_norm(parts, parts.shape[0], parts.stride(0), x, w, h, self.cfg.rms_norm_eps)
+        return x, h
+
+    # ---- token mixers
+    def gdn_mix(self, lw, proj, batch: Batch, cache, layer):
+        cfg = self.cfg
+        d = self._dev(batch)
+        vh = lw.a_log.shape[0]
+        kh = vh * cfg.linear_num_key_heads // cfg.linear_num_value_heads
+        out = torch.empty(proj.shape[0], vh * cfg.linear_value_head_dim, dtype=torch.bfloat16, device=self.device)
+        self.launches += 1
+        self.ext.gdn_scan(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
+                          d["seq_slot"], d["seq_start"], len(batch.seq_slots), out, kh, vh, cfg.linear_key_head_dim,
+                          cfg.linear_value_head_dim, cfg.rms_norm_eps, False)
+        return out
+
+    def attn_mix(self, lw, qkv, batch: Batch, cache, layer):
+        cfg = self.cfg
+        d = self._dev(batch)
+        hd = cfg.head_dim
+        kp, vp = cache.k_pages[layer], cache.v_pages[layer]
+        nkv = kp.shape[2]
+        nq = (qkv.shape[1] - 2 * nkv * hd) // (2 * hd)
+        T = qkv.shape[0]
+        q = torch.empty(T, nq, hd, dtype=torch.bfloat16, device=self.device)
+        self.ext.attn_prep(qkv, nq, nkv, hd, lw.q_norm, lw.k_norm, d["positions"], d["row_slot"], cache.block_table, q, kp, vp,
+                           cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_norm_eps)
+        out = torch.empty(T, nq * hd, dtype=torch.bfloat16, device=self.device)
+        split = batch.phase == "decode"
+        partial, n_split = None, 1
+        if split:
+            n_split = -(-d["max_len"] // self.ext.attn_split_keys())
+            partial = torch.empty(T * nq * n_split * (hd + 2), dtype=torch.float32, device=self.device)
+        self.launches += 3 if split else 2
+        self.ext.attn_rows(q, qkv, kp, vp, d["positions"], d["row_slot"], cache.block_table, nq, nkv, hd, split, partial, n_split, out)
+        return out
+
+    # ---- MoE
+    def route(self, logits, mw):
+        cfg = self.cfg
+        T = logits.shape[0]
+        k, ns, E = cfg.num_experts_per_tok, mw.n_shared, cfg.num_experts
+        bn = 16 if T <= 16 else (32 if T <= 64 else 64)
+        slots = k + ns
+        max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
+        max_rows = T * slots
+        dev, i32 = self.device, torch.int32
+        counts = self._moe_ws.get((mw.n_local, "counts"))
+        if counts is None:
+            counts = self._moe_ws[(mw.n_local, "counts")] = torch.zeros(max(1, mw.n_local), dtype=i32, device=dev)
+        r = SimpleNamespace(
+            ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
+            sg=torch.empty(T, dtype=torch.float32, device=dev), pos=torch.empty(T, k, dtype=i32, device=dev),
+            offsets=torch.empty(mw.n_local + ns, dtype=i32, device=dev), tasks=torch.empty(max_tasks, 4, dtype=i32, device=dev),
+            meta=torch.zeros(4, dtype=i32, device=dev), row_token=torch.empty(max_rows, dtype=i32, device=dev),
+            slot_row=torch.empty(T, slots, dtype=i32, device=dev), bn=bn, max_tasks=max_tasks, max_rows=max_rows, T=T, k=k, ns=ns)
+        self.launches += 3
+        self.ext.moe_route(logits, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, bn, r.ids, r.wts, r.sg, counts, r.pos,
+                           r.offsets, r.tasks, r.meta, max_tasks, r.row_token, r.slot_row)
+        return r
+
+    def moe_experts(self, mw, h, r, phase: str = "prefill"):
+        H, I2 = mw.down.n, mw.gate_up.n
+        xs = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
+        self.launches += 1
+        self.ext.gather_rows(h, r.row_token, r.meta, xs, r.max_rows)
+        mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
+        self._gemm(xs, mw.gate_up, mid, 2, r.bn, 1, r.max_rows, I2 // 2, 0, r.tasks, r.meta, r.max_tasks)
+        y = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
+        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks, r.meta, r.max_tasks)
+        if self.tp == 1:
+            return y, None
+        # dense [T, slots, H] layout for the exchange between expert-parallel ranks
+        owned = r.slot_row >= 0
+        dense = torch.zeros(r.T, r.k + r.ns, H, dtype=torch.bfloat16, device=self.device)
+        dense[owned] = y[r.slot_row[owned].long()]
+        r.slot_row = torch.arange(r.T * (r.k + r.ns), dtype=torch.int32, device=self.device).view(r.T, r.k + r.ns)
+        return dense, owned
+
+    def combine_add_norm(self, pair_out, r, x, norm_w):
+        H = x.shape[1]
+        h = torch.empty(x.shape[0], H, dtype=torch.bfloat16, device=self.device) if norm_w is not None else None
+        self.launches += 1
+        self.ext.combine_add_norm(pair_out.view(-1, H), r.slot_row, r.ids, r.wts, r.sg, r.k, r.ns, x, norm_w, h, self.cfg.rms_norm_eps)
+        return x, h
+
+    # ---- head
+    def head_logits(self, h, lm_head):
+        return self.linear(h, lm_head, out_fp32=True)
+
+    def head_argmax(self, h, lm_head, vocab0: int):
+        logits = self.head_logits(h, lm_head)
+        val = torch.empty(h.shape[0], dtype=torch.float32, device=self.device)
+        idx = torch.empty(h.shape[0], dtype=torch.int64, device=self.device)
+        self.launches += 1
+        self.ext.argmax_rows(logits, vocab0, val, idx)
+        return val, idx

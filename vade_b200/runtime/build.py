@@ -13,11 +13,11 @@ from .cache import Cache
 from .engine import Engine
 
 
-def make_ops(cfg: ModelConfig, device, act: torch.dtype, reference: bool = False):
+def make_ops(cfg: ModelConfig, device, act: torch.dtype, reference: bool = False, tp: int = 1):
     dev = torch.device(device)
     if dev.type == "cuda" and not reference:
         from ..ops.cuda import CudaOps
-        return CudaOps(cfg, dev)
+        return CudaOps(cfg, dev, tp)
     return RefOps(cfg, act)
 
 
@@ -38,7 +38,7 @@ def build_engine(cfg: ModelConfig, source=None, *, device="cpu", act: torch.dtyp
             from ..checkpoint.synth import synth_state_dict, DictSource
             source = DictSource(synth_state_dict(cfg, seed))
         weights = W.load_weights(cfg, source, plan, act, dev, with_mtp, keep_rowmajor)
-    ops = make_ops(cfg, dev, act, reference_ops)
+    ops = make_ops(cfg, dev, act, reference_ops, tp)
     comm = comm or LocalComm()
     model = HybridModel(cfg, weights, plan, ops, comm)
     if pages is None:

@@ -1,0 +1,84 @@
+"""CUDA-graph decode steps: one captured graph per padded batch width.
+
+A decode step is launch-bound (hundreds of small kernels), so the whole step (all layers, the
+head, the greedy choice and the position bump) is captured once per width and replayed.  The graph
+reads its rows from static device buffers (token, position, slot per row) and writes the chosen
+tokens back into the token buffer, so consecutive greedy steps need no host round trip; a server
+that samples on the host overwrites the token buffer between replays instead.
+
+Everything shape-dependent is fixed at capture: one row per sequence, the attention split count
+for the longest context the graph may see, the MoE task-table bounds.  Slot tables and KV pages
+outlive the graphs.  Parity: the reference's per-width decode graph bank
+(engine/crates/engine/src/flash/next_pool.rs:1-66,345-650).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.api import Batch
+
+
+class DecodeGraph:
+    def __init__(self, engine, slots: list, max_len: int):
+        """``slots``: cache slot of each row (one row per sequence); ``max_len``: longest context
+        (position + 1) any replay of this graph will see; its KV pages must already be mapped."""
+        self.engine = engine
+        self.width = len(slots)
+        dev = engine.device
+        self.tokens = torch.zeros(self.width, dtype=torch.int64, device=dev)
+        self.positions = torch.zeros(self.width, dtype=torch.int32, device=dev)
+        self.row_slot = torch.tensor(slots, dtype=torch.int32, device=dev)
+        self.seq_start = torch.arange(self.width + 1, dtype=torch.int32, device=dev)
+        self.max_len = max_len
+        self.slots = list(slots)
+        self.graph = None
+        self.x = self.h = None
+        self.kernels = 0
+
+    def _batch(self) -> Batch:
+        b = Batch(self.tokens, self.positions, self.row_slot, self.slots, list(range(self.width + 1)),
+                  [0] * self.width, "decode")
+        b.dev = {"positions": self.positions, "row_slot": self.row_slot, "seq_slot": self.row_slot,
+                 "seq_start": self.seq_start, "max_len": self.max_len}
+        return b
+
+    def _step(self):
+        eng = self.engine
+        x, h = eng.model.forward(self._batch(), eng.cache)
+        nxt = eng.model.greedy(h)
+        self.tokens.copy_(nxt)
+        self.positions.add_(1)
+        return x, h
+
+    def capture(self, tokens: list, positions: list, warmup: int = 2) -> None:
+        """Warm up eagerly on a side stream (same inputs, state restored afterwards), then capture."""
+        eng = self.engine
+        snaps = [eng.cache.snapshot(s) for s in self.slots]
+        tok = torch.tensor(tokens, dtype=torch.int64, device=eng.device)
+        pos = torch.tensor(positions, dtype=torch.int32, device=eng.device)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.tokens.copy_(tok), self.positions.copy_(pos)
+                self._step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.tokens.copy_(tok), self.positions.copy_(pos)
+        before = eng.model.ops.launches
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.x, self.h = self._step()
+        self.kernels = eng.model.ops.launches - before
+        # capture does not execute: restore inputs and recurrent state touched by the warm-up
+        for s, snap in zip(self.slots, snaps):
+            length = eng.cache.length[s]
+            for i, st in snap.gdn.items():
+                eng.cache.gdn_state[i][s].copy_(st)
+            for i, hh in snap.conv.items():
+                eng.cache.conv_hist[i][s].copy_(hh)
+            eng.cache.length[s] = length
+        self.tokens.copy_(tok), self.positions.copy_(pos)
+
+    def replay(self) -> None:
+        self.graph.replay()
