@@ -4,7 +4,7 @@
 //                dims (rotate-half), q written as bf16 rows, k/v appended to the row's cache page
 //   attn_rows    one CTA per (row, kv head[, key split]); one warp per query head of the group;
 //                lanes own 8 of the 256 dims; online softmax over the row's visible keys.
-//                Decode class: keys are cut into fixed 256-key splits (independent of the batch),
+//                Decode class: keys are cut into fixed 128-key splits (independent of the batch),
 //                partials {m, l, acc} go to scratch and attn_merge joins them in split order.
 //                Prefill class: one pass over all keys, output written directly.
 //   output       attention * sigmoid(gate), bf16, gate read from the q projection rows
@@ -19,23 +19,40 @@ namespace vade {
 
 constexpr int kHD = 256;
 constexpr int kPage = 64;
-constexpr int kSplit = 256;
+constexpr int kSplit = 128;
 
-__global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int nq, int nkv,
+// One projection value: a bf16 element, or the bf16 rounding of the ascending sum of fp32 K-range partials.
+template <bool PARTS>
+__device__ __forceinline__ float qkv_at(const void* qkv, long long row, int ld, int col, int n_parts, long long part_stride) {
+    if (!PARTS) return __bfloat162float(static_cast<const __nv_bfloat16*>(qkv)[row * ld + col]);
+    const float* p = static_cast<const float*>(qkv) + row * ld + col;
+    if (n_parts == 4) {
+        const float a0 = p[0], a1 = p[part_stride], a2 = p[2 * part_stride], a3 = p[3 * part_stride];
+        return bf16_round(((a0 + a1) + a2) + a3);
+    }
+    float a = p[0];
+    for (int i = 1; i < n_parts; ++i) a += p[i * part_stride];
+    return bf16_round(a);
+}
+
+template <bool PARTS>
+__global__ void attn_prep_kernel(const void* __restrict__ qkv, int ld, int n_parts, long long part_stride, int nq, int nkv,
                                  const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                  const int* __restrict__ positions, const int* __restrict__ row_slot,
                                  const int* __restrict__ block_table, int max_pages,
-                                 __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
-                                 __nv_bfloat16* __restrict__ v_pages, int rot, double log_theta, float eps) {
+                                 __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ gate_out,
+                                 __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int rot,
+                                 double log_theta, float eps) {
     __shared__ float xs[kHD];
     __shared__ float red[8];
     const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int pos = positions[row];
-    const __nv_bfloat16* base = qkv + static_cast<long long>(row) * ld;
     const bool is_q = head < nq;
     const int kvh = is_q ? 0 : (head - nq);
-    const __nv_bfloat16* src = is_q ? base + head * 2 * kHD : base + nq * 2 * kHD + kvh * kHD;
-    const float x = __bfloat162float(src[d]);
+    const int col = is_q ? head * 2 * kHD + d : nq * 2 * kHD + kvh * kHD + d;
+    const float x = qkv_at<PARTS>(qkv, row, ld, col, n_parts, part_stride);
+    // the other value this thread forwards: the head's output gate (query heads) or the value row (kv heads)
+    const float other = qkv_at<PARTS>(qkv, row, ld, is_q ? col + kHD : col + nkv * kHD, n_parts, part_stride);
     float ss = x * x;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -60,11 +77,12 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, 
     }
     if (is_q) {
         q_out[(static_cast<long long>(row) * nq + head) * kHD + d] = __float2bfloat16_rn(y);
+        gate_out[(static_cast<long long>(row) * nq + head) * kHD + d] = __float2bfloat16_rn(other);
     } else {
         const int page = block_table[static_cast<long long>(row_slot[row]) * max_pages + pos / kPage];
         const long long at = ((static_cast<long long>(page) * kPage + pos % kPage) * nkv + kvh) * kHD + d;
         k_pages[at] = __float2bfloat16_rn(y);
-        v_pages[at] = base[nq * 2 * kHD + nkv * kHD + kvh * kHD + d];
+        v_pages[at] = __float2bfloat16_rn(other);
     }
 }
 
@@ -74,12 +92,20 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
     for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 
+// One warp = one query head.  Keys are visited 32 at a time: lane j scores key j against the whole
+// query (query in shared memory, key row read as 16-byte pieces), the 32 scores are merged into the
+// running softmax with one butterfly, then lane d accumulates dims 8d..8d+7 of the output over
+// the 32 value rows (row reads are coalesced, probabilities come by shuffle).  The visiting order
+// (ascending key groups of 32, ascending key inside a group) is fixed, so a row's result depends
+// only on its own keys.
 template <bool SPLIT>
-__global__ void attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ qkv, int ld,
-                                 const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
-                                 const int* __restrict__ positions, const int* __restrict__ row_slot,
-                                 const int* __restrict__ block_table, int max_pages, int nq, int nkv, float scale,
-                                 float* __restrict__ partial, int n_split, __nv_bfloat16* __restrict__ out) {
+__global__ void __launch_bounds__(512)
+attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ gate_buf,
+                 const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                 const int* __restrict__ positions, const int* __restrict__ row_slot,
+                 const int* __restrict__ block_table, int max_pages, int nq, int nkv, float scale,
+                 float* __restrict__ partial, int n_split, __nv_bfloat16* __restrict__ out) {
+    extern __shared__ float q_s[];                 // [group][256]
     const int row = blockIdx.x, kvh = blockIdx.y, split = SPLIT ? blockIdx.z : 0;
     const int group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,31 +114,76 @@ __global__ void attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv
     const int k0 = SPLIT ? split * kSplit : 0;
     const int k1 = SPLIT ? min(len, k0 + kSplit) : len;
     if (k0 >= len) return;
-    float qv[8];
-    unpack8(*reinterpret_cast<const uint4*>(q + (static_cast<long long>(row) * nq + head) * kHD + lane * 8), qv);
+    {
+        float qv[8];
+        unpack8(*reinterpret_cast<const uint4*>(q + (static_cast<long long>(row) * nq + head) * kHD + lane * 8), qv);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qv[i] *= scale;
+        for (int i = 0; i < 8; ++i) q_s[warp * kHD + lane * 8 + i] = qv[i] * scale;
+    }
+    __syncwarp();
+    const float4* qs4 = reinterpret_cast<const float4*>(q_s + warp * kHD);
     const int* table = block_table + static_cast<long long>(row_slot[row]) * max_pages;
+    const long long head_off = static_cast<long long>(kvh) * kHD;
+    const long long row_stride = static_cast<long long>(nkv) * kHD;
     float m = -FLT_MAX, l = 0.f, acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int key = k0; key < k1; ++key) {
-        const long long at = ((static_cast<long long>(table[key / kPage]) * kPage + key % kPage) * nkv + kvh) * kHD + lane * 8;
-        float kf[8], vf[8];
-        unpack8(*reinterpret_cast<const uint4*>(k_pages + at), kf);
-        unpack8(*reinterpret_cast<const uint4*>(v_pages + at), vf);
-        float s = 0.f;
+    for (int kb = k0; kb < k1; kb += 32) {
+        // all 32 keys of a group sit in one 64-key page (groups start on multiples of 32)
+        const long long page_base = (static_cast<long long>(table[kb / kPage]) * kPage + (kb % kPage)) * row_stride + head_off;
+        const int key = kb + lane;
+        const bool live = key < k1;
+        float s = -FLT_MAX;
+        if (live) {
+            const uint4* kr = reinterpret_cast<const uint4*>(k_pages + page_base + lane * row_stride);
+            float s0 = 0.f, s1 = 0.f;              // even / odd 8-column pieces, joined once at the end
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s += qv[i] * kf[i];
+            for (int c0 = 0; c0 < kHD / 8; c0 += 8) {
+                uint4 kk[8];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const float mn = fmaxf(m, s);
+                for (int u = 0; u < 8; ++u) kk[u] = kr[c0 + u];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    float kf[8];
+                    unpack8(kk[u], kf);
+                    const float4 qa = qs4[2 * (c0 + u)], qb = qs4[2 * (c0 + u) + 1];
+                    float& t = (u & 1) ? s1 : s0;
+                    t += qa.x * kf[0]; t += qa.y * kf[1]; t += qa.z * kf[2]; t += qa.w * kf[3];
+                    t += qb.x * kf[4]; t += qb.y * kf[5]; t += qb.z * kf[6]; t += qb.w * kf[7];
+                }
+            }
+            s = s0 + s1;
+        }
+        float gm = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+        const float mn = fmaxf(m, gm);
         const float corr = __expf(m - mn);
-        const float p = __expf(s - mn);
-        l = l * corr + p;
+        const float p = live ? __expf(s - mn) : 0.f;
+        float ps = p;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = acc[i] * corr + p * vf[i];
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l = l * corr + ps;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= corr;
         m = mn;
+        const int nk = min(32, k1 - kb);
+        const __nv_bfloat16* vr = v_pages + page_base + lane * 8;
+#pragma unroll
+        for (int j0 = 0; j0 < 32; j0 += 8) {
+            uint4 vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                vv[u] = (j0 + u < nk) ? *reinterpret_cast<const uint4*>(vr + (j0 + u) * row_stride) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float pj = __shfl_sync(0xffffffffu, p, j0 + u);
+                float vf[8];
+                unpack8(vv[u], vf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += pj * vf[i];
+            }
+        }
     }
     if (SPLIT) {
         float* dst = partial + ((static_cast<long long>(row) * nq + head) * n_split + split) * (kHD + 2);
@@ -120,7 +191,7 @@ __global__ void attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv
 #pragma unroll
         for (int i = 0; i < 8; ++i) dst[2 + lane * 8 + i] = acc[i];
     } else {
-        const __nv_bfloat16* gate = qkv + static_cast<long long>(row) * ld + head * 2 * kHD + kHD + lane * 8;
+        const __nv_bfloat16* gate = gate_buf + (static_cast<long long>(row) * nq + head) * kHD + lane * 8;
         __nv_bfloat16* dst = out + (static_cast<long long>(row) * nq + head) * kHD + lane * 8;
         const float inv = 1.f / l;
 #pragma unroll
@@ -129,50 +200,59 @@ __global__ void attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv
 }
 
 __global__ void attn_merge_kernel(const float* __restrict__ partial, int n_split, const int* __restrict__ positions,
-                                  const __nv_bfloat16* __restrict__ qkv, int ld, int nq, __nv_bfloat16* __restrict__ out) {
+                                  const __nv_bfloat16* __restrict__ gate_buf, int nq, __nv_bfloat16* __restrict__ out) {
     const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int used = (positions[row] + kSplit) / kSplit;          // ceil((pos + 1) / split)
     const float* src = partial + (static_cast<long long>(row) * nq + head) * n_split * (kHD + 2);
     float M = -FLT_MAX;
+#pragma unroll 8
     for (int s = 0; s < used; ++s) M = fmaxf(M, src[s * (kHD + 2)]);
     float L = 0.f, o = 0.f;
+#pragma unroll 8
     for (int s = 0; s < used; ++s) {
         const float e = __expf(src[s * (kHD + 2)] - M);
         L += src[s * (kHD + 2) + 1] * e;
         o += src[s * (kHD + 2) + 2 + d] * e;
     }
-    const float gate = __bfloat162float(qkv[static_cast<long long>(row) * ld + head * 2 * kHD + kHD + d]);
+    const float gate = __bfloat162float(gate_buf[(static_cast<long long>(row) * nq + head) * kHD + d]);
     out[(static_cast<long long>(row) * nq + head) * kHD + d] = __float2bfloat16_rn(o / L * sigmoidf_(gate));
 }
 
-const char* attn_prep(const void* qkv, int ld, int rows, int nq, int nkv, int hd, const float* q_norm, const float* k_norm,
-                      const int* positions, const int* row_slot, const int* block_table, int max_pages, void* q_out,
-                      void* k_pages, void* v_pages, int rot, double theta, float eps, cudaStream_t s) {
+const char* attn_prep(const void* qkv, bool parts, int n_parts, long long part_stride, int ld, int rows, int nq, int nkv, int hd,
+                      const float* q_norm, const float* k_norm, const int* positions, const int* row_slot, const int* block_table,
+                      int max_pages, void* q_out, void* gate_out, void* k_pages, void* v_pages, int rot, double theta, float eps,
+                      cudaStream_t s) {
     if (hd != kHD) return "attention kernels handle head dimension 256";
-    attn_prep_kernel<<<dim3(rows, nq + nkv), kHD, 0, s>>>(static_cast<const __nv_bfloat16*>(qkv), ld, nq, nkv, q_norm, k_norm, positions,
-                                                         row_slot, block_table, max_pages, static_cast<__nv_bfloat16*>(q_out),
-                                                         static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages),
-                                                         rot, log(theta), eps);
+    const dim3 grid(rows, nq + nkv);
+    __nv_bfloat16 *qo = static_cast<__nv_bfloat16*>(q_out), *go = static_cast<__nv_bfloat16*>(gate_out);
+    __nv_bfloat16 *kp = static_cast<__nv_bfloat16*>(k_pages), *vp = static_cast<__nv_bfloat16*>(v_pages);
+    if (parts)
+        attn_prep_kernel<true><<<grid, kHD, 0, s>>>(qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
+                                                    block_table, max_pages, qo, go, kp, vp, rot, log(theta), eps);
+    else
+        attn_prep_kernel<false><<<grid, kHD, 0, s>>>(qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
+                                                     block_table, max_pages, qo, go, kp, vp, rot, log(theta), eps);
     return cudaGetLastError() == cudaSuccess ? nullptr : "attn_prep launch failed";
 }
 
-const char* attn_rows(const void* q, const void* qkv, int ld, const void* k_pages, const void* v_pages, const int* positions,
+const char* attn_rows(const void* q, const void* gate, const void* k_pages, const void* v_pages, const int* positions,
                       const int* row_slot, const int* block_table, int max_pages, int rows, int nq, int nkv, int hd,
                       bool split, float* partial, int n_split, void* out, cudaStream_t s) {
     if (hd != kHD) return "attention kernels handle head dimension 256";
     const int group = nq / nkv;
-    if (group < 1 || group > 32 || nq % nkv != 0) return "bad GQA group";
+    if (group < 1 || group > 16 || nq % nkv != 0) return "GQA group must be 1..16";
     const float scale = 1.0f / sqrtf(static_cast<float>(hd));
-    const __nv_bfloat16 *qp = static_cast<const __nv_bfloat16*>(q), *qk = static_cast<const __nv_bfloat16*>(qkv);
+    const __nv_bfloat16 *qp = static_cast<const __nv_bfloat16*>(q), *gp = static_cast<const __nv_bfloat16*>(gate);
     const __nv_bfloat16 *kp = static_cast<const __nv_bfloat16*>(k_pages), *vp = static_cast<const __nv_bfloat16*>(v_pages);
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+    const size_t sm = group * kHD * sizeof(float);
     if (split) {
-        attn_rows_kernel<true><<<dim3(rows, nkv, n_split), group * 32, 0, s>>>(qp, qk, ld, kp, vp, positions, row_slot, block_table,
-                                                                              max_pages, nq, nkv, scale, partial, n_split, o);
-        attn_merge_kernel<<<dim3(rows, nq), kHD, 0, s>>>(partial, n_split, positions, qk, ld, nq, o);
+        attn_rows_kernel<true><<<dim3(rows, nkv, n_split), group * 32, sm, s>>>(qp, gp, kp, vp, positions, row_slot, block_table,
+                                                                               max_pages, nq, nkv, scale, partial, n_split, o);
+        attn_merge_kernel<<<dim3(rows, nq), kHD, 0, s>>>(partial, n_split, positions, gp, nq, o);
     } else {
-        attn_rows_kernel<false><<<dim3(rows, nkv, 1), group * 32, 0, s>>>(qp, qk, ld, kp, vp, positions, row_slot, block_table,
-                                                                         max_pages, nq, nkv, scale, partial, 1, o);
+        attn_rows_kernel<false><<<dim3(rows, nkv, 1), group * 32, sm, s>>>(qp, gp, kp, vp, positions, row_slot, block_table,
+                                                                          max_pages, nq, nkv, scale, partial, 1, o);
     }
     return cudaGetLastError() == cudaSuccess ? nullptr : "attention launch failed";
 }

@@ -4,13 +4,17 @@
 
 namespace vade {
 
-const char* attn_prep(const void* qkv, int ld, int rows, int nq, int nkv, int hd, const float* q_norm, const float* k_norm,
-                      const int* positions, const int* row_slot, const int* block_table, int max_pages, void* q_out,
-                      void* k_pages, void* v_pages, int rot, double theta, float eps, cudaStream_t s);
+// qkv: bf16 [rows][ld], or (parts = true) fp32 [n_parts][rows][ld] K-range partials that are added in
+// ascending order and rounded to bf16.  Writes q and the per-head output gate as bf16 [rows][nq][hd]
+// and appends k/v to the row's cache page.
+const char* attn_prep(const void* qkv, bool parts, int n_parts, long long part_stride, int ld, int rows, int nq, int nkv, int hd,
+                      const float* q_norm, const float* k_norm, const int* positions, const int* row_slot, const int* block_table,
+                      int max_pages, void* q_out, void* gate_out, void* k_pages, void* v_pages, int rot, double theta, float eps,
+                      cudaStream_t s);
 
-// split = true: decode class (fixed 256-key splits, `partial` is fp32 scratch of
+// split = true: decode class (fixed 128-key splits, `partial` is fp32 scratch of
 // rows * nq * n_split * 258 floats); split = false: prefill class, single pass.
-const char* attn_rows(const void* q, const void* qkv, int ld, const void* k_pages, const void* v_pages, const int* positions,
+const char* attn_rows(const void* q, const void* gate, const void* k_pages, const void* v_pages, const int* positions,
                       const int* row_slot, const int* block_table, int max_pages, int rows, int nq, int nkv, int hd,
                       bool split, float* partial, int n_split, void* out, cudaStream_t s);
 

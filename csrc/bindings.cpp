@@ -73,7 +73,7 @@ void fold_add_norm(torch::Tensor parts, int64_t n_parts, int64_t part_stride, to
 
 void combine_add_norm(torch::Tensor y, torch::Tensor slot_row, torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, int64_t k,
                       int64_t ns, torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> h, double eps) {
-    need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 64, "combine arguments");
+    need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 32 && x.size(1) % 8 == 0, "combine arguments");
     c10::cuda::CUDAGuard guard(x.device());
     vade::combine_add_norm(y.data_ptr(), slot_row.data_ptr<int>(), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
                            static_cast<int>(k), static_cast<int>(ns), x.data_ptr<float>(), ptr<float>(w),
@@ -88,25 +88,46 @@ void gather_rows(torch::Tensor x, torch::Tensor row_token, torch::Tensor meta, t
                       static_cast<int>(x.size(1)), stream_of(x));
 }
 
-void moe_route(torch::Tensor logits, int64_t E, int64_t k, bool renorm, int64_t e0, int64_t n_local, int64_t ns, int64_t bn,
-               torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, torch::Tensor counts, torch::Tensor pos, torch::Tensor offsets,
-               torch::Tensor tasks, torch::Tensor meta, int64_t max_tasks, torch::Tensor row_token, torch::Tensor slot_row) {
-    need(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 && E <= 1024 && k <= 32, "route arguments");
+void moe_route(torch::Tensor logits, int64_t n_parts, int64_t E, int64_t k, bool renorm, int64_t e0, int64_t n_local, int64_t ns,
+               int64_t bn, torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, torch::Tensor counts, torch::Tensor pos,
+               torch::Tensor offsets, torch::Tensor tasks, torch::Tensor meta, int64_t max_tasks, torch::Tensor row_token,
+               torch::Tensor slot_row) {
+    // logits: fp32 [n_parts, T, ld] (or [T, ld] when n_parts == 1)
+    need(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous(), "route arguments");
     c10::cuda::CUDAGuard guard(logits.device());
-    vade::moe_route(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), static_cast<int>(logits.size(0)), static_cast<int>(E),
-                    static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local), static_cast<int>(ns), static_cast<int>(bn),
-                    ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(), counts.data_ptr<int>(), pos.data_ptr<int>(),
-                    offsets.data_ptr<int>(), tasks.data_ptr<int>(), meta.data_ptr<int>(), static_cast<int>(max_tasks),
-                    row_token.data_ptr<int>(), slot_row.data_ptr<int>(), stream_of(logits));
+    const int64_t T = logits.size(-2), ld = logits.size(-1);
+    check(vade::moe_route(logits.data_ptr<float>(), T * ld, static_cast<int>(n_parts), static_cast<int>(ld), static_cast<int>(T),
+                          static_cast<int>(E), static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local),
+                          static_cast<int>(ns), static_cast<int>(bn), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
+                          counts.data_ptr<int>(), pos.data_ptr<int>(), offsets.data_ptr<int>(), tasks.data_ptr<int>(),
+                          meta.data_ptr<int>(), static_cast<int>(max_tasks), row_token.data_ptr<int>(), slot_row.data_ptr<int>(),
+                          stream_of(logits)));
+}
+
+void moe_route_small(torch::Tensor logits, int64_t n_parts, int64_t E, int64_t k, bool renorm, int64_t e0, int64_t n_local, int64_t ns,
+                     torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, torch::Tensor tasks_up, torch::Tensor tasks_down,
+                     torch::Tensor meta, torch::Tensor slot_row) {
+    need(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous(), "route arguments");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t T = logits.size(-2), ld = logits.size(-1);
+    check(vade::moe_route_small(logits.data_ptr<float>(), T * ld, static_cast<int>(n_parts), static_cast<int>(ld), static_cast<int>(T),
+                                static_cast<int>(E), static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local),
+                                static_cast<int>(ns), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
+                                tasks_up.data_ptr<int>(), tasks_down.data_ptr<int>(), meta.data_ptr<int>(), slot_row.data_ptr<int>(),
+                                stream_of(logits)));
 }
 
 void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
               torch::Tensor dt_bias, torch::Tensor norm_w, torch::Tensor seq_slot, torch::Tensor seq_start, int64_t n_seq,
               torch::Tensor out, int64_t kh, int64_t vh, int64_t kd, int64_t vd, double eps, bool gate_silu) {
-    need(proj.scalar_type() == torch::kBFloat16 && proj.stride(1) == 1 && state.scalar_type() == torch::kFloat32 &&
-         hist.scalar_type() == torch::kFloat32 && out.scalar_type() == torch::kBFloat16 && out.is_contiguous(), "gdn arguments");
+    // proj: bf16 [rows, ld] or fp32 K-range partials [parts, rows, ld]
+    const bool parts = proj.dim() == 3;
+    need(proj.is_contiguous() && (parts ? proj.scalar_type() == torch::kFloat32 : proj.scalar_type() == torch::kBFloat16) &&
+         state.scalar_type() == torch::kFloat32 && hist.scalar_type() == torch::kFloat32 &&
+         out.scalar_type() == torch::kBFloat16 && out.is_contiguous(), "gdn arguments");
     c10::cuda::CUDAGuard guard(proj.device());
-    check(vade::gdn_scan(proj.data_ptr(), static_cast<int>(proj.stride(0)), conv_w.data_ptr<float>(), hist.data_ptr<float>(),
+    check(vade::gdn_scan(proj.data_ptr(), parts, parts ? static_cast<int>(proj.size(0)) : 1, parts ? proj.stride(0) : 0,
+                         static_cast<int>(proj.size(-1)), conv_w.data_ptr<float>(), hist.data_ptr<float>(),
                          state.data_ptr<float>(), a_log.data_ptr<float>(), dt_bias.data_ptr<float>(), norm_w.data_ptr<float>(),
                          seq_slot.data_ptr<int>(), seq_start.data_ptr<int>(), static_cast<int>(n_seq), out.data_ptr(),
                          static_cast<int>(kh), static_cast<int>(vh), static_cast<int>(kd), static_cast<int>(vd),
@@ -114,28 +135,40 @@ void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torc
 }
 
 void attn_prep(torch::Tensor qkv, int64_t nq, int64_t nkv, int64_t hd, torch::Tensor q_norm, torch::Tensor k_norm,
-               torch::Tensor positions, torch::Tensor row_slot, torch::Tensor block_table, torch::Tensor q_out,
+               torch::Tensor positions, torch::Tensor row_slot, torch::Tensor block_table, torch::Tensor q_out, torch::Tensor gate_out,
                torch::Tensor k_pages, torch::Tensor v_pages, int64_t rot, double theta, double eps) {
-    need(qkv.scalar_type() == torch::kBFloat16 && qkv.stride(1) == 1 && k_pages.scalar_type() == torch::kBFloat16 &&
-         positions.scalar_type() == torch::kInt32 && block_table.scalar_type() == torch::kInt32, "attn_prep arguments");
+    const bool parts = qkv.dim() == 3;
+    need(qkv.is_contiguous() && (parts ? qkv.scalar_type() == torch::kFloat32 : qkv.scalar_type() == torch::kBFloat16) &&
+         k_pages.scalar_type() == torch::kBFloat16 && positions.scalar_type() == torch::kInt32 &&
+         block_table.scalar_type() == torch::kInt32, "attn_prep arguments");
     c10::cuda::CUDAGuard guard(qkv.device());
-    check(vade::attn_prep(qkv.data_ptr(), static_cast<int>(qkv.stride(0)), static_cast<int>(qkv.size(0)), static_cast<int>(nq),
+    check(vade::attn_prep(qkv.data_ptr(), parts, parts ? static_cast<int>(qkv.size(0)) : 1, parts ? qkv.stride(0) : 0,
+                          static_cast<int>(qkv.size(-1)), static_cast<int>(qkv.size(-2)), static_cast<int>(nq),
                           static_cast<int>(nkv), static_cast<int>(hd), q_norm.data_ptr<float>(), k_norm.data_ptr<float>(),
                           positions.data_ptr<int>(), row_slot.data_ptr<int>(), block_table.data_ptr<int>(),
-                          static_cast<int>(block_table.size(1)), q_out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
-                          static_cast<int>(rot), theta, static_cast<float>(eps), stream_of(qkv)));
+                          static_cast<int>(block_table.size(1)), q_out.data_ptr(), gate_out.data_ptr(), k_pages.data_ptr(),
+                          v_pages.data_ptr(), static_cast<int>(rot), theta, static_cast<float>(eps), stream_of(qkv)));
 }
 
-void attn_rows(torch::Tensor q, torch::Tensor qkv, torch::Tensor k_pages, torch::Tensor v_pages, torch::Tensor positions,
+void attn_rows(torch::Tensor q, torch::Tensor gate, torch::Tensor k_pages, torch::Tensor v_pages, torch::Tensor positions,
                torch::Tensor row_slot, torch::Tensor block_table, int64_t nq, int64_t nkv, int64_t hd, bool split,
                c10::optional<torch::Tensor> partial, int64_t n_split, torch::Tensor out) {
-    need(q.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16, "attn_rows arguments");
+    need(q.scalar_type() == torch::kBFloat16 && gate.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
+         "attn_rows arguments");
     need(!split || (partial.has_value() && partial->numel() >= q.size(0) * nq * n_split * (hd + 2)), "attention scratch too small");
     c10::cuda::CUDAGuard guard(q.device());
-    check(vade::attn_rows(q.data_ptr(), qkv.data_ptr(), static_cast<int>(qkv.stride(0)), k_pages.data_ptr(), v_pages.data_ptr(),
+    check(vade::attn_rows(q.data_ptr(), gate.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
                           positions.data_ptr<int>(), row_slot.data_ptr<int>(), block_table.data_ptr<int>(),
                           static_cast<int>(block_table.size(1)), static_cast<int>(q.size(0)), static_cast<int>(nq), static_cast<int>(nkv),
                           static_cast<int>(hd), split, ptr<float>(partial), static_cast<int>(n_split), out.data_ptr(), stream_of(q)));
+}
+
+void swiglu_fold(torch::Tensor parts, torch::Tensor meta, torch::Tensor mid) {
+    need(parts.dim() == 3 && parts.scalar_type() == torch::kFloat32 && parts.is_contiguous() && parts.size(0) <= 8 &&
+         mid.scalar_type() == torch::kBFloat16 && mid.is_contiguous() && parts.size(2) == 2 * mid.size(1), "swiglu_fold arguments");
+    c10::cuda::CUDAGuard guard(parts.device());
+    vade::swiglu_fold(parts.data_ptr<float>(), parts.stride(0), static_cast<int>(parts.size(0)), meta.data_ptr<int>() + 1, mid.data_ptr(),
+                      static_cast<int>(parts.size(1)), static_cast<int>(mid.size(1)), stream_of(parts));
 }
 
 void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id) {
@@ -155,7 +188,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fold_add_norm", &fold_add_norm);
     m.def("combine_add_norm", &combine_add_norm);
     m.def("gather_rows", &gather_rows);
+    m.def("swiglu_fold", &swiglu_fold);
     m.def("moe_route", &moe_route);
+    m.def("moe_route_small", &moe_route_small);
     m.def("gdn_scan", &gdn_scan);
     m.def("attn_prep", &attn_prep);
     m.def("attn_rows", &attn_rows);

@@ -30,9 +30,23 @@ __device__ __forceinline__ float group_sum(float v, float* red, int g, int wg, i
     return ((red[g * 4 + 0] + red[g * 4 + 1]) + (red[g * 4 + 2] + red[g * 4 + 3]));
 }
 
-template <int REP>
+// One projection value: a bf16 element, or the bf16 rounding of the ascending sum of fp32 K-range partials.
+template <bool PARTS>
+__device__ __forceinline__ float proj_at(const void* proj, long long row, int ld, int col, int n_parts, long long part_stride) {
+    if (!PARTS) return __bfloat162float(static_cast<const __nv_bfloat16*>(proj)[row * ld + col]);
+    const float* p = static_cast<const float*>(proj) + row * ld + col;
+    if (n_parts == 4) {                         // the loads are independent; only the adds are ordered
+        const float a0 = p[0], a1 = p[part_stride], a2 = p[2 * part_stride], a3 = p[3 * part_stride];
+        return bf16_round(((a0 + a1) + a2) + a3);
+    }
+    float a = p[0];
+    for (int i = 1; i < n_parts; ++i) a += p[i * part_stride];
+    return bf16_round(a);
+}
+
+template <int REP, bool PARTS>
 __global__ void __launch_bounds__(REP * 128, 1)
-gdn_scan_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+gdn_scan_kernel(const void* __restrict__ proj, int ld, int n_parts, long long part_stride, const float* __restrict__ conv_w,
                 float* __restrict__ hist, float* __restrict__ state, const float* __restrict__ a_log,
                 const float* __restrict__ dt_bias, const float* __restrict__ norm_w,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
@@ -73,8 +87,12 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
     const float qscale = rsqrtf(static_cast<float>(kD));
 
     for (int r = r0; r < r1; ++r) {
-        const __nv_bfloat16* p = proj + static_cast<long long>(r) * ld;
-        const float xq = __bfloat162float(p[cq]), xk = __bfloat162float(p[ck]), xv = __bfloat162float(p[cv]);
+        const float xq = proj_at<PARTS>(proj, r, ld, cq, n_parts, part_stride);
+        const float xk = proj_at<PARTS>(proj, r, ld, ck, n_parts, part_stride);
+        const float xv = proj_at<PARTS>(proj, r, ld, cv, n_parts, part_stride);
+        const float xb = proj_at<PARTS>(proj, r, ld, ob, n_parts, part_stride);
+        const float xa = proj_at<PARTS>(proj, r, ld, oa, n_parts, part_stride);
+        const float z = proj_at<PARTS>(proj, r, ld, oz, n_parts, part_stride);
         float aq = 0.f, ak = 0.f, av = 0.f;
         aq += hq[0] * wq[0]; aq += hq[1] * wq[1]; aq += hq[2] * wq[2]; aq += xq * wq[3];
         ak += hk[0] * wk[0]; ak += hk[1] * wk[1]; ak += hk[2] * wk[2]; ak += xk * wk[3];
@@ -87,8 +105,8 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
         const float ssk = group_sum(k * k, red + rep * 4, g, wg, lane);
         q_s[g * kD + j] = q * rsqrtf(ssq + 1e-6f) * qscale;
         k_s[g * kD + j] = k * rsqrtf(ssk + 1e-6f);
-        const float beta = sigmoidf_(__bfloat162float(p[ob]));
-        const float ax = __bfloat162float(p[oa]) + dtb;
+        const float beta = sigmoidf_(xb);
+        const float ax = xa + dtb;
         const float sp_ = ax > 20.f ? ax : log1pf(__expf(ax));
         const float decay = __expf(neg_a * sp_);
         __syncthreads();
@@ -102,7 +120,6 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
 #pragma unroll
         for (int i = 0; i < kD; ++i) { S[i] += kv[i] * delta; o += S[i] * qv[i]; }
         const float sso = group_sum(o * o, red, g, wg, lane);
-        const float z = __bfloat162float(p[oz]);
         const float gz = gate_silu ? siluf_(z) : sigmoidf_(z);
         out[static_cast<long long>(r) * (vh * kD) + vhead * kD + j] = __float2bfloat16_rn(o * rsqrtf(sso / kD + eps) * nw * gz);
     }
@@ -115,20 +132,25 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
     }
 }
 
-const char* gdn_scan(const void* proj, int ld, const float* conv_w, float* hist, float* state, const float* a_log,
-                     const float* dt_bias, const float* norm_w, const int* seq_slot, const int* seq_start, int n_seq,
-                     void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu, cudaStream_t s) {
+const char* gdn_scan(const void* proj, bool parts, int n_parts, long long part_stride, int ld, const float* conv_w, float* hist,
+                     float* state, const float* a_log, const float* dt_bias, const float* norm_w, const int* seq_slot,
+                     const int* seq_start, int n_seq, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
+                     cudaStream_t s) {
     if (kd != kD || vd != kD) return "gdn_scan handles head dimension 128";
     if (vh % kh != 0 || vh / kh > 3) return "value heads per key head must be 1, 2 or 3";
     const int rep = vh / kh;
     const size_t smem = (2 * rep * kD + 2 * rep * 4) * sizeof(float);
     const dim3 grid(kh, n_seq);
-    const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
     const int gs = gate_silu ? 1 : 0;
-    if (rep == 1) gdn_scan_kernel<1><<<grid, 128, smem, s>>>(pj, ld, conv_w, hist, state, a_log, dt_bias, norm_w, seq_slot, seq_start, o, kh, vh, eps, gs);
-    else if (rep == 2) gdn_scan_kernel<2><<<grid, 256, smem, s>>>(pj, ld, conv_w, hist, state, a_log, dt_bias, norm_w, seq_slot, seq_start, o, kh, vh, eps, gs);
-    else gdn_scan_kernel<3><<<grid, 384, smem, s>>>(pj, ld, conv_w, hist, state, a_log, dt_bias, norm_w, seq_slot, seq_start, o, kh, vh, eps, gs);
+#define VADE_GDN(REP, PARTS) gdn_scan_kernel<REP, PARTS><<<grid, REP * 128, smem, s>>>(proj, ld, n_parts, part_stride, conv_w, hist, \
+        state, a_log, dt_bias, norm_w, seq_slot, seq_start, o, kh, vh, eps, gs)
+    if (parts) {
+        if (rep == 1) VADE_GDN(1, true); else if (rep == 2) VADE_GDN(2, true); else VADE_GDN(3, true);
+    } else {
+        if (rep == 1) VADE_GDN(1, false); else if (rep == 2) VADE_GDN(2, false); else VADE_GDN(3, false);
+    }
+#undef VADE_GDN
     return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_scan launch failed";
 }
 

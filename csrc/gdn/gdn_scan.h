@@ -6,8 +6,10 @@ namespace vade {
 
 // proj: bf16 [rows][ld] = [q | k | v | z | b | a] of the local heads; out: bf16 [rows][vh * vd].
 // hist fp32 [slots][3][conv channels]; state fp32 [slots][vh][kd][vd]; both updated in place.
-const char* gdn_scan(const void* proj, int ld, const float* conv_w, float* hist, float* state, const float* a_log,
-                     const float* dt_bias, const float* norm_w, const int* seq_slot, const int* seq_start, int n_seq,
-                     void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu, cudaStream_t s);
+// parts = true: proj is fp32 [n_parts][rows][ld] K-range partials (added in ascending order, rounded to bf16).
+const char* gdn_scan(const void* proj, bool parts, int n_parts, long long part_stride, int ld, const float* conv_w, float* hist,
+                     float* state, const float* a_log, const float* dt_bias, const float* norm_w, const int* seq_slot,
+                     const int* seq_start, int n_seq, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
+                     cudaStream_t s);
 
 }  // namespace vade

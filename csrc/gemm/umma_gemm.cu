@@ -9,8 +9,9 @@
 // One CTA computes one 128 x BN output tile over one K range:
 //   warp 0      producer: one bulk copy (NVFP4 block) or tiled TMA load (bf16 weights) plus one
 //               tiled TMA load of the X tile per 64-column K block, STAGES deep
-//   warps 2..5  NVFP4 only: expand nibbles to bf16 (e2m1 * e4m3, exact) into the 128-byte
-//               swizzled A tile; afterwards the epilogue: tcgen05.ld, row scale, store
+//   warps 2..9  NVFP4 only: expand nibbles to bf16 (e2m1 * e4m3, exact) into the 128-byte
+//               swizzled A tile (one thread per row and 32-column half); afterwards the epilogue:
+//               tcgen05.ld, row scale, store (each warp set takes half of the token columns)
 //   warp 1      one thread issues tcgen05.mma (4 x K16 per block) and commits to mbarriers
 // grid = (row tiles, token tiles or grouped tasks, K ranges).  With more than one range each
 // CTA writes an fp32 partial [range][token][row]; the caller folds ranges in a fixed tree.
@@ -30,7 +31,7 @@ constexpr int kTileM = 128;
 constexpr int kTileK = 64;
 constexpr int kWBlockBytes = 4608;
 constexpr int kAStageBytes = kTileM * kTileK * 2;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;             // warp 0 producer, warp 1 MMA, warps 2..9 dequant + epilogue
 
 struct GemmDev {
     const uint8_t* w_tiles;
@@ -50,20 +51,21 @@ struct GemmDev {
 };
 
 template <int BN, int STAGES, bool NVFP4, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (BN <= 32 ? 2 : 1))
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmDev a) {
     constexpr int kBStageBytes = BN * kTileK * 2;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
     constexpr uint32_t kTxBytes = (NVFP4 ? kWBlockBytes : kAStageBytes) + kBStageBytes;
 
-    int expert = 0, row0, nrows;
+    int expert = 0, row0, nrows, orow0;
     if (a.tasks != nullptr) {
         if (static_cast<int>(blockIdx.y) >= *a.num_tasks) return;
         const int4 t = a.tasks[blockIdx.y];
-        expert = t.x; row0 = t.y; nrows = t.z;
+        expert = t.x; row0 = t.y; nrows = t.z; orow0 = t.w;
     } else {
         row0 = blockIdx.y * BN;
         nrows = min(BN, a.tokens - row0);
+        orow0 = row0;
     }
     const int mtile = blockIdx.x;
     const int range = blockIdx.z;
@@ -89,7 +91,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&aready[s], 128);
+            mbar_init(&aready[s], 256);
             mbar_init(&empty[s], 1);
         }
         mbar_init(tmem_full, 1);
@@ -145,52 +147,48 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             umma_commit(tmem_full);
         }
     } else {
-        const int t = threadIdx.x - 64;          // 0..127: weight row inside the tile (dequant role)
+        const int t = (threadIdx.x - 64) & 127;   // weight row inside the tile
+        const int half = (threadIdx.x - 64) >> 7; // which 32-column half of the K block this thread expands
         if (NVFP4) {
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(&full[s], ph)) { fail(4); break; }
                 const uint8_t* raw = sW + s * kWBlockBytes;
+                const uint4 q = *reinterpret_cast<const uint4*>(raw + half * 2048 + t * 16);
                 const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 4096 + t * 4);
-                // four e4m3 block scales -> bf16x2 multipliers (scale * 2^112), see below
-                uint32_t mult[4];
+                // two e4m3 block scales -> bf16x2 multipliers (scale * 2^112)
+                uint32_t mult[2];
                 {
-                    uint32_t h01, h23;
-                    const uint16_t lo16 = static_cast<uint16_t>(sc4 & 0xFFFF), hi16 = static_cast<uint16_t>(sc4 >> 16);
-                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(lo16));
-                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(hi16));
+                    uint32_t h01;
+                    const uint16_t two = static_cast<uint16_t>((sc4 >> (16 * half)) & 0xFFFF);
+                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(two));
                     const __half2 a01 = *reinterpret_cast<const __half2*>(&h01);
-                    const __half2 a23 = *reinterpret_cast<const __half2*>(&h23);
-                    const float f[4] = {__low2float(a01), __high2float(a01), __low2float(a23), __high2float(a23)};
+                    const float f[2] = {__low2float(a01), __high2float(a01)};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 2; ++j) {
                         const uint32_t b = __float_as_uint(f[j] * 0x1p112f) >> 16;   // exact: <= 4 significant bits
                         mult[j] = b | (b << 16);
                     }
                 }
                 uint8_t* arow = sA + s * kAStageBytes + t * 128;
+                const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const uint4 q = *reinterpret_cast<const uint4*>(raw + half * 2048 + t * 16);
-                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+                for (int w = 0; w < 4; ++w) {
+                    // 8 nibbles of one word = columns 32*half + 8*w .. +7; block scale index 2*half + w/2
+                    const uint32_t m2 = mult[w >> 1];
+                    uint32_t o[4];
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        // 8 nibbles of one word = columns 32*half + 8*w .. +7; block scale index 2*half + w/2
-                        const uint32_t m2 = mult[2 * half + (w >> 1)];
-                        uint32_t o[4];
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            uint32_t h2;
-                            const uint16_t byte = static_cast<uint16_t>((words[w] >> (8 * b)) & 0xFF);
-                            asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(byte));
-                            // f16 bits >> 3 read as bf16 equal value * 2^-112 (normal for |v| >= 0.5, zero stays zero)
-                            const uint32_t p = ((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u);
-                            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[b]) : "r"(p), "r"(m2));
-                        }
-                        const int chunk = half * 4 + w;
-                        *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int b = 0; b < 4; ++b) {
+                        uint32_t h2;
+                        const uint16_t byte = static_cast<uint16_t>((words[w] >> (8 * b)) & 0xFF);
+                        asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(byte));
+                        // f16 bits >> 3 read as bf16 equal value * 2^-112 (normal for |v| >= 0.5, zero stays zero)
+                        const uint32_t p = ((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u);
+                        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[b]) : "r"(p), "r"(m2));
                     }
+                    const int chunk = half * 4 + w;
+                    *reinterpret_cast<uint4*>(arow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&aready[s]);
@@ -204,14 +202,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         tc_fence_after_sync();
         if (ok) {
             const float rs = (m < a.n_out) ? a.row_scale[static_cast<long long>(expert) * a.rs_expert_stride + m] : 0.f;
-            for (int c = 0; c < BN; c += 16) {
+            constexpr int kColsPerSet = BN >= 32 ? BN / 2 : BN;
+            const int cbeg = BN >= 32 ? half * kColsPerSet : 0;
+            const int cend = (BN >= 32 || half == 0) ? cbeg + kColsPerSet : 0;
+            for (int c = cbeg; c < cend; c += 16) {
                 if (c >= nrows) break;
                 float v[16];
                 tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c, v);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float y = v[j] * rs;
-                    const long long tok = row0 + c + j;
+                    const long long tok = orow0 + c + j;
                     if (EPI == 2) {
                         const float yb = bf16_round(y);
                         const float other = __shfl_xor_sync(0xffffffffu, yb, 1);
@@ -276,8 +277,8 @@ static const char* launch_one(const GemmArgs& h, const CUtensorMap& tx, const CU
 template <bool NVFP4, int EPI>
 static const char* launch_bn(const GemmArgs& h, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, dim3 grid, cudaStream_t s) {
     switch (h.bn) {
-        case 16:  return launch_one<16, 8, NVFP4, EPI>(h, tx, tw, d, grid, s);
-        case 32:  return launch_one<32, 8, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 16:  return launch_one<16, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 32:  return launch_one<32, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
         case 64:  return launch_one<64, 6, NVFP4, EPI>(h, tx, tw, d, grid, s);
         case 128: return launch_one<128, 5, NVFP4, EPI>(h, tx, tw, d, grid, s);
         case 256: return launch_one<256, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);

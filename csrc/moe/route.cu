@@ -1,14 +1,19 @@
 // MoE routing on the device: softmax -> top-k (ties to the lower expert id) -> renormalise, then the
-// expert-sorted row layout the grouped GEMM consumes.
+// row layout the grouped GEMM consumes.  Router logits may arrive as several K-range partials
+// (fp32 [parts][T][ld]); they are added in ascending part order before the softmax.
 //
-//   route_count   one warp per token: fp32 softmax numerators, k selection rounds, weights; each
-//                 selected pair of a LOCAL expert takes a position inside its expert with an
-//                 integer atomic (positions only decide which row of the gathered matrix a pair
-//                 occupies, never any arithmetic)
-//   scan_tasks    one CTA: prefix sums over local + shared experts, task table for the grouped
-//                 GEMM ({expert, first row, rows}), totals; re-zeroes the counters for the next call
-//   scatter_rows  one thread per (token, slot): row_token[] (gather list) and slot_row[][] (where
-//                 the combine finds each slot's output; -1 when another rank owns the expert)
+// Large passes (prompt tiles):
+//   route_count   one warp per token; each selected pair of a LOCAL expert takes a position inside
+//                 its expert with an integer atomic (positions only decide which row of the gathered
+//                 matrix a pair occupies, never any arithmetic)
+//   scan_tasks    one CTA: prefix sums over local + shared experts, task table {expert, first row,
+//                 rows, first output row}, totals; re-zeroes the counters for the next call
+//   scatter_rows  one thread per (token, slot): row_token[] (gather list) and slot_row[][] (where the
+//                 combine finds each slot's output; -1 when another rank owns the expert)
+// Small passes (decode / verify, T <= 16):
+//   route_small   one CTA does all of it without a gather: every ACTIVE expert (ascending id) becomes
+//                 one task over all T token rows (the token tile is 16 wide anyway); outputs of
+//                 tokens that did not pick the expert are never read.
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cfloat>
@@ -17,42 +22,44 @@
 
 namespace vade {
 
-constexpr int kMaxPerLane = 32;      // up to 1024 experts
-
-__global__ void route_count_kernel(const float* __restrict__ logits, int ld, int T, int E, int k, int renorm,
-                                   int e0, int n_local, int* __restrict__ ids, float* __restrict__ wts,
-                                   float* __restrict__ sg, int* __restrict__ counts, int* __restrict__ pos) {
-    const int warps_per_block = blockDim.x >> 5;
-    const int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (t >= T) return;
-    const float* row = logits + static_cast<long long>(t) * ld;
-    const int per = (E + 31) / 32;
-    float v[kMaxPerLane];
+// top-k of one token by one warp.  PER = ceil(E / 32) logits per lane, kept in registers.
+template <int PER>
+__device__ __forceinline__ void warp_topk(const float* __restrict__ logits, long long part_stride, int n_parts, int E, int k,
+                                          int renorm, int lane, float& sel_w, int& sel_e, float& gate_logit) {
+    float v[PER];
     float mx = -FLT_MAX;
-#pragma unroll 4
-    for (int i = 0; i < per; ++i) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
         const int e = i * 32 + lane;
-        v[i] = e < E ? row[e] : -FLT_MAX;
-        mx = fmaxf(mx, v[i]);
+        float a = -FLT_MAX;
+        if (e < E) {
+            a = logits[e];
+            for (int p = 1; p < n_parts; ++p) a += logits[p * part_stride + e];
+        }
+        v[i] = a;
+        mx = fmaxf(mx, a);
     }
+    gate_logit = logits[E];
+    for (int p = 1; p < n_parts; ++p) gate_logit += logits[p * part_stride + E];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.f;
-    for (int i = 0; i < per; ++i) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
         const int e = i * 32 + lane;
         v[i] = e < E ? __expf(v[i] - mx) : -1.f;      // numerators; -1 marks "not a candidate"
         if (e < E) sum += v[i];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    float sel_w = 0.f;
-    int sel_e = -1;
     float picked = 0.f;
+    sel_w = 0.f;
+    sel_e = -1;
     for (int r = 0; r < k; ++r) {
         float bv = -1.f;
         int be = 0x7fffffff;
-        for (int i = 0; i < per; ++i) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
             const int e = i * 32 + lane;
             if (v[i] > bv) { bv = v[i]; be = e; }       // ascending e inside the lane: ties keep the lower id
         }
@@ -62,39 +69,89 @@ __global__ void route_count_kernel(const float* __restrict__ logits, int ld, int
             const int oe = __shfl_xor_sync(0xffffffffu, be, o);
             if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
         }
-        if ((be & 31) == lane) v[be >> 5] = -1.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (i * 32 + lane == be) v[i] = -1.f;
         if (lane == r) { sel_w = bv; sel_e = be; }
         picked += bv;
     }
-    if (lane < k) {
-        const float w = renorm ? sel_w / picked : sel_w / sum;
-        ids[t * k + lane] = sel_e;
-        wts[t * k + lane] = w;
-        const int le = sel_e - e0;
-        pos[t * k + lane] = (le >= 0 && le < n_local) ? atomicAdd(&counts[le], 1) : -1;
-    }
-    if (lane == 0) sg[t] = sigmoidf_(row[E]);
+    sel_w = renorm ? sel_w / picked : sel_w / sum;
 }
 
-__global__ void scan_tasks_kernel(int* __restrict__ counts, int n_local, int ns, int T, int bn,
-                                  int* __restrict__ offsets, int4* __restrict__ tasks, int* __restrict__ meta, int max_tasks) {
-    // meta[0] = number of tasks, meta[1] = number of rows
-    if (threadIdx.x != 0) return;
-    int row = 0, nt = 0;
-    const int ne = n_local + ns;
-    for (int e = 0; e < ne; ++e) {
-        const int c = e < n_local ? counts[e] : T;
-        offsets[e] = row;
-        for (int r = 0; r < c; r += bn) {
-            if (nt < max_tasks) tasks[nt] = make_int4(e, row + r, min(bn, c - r), 0);
-            ++nt;
-        }
-        row += c;
-        if (e < n_local) counts[e] = 0;
+template <int PER>
+__global__ void route_count_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E,
+                                   int k, int renorm, int e0, int n_local, int* __restrict__ ids, float* __restrict__ wts,
+                                   float* __restrict__ sg, int* __restrict__ counts, int* __restrict__ pos) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float w, gl;
+    int e;
+    warp_topk<PER>(logits + static_cast<long long>(t) * ld, part_stride, n_parts, E, k, renorm, lane, w, e, gl);
+    if (lane < k) {
+        ids[t * k + lane] = e;
+        wts[t * k + lane] = w;
+        const int le = e - e0;
+        pos[t * k + lane] = (le >= 0 && le < n_local) ? atomicAdd(&counts[le], 1) : -1;
     }
-    meta[0] = min(nt, max_tasks);
-    meta[1] = row;
-    meta[2] = nt;          // > max_tasks would mean the host bound was wrong; the host checks in debug runs
+    if (lane == 0) sg[t] = sigmoidf_(gl);
+}
+
+// Inclusive scan of two integers across the block (1024 threads), fixed order.
+__device__ __forceinline__ void block_scan2(int& a, int& b, int* sa, int* sb) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int ta = __shfl_up_sync(0xffffffffu, a, o), tb = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) { a += ta; b += tb; }
+    }
+    if (lane == 31) { sa[warp] = a; sb[warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        int wa = sa[lane], wb = sb[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int ta = __shfl_up_sync(0xffffffffu, wa, o), tb = __shfl_up_sync(0xffffffffu, wb, o);
+            if (lane >= o) { wa += ta; wb += tb; }
+        }
+        sa[lane] = wa; sb[lane] = wb;
+    }
+    __syncthreads();
+    if (warp > 0) { a += sa[warp - 1]; b += sb[warp - 1]; }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024, 1)
+scan_tasks_kernel(int* __restrict__ counts, int n_local, int ns, int T, int bn,
+                  int* __restrict__ offsets, int4* __restrict__ tasks, int* __restrict__ meta, int max_tasks) {
+    // meta[0] = number of tasks, meta[1] = number of rows, meta[2] = tasks wanted (> max_tasks means the host bound was wrong)
+    __shared__ int sa[32], sb[32];
+    const int ne = n_local + ns;
+    int carry_rows = 0, carry_tasks = 0;
+    for (int base = 0; base < ne; base += 1024) {
+        const int e = base + threadIdx.x;
+        const int c = e < ne ? (e < n_local ? counts[e] : T) : 0;
+        const int nt = (c + bn - 1) / bn;
+        int ic = c, it = nt;
+        block_scan2(ic, it, sa, sb);
+        const int row_off = carry_rows + ic - c, task_off = carry_tasks + it - nt;
+        if (e < ne) {
+            offsets[e] = row_off;
+            for (int r = 0; r < nt; ++r)
+                if (task_off + r < max_tasks)
+                    tasks[task_off + r] = make_int4(e, row_off + r * bn, min(bn, c - r * bn), row_off + r * bn);
+            if (e < n_local) counts[e] = 0;
+        }
+        carry_rows += sa[31];
+        carry_tasks += sb[31];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        meta[0] = min(carry_tasks, max_tasks);
+        meta[1] = carry_rows;
+        meta[2] = carry_tasks;
+    }
 }
 
 __global__ void scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const int* __restrict__ offsets,
@@ -114,14 +171,127 @@ __global__ void scatter_rows_kernel(const int* __restrict__ ids, const int* __re
     if (row >= 0) row_token[row] = t;
 }
 
-void moe_route(const float* logits, int ld, int T, int E, int k, bool renorm, int e0, int n_local, int ns, int bn,
-               int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks, int* meta, int max_tasks,
-               int* row_token, int* slot_row, cudaStream_t s) {
+// T <= 16 rows, n_local <= 1024 experts, one CTA of 1024 threads.
+template <int PER>
+__global__ void __launch_bounds__(1024, 1)
+route_small_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k, int renorm,
+                   int e0, int n_local, int ns, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sg,
+                   int4* __restrict__ tasks_up, int4* __restrict__ tasks_down, int* __restrict__ meta, int* __restrict__ slot_row) {
+    extern __shared__ float lg[];              // [T][E + 1] logits with their K-range partials added
+    __shared__ int present[1024];
+    __shared__ int index_of[1024];
+    __shared__ int sa[32], sb[32];
+    __shared__ int sel[16 * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    present[threadIdx.x] = 0;
+    // all partial loads of an element are issued together, then added in ascending part order
+    for (int i = threadIdx.x; i < T * (E + 1); i += blockDim.x) {
+        const int t = i / (E + 1), e = i % (E + 1);
+        const float* src = logits + static_cast<long long>(t) * ld + e;
+        float a;
+        if (n_parts == 8) {
+            float p[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) p[u] = src[u * part_stride];
+            a = p[0];
+#pragma unroll
+            for (int u = 1; u < 8; ++u) a += p[u];
+        } else {
+            a = src[0];
+            for (int u = 1; u < n_parts; ++u) a += src[u * part_stride];
+        }
+        lg[i] = a;
+    }
+    __syncthreads();
+    if (warp < T) {
+        float w, gl;
+        int e;
+        warp_topk<PER>(lg + warp * (E + 1), 0, 1, E, k, renorm, lane, w, e, gl);
+        if (lane < k) {
+            ids[warp * k + lane] = e;
+            wts[warp * k + lane] = w;
+            sel[warp * 32 + lane] = e;
+            const int le = e - e0;
+            if (le >= 0 && le < n_local) present[le] = 1;
+        }
+        if (lane == 0) sg[warp] = sigmoidf_(gl);
+    }
+    __syncthreads();
+    const int mine = threadIdx.x < n_local ? present[threadIdx.x] : 0;
+    int inc = mine, dummy = 0;
+    block_scan2(inc, dummy, sa, sb);
+    const int n_active = sa[31];
+    const int idx = inc - mine;
+    index_of[threadIdx.x] = idx;
+    if (mine) {
+        tasks_up[idx] = make_int4(threadIdx.x, 0, T, idx * 16);
+        tasks_down[idx] = make_int4(threadIdx.x, idx * 16, T, idx * 16);
+    }
+    if (threadIdx.x < ns) {
+        const int i = n_active + threadIdx.x;
+        tasks_up[i] = make_int4(n_local + threadIdx.x, 0, T, i * 16);
+        tasks_down[i] = make_int4(n_local + threadIdx.x, i * 16, T, i * 16);
+    }
+    if (threadIdx.x == 0) {
+        meta[0] = n_active + ns;
+        meta[1] = (n_active + ns) * 16;
+        meta[2] = n_active + ns;
+    }
+    __syncthreads();
+    const int slots = k + ns;
+    for (int i = threadIdx.x; i < T * slots; i += blockDim.x) {
+        const int t = i / slots, j = i % slots;
+        int row = -1;
+        if (j < k) {
+            const int le = sel[t * 32 + j] - e0;
+            if (le >= 0 && le < n_local) row = index_of[le] * 16 + t;
+        } else {
+            row = (n_active + (j - k)) * 16 + t;
+        }
+        slot_row[i] = row;
+    }
+}
+
+template <int PER>
+static void route_large(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
+                        int n_local, int* ids, float* wts, float* sg, int* counts, int* pos, cudaStream_t s) {
     const int wpb = 4;
-    route_count_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>(logits, ld, T, E, k, renorm ? 1 : 0, e0, n_local, ids, wts, sg, counts, pos);
-    scan_tasks_kernel<<<1, 32, 0, s>>>(counts, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
+    route_count_kernel<PER><<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>(logits, part_stride, n_parts, ld, T, E, k, renorm ? 1 : 0, e0,
+                                                                     n_local, ids, wts, sg, counts, pos);
+}
+
+const char* moe_route(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
+                      int n_local, int ns, int bn, int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks,
+                      int* meta, int max_tasks, int* row_token, int* slot_row, cudaStream_t s) {
+    if (E > 1024 || k > 32) return "router supports up to 1024 experts and top-32";
+    if (E <= 128) route_large<4>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
+    else if (E <= 512) route_large<16>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
+    else route_large<32>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
+    scan_tasks_kernel<<<1, 1024, 0, s>>>(counts, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
     const int total = T * (k + ns);
     scatter_rows_kernel<<<(total + 255) / 256, 256, 0, s>>>(ids, pos, offsets, T, k, ns, e0, n_local, row_token, slot_row);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "route launch failed";
+}
+
+const char* moe_route_small(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
+                            int n_local, int ns, int* ids, float* wts, float* sg, int* tasks_up, int* tasks_down, int* meta,
+                            int* slot_row, cudaStream_t s) {
+    if (T > 16 || n_local > 1024 || E > 1024 || k > 32 || ns > 32) return "route_small handles up to 16 rows and 1024 experts";
+    int4* tu = reinterpret_cast<int4*>(tasks_up);
+    int4* td = reinterpret_cast<int4*>(tasks_down);
+    const int rn = renorm ? 1 : 0;
+    const size_t sm = static_cast<size_t>(T) * (E + 1) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(route_small_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1025 * 4);
+        cudaFuncSetAttribute(route_small_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1025 * 4);
+        cudaFuncSetAttribute(route_small_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1025 * 4);
+        configured = true;
+    }
+    if (E <= 128) route_small_kernel<4><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    else if (E <= 512) route_small_kernel<16><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    else route_small_kernel<32><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "route_small launch failed";
 }
 
 }  // namespace vade

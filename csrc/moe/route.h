@@ -4,11 +4,18 @@
 
 namespace vade {
 
-// logits fp32 [T][ld] with E router columns followed by the shared-expert gate column.
+// logits fp32 [n_parts][T][ld] (K-range partials, added in ascending order) with E router columns
+// followed by the shared-expert gate column.
 // Outputs: ids/wts [T][k], sg [T], tasks int4 [max_tasks], meta {tasks, rows, tasks wanted},
 // row_token [rows], slot_row [T][k + ns].  counts [n_local] must be zero on entry and is zero on exit.
-void moe_route(const float* logits, int ld, int T, int E, int k, bool renorm, int e0, int n_local, int ns, int bn,
-               int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks, int* meta, int max_tasks,
-               int* row_token, int* slot_row, cudaStream_t s);
+const char* moe_route(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
+                      int n_local, int ns, int bn, int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks,
+                      int* meta, int max_tasks, int* row_token, int* slot_row, cudaStream_t s);
+
+// T <= 16: no gather; one task per active expert over all T rows.  tasks_up reads x rows [0, T),
+// tasks_down reads the 16-row block its gate/up task wrote; both write output block i * 16.
+const char* moe_route_small(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
+                            int n_local, int ns, int* ids, float* wts, float* sg, int* tasks_up, int* tasks_down, int* meta,
+                            int* slot_row, cudaStream_t s);
 
 }  // namespace vade

@@ -51,73 +51,112 @@ __global__ void rmsnorm_kernel(const TIn* __restrict__ x, const float* __restric
         h[row * ldh + h_off + i] = __float2bfloat16_rn(to_f32(x[row * H + i]) * inv * (1.f + w[i]));
 }
 
-// x += ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7));  h = norm(x) if w != nullptr
-__global__ void fold_add_norm_kernel(const float* __restrict__ parts, long long part_stride, int n_parts,
-                                     float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ h,
-                                     int H, float eps) {
+// x += ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7));  h = norm(x) if w != nullptr.
+// Each thread owns float4 pieces and issues the loads of all parts before it adds, so one row
+// costs about one memory round trip.
+template <int NP>
+__global__ void __launch_bounds__(kRowThreads)
+fold_add_norm_kernel(const float* __restrict__ parts, long long part_stride, float* __restrict__ x,
+                     const float* __restrict__ w, __nv_bfloat16* __restrict__ h, int H, float eps) {
     __shared__ float red[32];
     const long long row = blockIdx.x;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float* p = parts + row * H + i;
-        float s;
-        if (n_parts == 8) {
-            s = ((p[0] + p[part_stride]) + (p[2 * part_stride] + p[3 * part_stride]))
-              + ((p[4 * part_stride] + p[5 * part_stride]) + (p[6 * part_stride] + p[7 * part_stride]));
-        } else if (n_parts == 4) {
-            s = (p[0] + p[part_stride]) + (p[2 * part_stride] + p[3 * part_stride]);
-        } else if (n_parts == 2) {
-            s = p[0] + p[part_stride];
-        } else {
-            s = p[0];
+    for (int v = threadIdx.x; v < H / 4; v += blockDim.x) {
+        float4 p[NP];
+#pragma unroll
+        for (int i = 0; i < NP; ++i) p[i] = *reinterpret_cast<const float4*>(parts + i * part_stride + row * H + v * 4);
+        float4 xv = *reinterpret_cast<const float4*>(x + row * H + v * 4);
+        float s[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float t[NP];
+#pragma unroll
+            for (int i = 0; i < NP; ++i) t[i] = reinterpret_cast<const float*>(&p[i])[c];
+#pragma unroll
+            for (int n = NP; n > 1; n >>= 1)
+#pragma unroll
+                for (int i = 0; i < n / 2; ++i) t[i] = t[2 * i] + t[2 * i + 1];
+            s[c] = t[0];
         }
-        const float v = x[row * H + i] + s;
-        x[row * H + i] = v;
-        ss += v * v;
+        xv.x += s[0]; xv.y += s[1]; xv.z += s[2]; xv.w += s[3];
+        *reinterpret_cast<float4*>(x + row * H + v * 4) = xv;
+        ss += xv.x * xv.x; ss += xv.y * xv.y; ss += xv.z * xv.z; ss += xv.w * xv.w;
     }
     if (w == nullptr) return;
     const float inv = rsqrtf(block_sum(ss, red) / H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-        h[row * H + i] = __float2bfloat16_rn(x[row * H + i] * inv * (1.f + w[i]));
+    for (int v = threadIdx.x; v < H / 4; v += blockDim.x) {
+        const float4 xv = *reinterpret_cast<const float4*>(x + row * H + v * 4);
+        const float4 wv = *reinterpret_cast<const float4*>(w + v * 4);
+        __nv_bfloat162 a = __floats2bfloat162_rn(xv.x * inv * (1.f + wv.x), xv.y * inv * (1.f + wv.y));
+        __nv_bfloat162 b = __floats2bfloat162_rn(xv.z * inv * (1.f + wv.z), xv.w * inv * (1.f + wv.w));
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&a);
+        o.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(h + row * H + v * 4) = o;
+    }
 }
 
 // x[t] += sum over the token's slots in ascending expert id of weight * y[row_of(t, slot)], then the
 // shared virtual experts (ids above every routed id) in order; h = norm(x) if w != nullptr.
 // y is bf16 [rows][H]; slot_row[t][slot] gives the row of y (or -1 if the slot is not present).
-__global__ void combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_row,
-                                        const int* __restrict__ ids, const float* __restrict__ wts, const float* __restrict__ sg,
-                                        int k, int ns, float* __restrict__ x, const float* __restrict__ w,
-                                        __nv_bfloat16* __restrict__ h, int H, float eps) {
+// Lanes of warp 0 rank the routed slots by expert id in parallel; every thread then owns 8
+// contiguous columns and loads all slots' pieces before the ordered adds.
+constexpr int kMaxSlots = 32;
+__global__ void __launch_bounds__(kRowThreads)
+combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_row,
+                        const int* __restrict__ ids, const float* __restrict__ wts, const float* __restrict__ sg,
+                        int k, int ns, float* __restrict__ x, const float* __restrict__ w,
+                        __nv_bfloat16* __restrict__ h, int H, float eps) {
     __shared__ float red[32];
-    __shared__ int order[64];
-    __shared__ float ow[64];
-    __shared__ int orow[64];
+    __shared__ float ow[kMaxSlots];
+    __shared__ int orow[kMaxSlots];
     const long long t = blockIdx.x;
     const int slots = k + ns;
-    if (threadIdx.x == 0) {
-        // insertion sort of the k routed slots by expert id (ids are distinct per token)
-        for (int j = 0; j < k; ++j) order[j] = j;
-        for (int a = 1; a < k; ++a) {
-            const int cur = order[a];
-            const int key = ids[t * k + cur];
-            int b = a - 1;
-            while (b >= 0 && ids[t * k + order[b]] > key) { order[b + 1] = order[b]; --b; }
-            order[b + 1] = cur;
-        }
-        for (int j = 0; j < k; ++j) { ow[j] = wts[t * k + order[j]]; orow[j] = slot_row[t * slots + order[j]]; }
-        for (int j = 0; j < ns; ++j) { ow[k + j] = sg[t]; orow[k + j] = slot_row[t * slots + k + j]; }
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const int id = lane < k ? ids[t * k + lane] : 0x7fffffff;
+        const float wt = lane < k ? wts[t * k + lane] : (lane < slots ? sg[t] : 0.f);
+        const int r = lane < slots ? slot_row[t * slots + lane] : -1;
+        int rank = 0;
+        for (int j = 0; j < k; ++j) rank += (__shfl_sync(0xffffffffu, id, j) < id) ? 1 : 0;
+        if (lane < k) { ow[rank] = wt; orow[rank] = r; }
+        else if (lane < slots) { ow[lane] = wt; orow[lane] = r; }
     }
     __syncthreads();
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < slots; ++j) {
-            const int r = orow[j];
-            if (r >= 0) acc += ow[j] * __bfloat162float(y[static_cast<long long>(r) * H + i]);
+    for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+        for (int j0 = 0; j0 < slots; j0 += 4) {
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int r = j0 + u < slots ? orow[j0 + u] : -1;
+                q[u] = r >= 0 ? *reinterpret_cast<const uint4*>(y + static_cast<long long>(r) * H + v * 8) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (j0 + u < slots && orow[j0 + u] >= 0) {
+                    const float wj = ow[j0 + u];
+                    const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 f = __bfloat1622float2(pp[c]);
+                        acc[2 * c] += wj * f.x;
+                        acc[2 * c + 1] += wj * f.y;
+                    }
+                }
+            }
         }
-        const float v = x[t * H + i] + acc;
-        x[t * H + i] = v;
-        ss += v * v;
+        float* xp = x + t * H + v * 8;
+        float4 a = *reinterpret_cast<float4*>(xp), b = *reinterpret_cast<float4*>(xp + 4);
+        a.x += acc[0]; a.y += acc[1]; a.z += acc[2]; a.w += acc[3];
+        b.x += acc[4]; b.y += acc[5]; b.z += acc[6]; b.w += acc[7];
+        *reinterpret_cast<float4*>(xp) = a;
+        *reinterpret_cast<float4*>(xp + 4) = b;
+        ss += a.x * a.x; ss += a.y * a.y; ss += a.z * a.z; ss += a.w * a.w;
+        ss += b.x * b.x; ss += b.y * b.y; ss += b.z * b.z; ss += b.w * b.w;
     }
     if (w == nullptr) return;
     const float inv = rsqrtf(block_sum(ss, red) / H + eps);
@@ -135,6 +174,30 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// mid[r][f] = bf16( silu(g) * u ),  g / u = bf16 roundings of the scaled ascending sums of the fp32
+// K-range partials of interleaved gate/up rows (column 2f = gate, 2f + 1 = up).
+__global__ void swiglu_fold_kernel(const float* __restrict__ parts, long long part_stride, int n_parts,
+                                   const int* __restrict__ n_rows, __nv_bfloat16* __restrict__ mid, int I) {
+    const int r = blockIdx.x;
+    if (r >= *n_rows) return;
+    for (int f = threadIdx.x; f < I; f += blockDim.x) {
+        const float2* p = reinterpret_cast<const float2*>(parts + static_cast<long long>(r) * 2 * I) + f;
+        float2 a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = i < n_parts ? p[i * (part_stride / 2)] : make_float2(0.f, 0.f);
+        float g = a[0].x, u = a[0].y;
+#pragma unroll
+        for (int i = 1; i < 8; ++i) if (i < n_parts) { g += a[i].x; u += a[i].y; }
+        g = bf16_round(g);
+        u = bf16_round(u);
+        mid[static_cast<long long>(r) * I + f] = __float2bfloat16_rn(siluf_(g) * u);
+    }
+}
+
+void swiglu_fold(const float* parts, long long part_stride, int n_parts, const int* n_rows, void* mid, int max_rows, int I, cudaStream_t s) {
+    swiglu_fold_kernel<<<max_rows, 256, 0, s>>>(parts, part_stride, n_parts, n_rows, static_cast<__nv_bfloat16*>(mid), I);
+}
+
 void embed(const void* table, const long long* tokens, float* x, int rows, int H, cudaStream_t s) {
     embed_kernel<<<rows, kRowThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(table), tokens, x, H);
 }
@@ -146,7 +209,13 @@ void rmsnorm(const void* x, bool x_is_bf16, const float* w, void* h, int rows, i
 }
 void fold_add_norm(const float* parts, long long part_stride, int n_parts, float* x, const float* w, void* h,
                    int rows, int H, float eps, cudaStream_t s) {
-    fold_add_norm_kernel<<<rows, kRowThreads, 0, s>>>(parts, part_stride, n_parts, x, w, static_cast<__nv_bfloat16*>(h), H, eps);
+    __nv_bfloat16* hb = static_cast<__nv_bfloat16*>(h);
+    switch (n_parts) {
+        case 1: fold_add_norm_kernel<1><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
+        case 2: fold_add_norm_kernel<2><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
+        case 4: fold_add_norm_kernel<4><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
+        default: fold_add_norm_kernel<8><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
+    }
 }
 void combine_add_norm(const void* y, const int* slot_row, const int* ids, const float* wts, const float* sg, int k, int ns,
                       float* x, const float* w, void* h, int rows, int H, float eps, cudaStream_t s) {

@@ -40,8 +40,7 @@ class HybridModel:
             parts = ops.linear_ranges(mixed, lw.out_proj, self.r_local, phase=ph)
         parts = comm.gather_partials(parts)
         x, h2 = ops.fold_add_norm(parts, x, lw.post_norm)
-        logits = ops.linear(h2, lw.moe.router, out_fp32=True, phase=ph)
-        routing = ops.route(logits, lw.moe)
+        routing = ops.route(h2, lw.moe, ph)
         pair_out, owned = ops.moe_experts(lw.moe, h2, routing, phase=ph)
         pair_out = comm.gather_pairs(pair_out, owned)
         return ops.combine_add_norm(pair_out, routing, x, next_norm)

@@ -118,9 +118,14 @@ class RefOps:
         return R._round((o * torch.sigmoid(gate)).reshape(T, nq * hd), self.act)
 
     # ---- MoE
-    def route(self, logits, mw):
+    def route(self, h, mw, phase: str = "prefill"):
+        return self.route_logits(self.linear(h, mw.router, out_fp32=True), mw)
+
+    def route_logits(self, logits, mw, n_parts: int = 1):
         """Routing of every row: ids [T, k] (descending probability), weights, shared-expert gate."""
         cfg = self.cfg
+        if n_parts > 1:
+            logits = logits.sum(0)
         E = cfg.num_experts
         ids, w = R.route_topk(logits[:, :E], cfg.num_experts_per_tok, cfg.norm_topk_prob)
         return SimpleNamespace(ids=ids, wts=w, sg=torch.sigmoid(logits[:, E].float()))

@@ -74,10 +74,25 @@ class CudaOps:
         self.ext.rmsnorm(x, w, out, self.cfg.rms_norm_eps, out.stride(0), off)
         return out
 
+    #: decode-class column-parallel products are cut into this many K ranges (more CTAs in flight for
+    #: few rows); their consumers add the fp32 partials in ascending order.  The split depends on the
+    #: arithmetic class only, never on the number of rows, so a chat's bits do not depend on its batch.
+    DECODE_PARTS = 4
+
     def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
         T = h.shape[0]
+        if phase == "decode" and not out_fp32 and q.k % (self.DECODE_PARTS * 64) == 0:
+            return self.linear_parts(h, q, self.DECODE_PARTS)
         out = torch.empty(T, q.n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=self.device)
         self._gemm(h, q, out, 1 if out_fp32 else 0, _bn_for(T), 1, T, q.n, 0)
+        return out
+
+    def linear_parts(self, h, q, ranges: int):
+        """fp32 K-range partials [ranges, T, n] of a matrix whose consumer adds them itself (decode
+        class: more CTAs in flight for a one-row pass)."""
+        T = h.shape[0]
+        out = torch.empty(ranges, T, q.n, dtype=torch.float32, device=self.device)
+        self._gemm(h, q, out, 1, _bn_for(T), ranges, T, q.n, T * q.n)
         return out
 
     def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
@@ -98,7 +113,7 @@ class CudaOps:
         d = self._dev(batch)
         vh = lw.a_log.shape[0]
         kh = vh * cfg.linear_num_key_heads // cfg.linear_num_value_heads
-        out = torch.empty(proj.shape[0], vh * cfg.linear_value_head_dim, dtype=torch.bfloat16, device=self.device)
+        out = torch.empty(proj.shape[-2], vh * cfg.linear_value_head_dim, dtype=torch.bfloat16, device=self.device)
         self.launches += 1
         self.ext.gdn_scan(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
                           d["seq_slot"], d["seq_start"], len(batch.seq_slots), out, kh, vh, cfg.linear_key_head_dim,
@@ -111,11 +126,12 @@ class CudaOps:
         hd = cfg.head_dim
         kp, vp = cache.k_pages[layer], cache.v_pages[layer]
         nkv = kp.shape[2]
-        nq = (qkv.shape[1] - 2 * nkv * hd) // (2 * hd)
-        T = qkv.shape[0]
+        nq = (qkv.shape[-1] - 2 * nkv * hd) // (2 * hd)
+        T = qkv.shape[-2]
         q = torch.empty(T, nq, hd, dtype=torch.bfloat16, device=self.device)
-        self.ext.attn_prep(qkv, nq, nkv, hd, lw.q_norm, lw.k_norm, d["positions"], d["row_slot"], cache.block_table, q, kp, vp,
-                           cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_norm_eps)
+        gate = torch.empty(T, nq, hd, dtype=torch.bfloat16, device=self.device)
+        self.ext.attn_prep(qkv, nq, nkv, hd, lw.q_norm, lw.k_norm, d["positions"], d["row_slot"], cache.block_table, q, gate,
+                           kp, vp, cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_norm_eps)
         out = torch.empty(T, nq * hd, dtype=torch.bfloat16, device=self.device)
         split = batch.phase == "decode"
         partial, n_split = None, 1
@@ -123,42 +139,74 @@ class CudaOps:
             n_split = -(-d["max_len"] // self.ext.attn_split_keys())
             partial = torch.empty(T * nq * n_split * (hd + 2), dtype=torch.float32, device=self.device)
         self.launches += 3 if split else 2
-        self.ext.attn_rows(q, qkv, kp, vp, d["positions"], d["row_slot"], cache.block_table, nq, nkv, hd, split, partial, n_split, out)
+        self.ext.attn_rows(q, gate, kp, vp, d["positions"], d["row_slot"], cache.block_table, nq, nkv, hd, split, partial, n_split, out)
         return out
 
     # ---- MoE
-    def route(self, logits, mw):
+    def route(self, h, mw, phase: str = "prefill"):
+        """Router product + top-k + the row layout of the grouped GEMM."""
+        T = h.shape[0]
+        if phase == "decode" and T <= 16 and mw.router.k % (8 * 64) == 0:
+            return self.route_logits(self.linear_parts(h, mw.router, 8), mw, 8)
+        return self.route_logits(self.linear(h, mw.router, out_fp32=True), mw, 1)
+
+    def route_logits(self, logits, mw, n_parts: int = 1):
         cfg = self.cfg
-        T = logits.shape[0]
+        T = logits.shape[-2]
         k, ns, E = cfg.num_experts_per_tok, mw.n_shared, cfg.num_experts
-        bn = 16 if T <= 16 else (32 if T <= 64 else 64)
         slots = k + ns
-        max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
-        max_rows = T * slots
         dev, i32 = self.device, torch.int32
+        r = SimpleNamespace(
+            ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
+            sg=torch.empty(T, dtype=torch.float32, device=dev), meta=torch.zeros(4, dtype=i32, device=dev),
+            slot_row=torch.empty(T, slots, dtype=i32, device=dev), T=T, k=k, ns=ns)
+        if T <= 16:
+            # small pass: one task per active expert over all T rows, no gather
+            r.small, r.bn = True, 16
+            r.max_tasks = min(mw.n_local, T * k) + ns
+            r.max_rows = r.max_tasks * 16
+            r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
+            r.tasks_down = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
+            self.launches += 1
+            self.ext.moe_route_small(logits, n_parts, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, r.ids, r.wts, r.sg,
+                                     r.tasks, r.tasks_down, r.meta, r.slot_row)
+            return r
+        r.small = False
+        r.bn = bn = 32 if T <= 64 else 64
+        r.max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
+        r.max_rows = T * slots
         counts = self._moe_ws.get((mw.n_local, "counts"))
         if counts is None:
             counts = self._moe_ws[(mw.n_local, "counts")] = torch.zeros(max(1, mw.n_local), dtype=i32, device=dev)
-        r = SimpleNamespace(
-            ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
-            sg=torch.empty(T, dtype=torch.float32, device=dev), pos=torch.empty(T, k, dtype=i32, device=dev),
-            offsets=torch.empty(mw.n_local + ns, dtype=i32, device=dev), tasks=torch.empty(max_tasks, 4, dtype=i32, device=dev),
-            meta=torch.zeros(4, dtype=i32, device=dev), row_token=torch.empty(max_rows, dtype=i32, device=dev),
-            slot_row=torch.empty(T, slots, dtype=i32, device=dev), bn=bn, max_tasks=max_tasks, max_rows=max_rows, T=T, k=k, ns=ns)
+        r.pos = torch.empty(T, k, dtype=i32, device=dev)
+        r.offsets = torch.empty(mw.n_local + ns, dtype=i32, device=dev)
+        r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
+        r.tasks_down = r.tasks
+        r.row_token = torch.empty(r.max_rows, dtype=i32, device=dev)
         self.launches += 3
-        self.ext.moe_route(logits, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, bn, r.ids, r.wts, r.sg, counts, r.pos,
-                           r.offsets, r.tasks, r.meta, max_tasks, r.row_token, r.slot_row)
+        self.ext.moe_route(logits, n_parts, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, bn, r.ids, r.wts, r.sg, counts,
+                           r.pos, r.offsets, r.tasks, r.meta, r.max_tasks, r.row_token, r.slot_row)
         return r
 
     def moe_experts(self, mw, h, r, phase: str = "prefill"):
         H, I2 = mw.down.n, mw.gate_up.n
-        xs = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
-        self.launches += 1
-        self.ext.gather_rows(h, r.row_token, r.meta, xs, r.max_rows)
+        if r.small:
+            xs = h
+        else:
+            xs = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
+            self.launches += 1
+            self.ext.gather_rows(h, r.row_token, r.meta, xs, r.max_rows)
         mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
-        self._gemm(xs, mw.gate_up, mid, 2, r.bn, 1, r.max_rows, I2 // 2, 0, r.tasks, r.meta, r.max_tasks)
+        P = self.DECODE_PARTS
+        if phase == "decode" and mw.gate_up.k % (P * 64) == 0:
+            gu = torch.empty(P, r.max_rows, I2, dtype=torch.float32, device=self.device)
+            self._gemm(xs, mw.gate_up, gu, 1, r.bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks)
+            self.launches += 1
+            self.ext.swiglu_fold(gu, r.meta, mid)
+        else:
+            self._gemm(xs, mw.gate_up, mid, 2, r.bn, 1, r.max_rows, I2 // 2, 0, r.tasks, r.meta, r.max_tasks)
         y = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
-        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks, r.meta, r.max_tasks)
+        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks)
         if self.tp == 1:
             return y, None
         # dense [T, slots, H] layout for the exchange between expert-parallel ranks
