@@ -14,6 +14,8 @@
 #include <cfloat>
 #include "../common/ptx.cuh"
 #include "attn.h"
+#include "attn_static.h"
+#include <mutex>
 
 namespace vade {
 
@@ -260,3 +262,50 @@ const char* attn_rows(const void* q, const void* gate, const void* k_pages, cons
 int attn_split_keys() { return kSplit; }
 
 }  // namespace vade
+
+// ---------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (see attn_static.h): the split partials go to an array that
+// is part of the library image.  In host code the array's name is only a stand-in; the device
+// address comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) float vade_attn_static_scratch[VADE_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+
+// Device address of the static array on the current device (nullptr on failure).
+float* static_scratch_on_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, vade_attn_static_scratch) != cudaSuccess) return nullptr;
+        g_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    return g_scratch_addr[dev];
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default")))
+int vade_attn_decode_static(const void* q, const void* gate, const void* k_pages, const void* v_pages, const int* positions,
+                            const int* row_slot, const int* block_table, int max_pages, int rows, int nq, int nkv, int hd,
+                            int max_len, void* out, cudaStream_t stream) {
+    if (!q || !gate || !k_pages || !v_pages || !positions || !row_slot || !block_table || !out) return VADE_ATTN_STATIC_BAD_ARGUMENT;
+    if (rows <= 0 || nq <= 0 || nkv <= 0 || max_len <= 0 || max_pages <= 0) return VADE_ATTN_STATIC_BAD_ARGUMENT;
+    const int n_split = (max_len + vade::attn_split_keys() - 1) / vade::attn_split_keys();
+    const unsigned long long need = 1ull * rows * nq * n_split * (hd + 2);
+    if (need > VADE_ATTN_STATIC_SCRATCH_FLOATS) return VADE_ATTN_STATIC_TOO_LARGE;
+    float* scratch = static_scratch_on_current_device();
+    if (scratch == nullptr) return VADE_ATTN_STATIC_CUDA_ERROR;
+    const char* err = vade::attn_rows(q, gate, k_pages, v_pages, positions, row_slot, block_table, max_pages, rows, nq, nkv, hd,
+                                      true, scratch, n_split, out, stream);
+    if (err == nullptr) return VADE_ATTN_STATIC_OK;
+    return (hd != 256 || nq % nkv != 0 || nq / nkv > 16) ? VADE_ATTN_STATIC_BAD_ARGUMENT : VADE_ATTN_STATIC_CUDA_ERROR;
+}
+
+extern "C" __attribute__((visibility("default")))
+unsigned long long vade_attn_static_scratch_bytes(void) {
+    return 4ull * VADE_ATTN_STATIC_SCRATCH_FLOATS;
+}

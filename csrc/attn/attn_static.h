@@ -1,0 +1,46 @@
+// Decode attention for callers that must not allocate.  This entry point has no counterpart in
+// the reference engine; it exists for hosts of this library that cannot call cudaMalloc at the
+// point where they run a decode step: code running between the begin and end of a stream capture,
+// plug-ins whose memory is owned and budgeted by an outer runtime, and real-time loops that forbid
+// any call that may take the driver's allocator lock.
+//
+// vade_attn_decode_static() computes exactly what the split (decode-class) path of attn_rows()
+// computes, but the fp32 split partials {m, l, acc[256]} live in a fixed array that is part of the
+// library image instead of a caller-provided buffer:
+//
+//   * the array holds VADE_ATTN_STATIC_SCRATCH_FLOATS floats (8 MiB); every GPU that loads the
+//     library keeps that much device memory until the process exits;
+//   * a call needs rows * nq * ceil(max_len / 128) * 258 floats and is refused with
+//     VADE_ATTN_STATIC_TOO_LARGE when that exceeds the array (nothing is launched);
+//   * the first call on each device looks the array's device address up (a synchronous runtime
+//     query, done once per device with that device current); make that first call before any stream
+//     capture begins on the device;
+//   * all calls on a device share the one array: two calls whose kernels may overlap on the GPU
+//     (different streams without an ordering between them) race on it.  Calls on one stream are safe.
+//     The array keeps the previous call's contents; every word a call reads is written by that same
+//     call first, so nothing needs clearing.
+//
+// The function launches on `stream`, allocates nothing (no cudaMalloc/cudaFree, no library
+// routine that allocates), and returns 0 on success or one of the codes below.
+#pragma once
+#include <cuda_runtime.h>
+
+#define VADE_ATTN_STATIC_SCRATCH_FLOATS (2u * 1024u * 1024u)
+#define VADE_ATTN_STATIC_OK 0
+#define VADE_ATTN_STATIC_TOO_LARGE 1      // rows * nq * splits * 258 floats do not fit the array
+#define VADE_ATTN_STATIC_BAD_ARGUMENT 2   // null pointer, unsupported head dimension or GQA group
+#define VADE_ATTN_STATIC_CUDA_ERROR 3     // address lookup or launch failed; see cudaGetLastError()
+
+extern "C" {
+
+// q, gate: bf16 [rows][nq][hd]; k_pages, v_pages: bf16 [pages][64][nkv][hd]; positions, row_slot:
+// int32 [rows]; block_table: int32 [slots][max_pages]; out: bf16 [rows][nq * hd].
+// max_len: the largest (position + 1) among the rows; it sizes the split grid.
+int vade_attn_decode_static(const void* q, const void* gate, const void* k_pages, const void* v_pages, const int* positions,
+                            const int* row_slot, const int* block_table, int max_pages, int rows, int nq, int nkv, int hd,
+                            int max_len, void* out, cudaStream_t stream);
+
+// Bytes of device memory the static array occupies on every GPU that loads the library.
+unsigned long long vade_attn_static_scratch_bytes(void);
+
+}

@@ -1,0 +1,77 @@
+"""The allocation-free decode-attention entry point, called through its exported C symbol.
+
+Some hosts of this library cannot allocate device memory when they run a decode step (they are
+inside a stream capture, or an outer runtime owns and budgets all memory, or their loop forbids
+calls that take the allocator lock).  ``vade_attn_decode_static`` serves them: the split partials
+live in a fixed 8 MiB array inside the library instead of a caller-provided buffer.  This test
+drives it with ctypes and checks it against the ordinary entry point (which takes a scratch
+tensor) on two calls in a row, because the shared array keeps the first call's contents.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from vade_b200.ops import _ext
+    ext = _ext.load()
+    lib = ctypes.CDLL(_ext.so_path())
+    fn = lib.vade_attn_decode_static
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p, ctypes.c_void_p]
+    lib.vade_attn_static_scratch_bytes.restype = ctypes.c_ulonglong
+    return ext, lib, fn
+
+
+def _case(seed, rows, ctx, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    nq, nkv, hd, page = 8, 2, 256, 64
+    pages = rows * (-(-ctx // page)) + 1
+    mk = lambda *s: torch.randn(*s, device=dev, generator=g).to(torch.bfloat16)
+    q, gate = mk(rows, nq, hd), mk(rows, nq, hd)
+    kp, vp = mk(pages, page, nkv, hd), mk(pages, page, nkv, hd)
+    per = -(-ctx // page)
+    table = torch.arange(rows * per, dtype=torch.int32, device=dev).view(rows, per).contiguous()
+    positions = torch.tensor([ctx - 1 - 37 * r for r in range(rows)], dtype=torch.int32, device=dev)
+    row_slot = torch.arange(rows, dtype=torch.int32, device=dev)
+    return q, gate, kp, vp, positions, row_slot, table, nq, nkv, hd
+
+
+def test_static_scratch_entry_matches_ordinary_entry_twice():
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    ext, lib, fn = _lib()
+    assert lib.vade_attn_static_scratch_bytes() == 8 << 20
+    stream = torch.cuda.current_stream().cuda_stream
+    for seed, rows, ctx in ((1, 3, 700), (2, 2, 333)):       # second call reuses the array after a different shape
+        q, gate, kp, vp, positions, row_slot, table, nq, nkv, hd = _case(seed, rows, ctx, dev)
+        n_split = -(-ctx // ext.attn_split_keys())
+        want = torch.empty(rows, nq * hd, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(rows * nq * n_split * (hd + 2), dtype=torch.float32, device=dev)
+        ext.attn_rows(q, gate, kp, vp, positions, row_slot, table, nq, nkv, hd, True, scratch, n_split, want)
+        got = torch.full_like(want, float("nan"))
+        rc = fn(q.data_ptr(), gate.data_ptr(), kp.data_ptr(), vp.data_ptr(), positions.data_ptr(), row_slot.data_ptr(),
+                table.data_ptr(), table.shape[1], rows, nq, nkv, hd, ctx, got.data_ptr(), stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all()
+        assert torch.allclose(got.float(), want.float(), rtol=3e-2, atol=1e-2)
+
+
+def test_static_scratch_entry_rejects_oversized_and_bad_calls():
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    ext, lib, fn = _lib()
+    q, gate, kp, vp, positions, row_slot, table, nq, nkv, hd = _case(3, 2, 200, dev)
+    out = torch.empty(2, nq * hd, dtype=torch.bfloat16, device=dev)
+    args = [q.data_ptr(), gate.data_ptr(), kp.data_ptr(), vp.data_ptr(), positions.data_ptr(), row_slot.data_ptr(),
+            table.data_ptr(), table.shape[1]]
+    stream = torch.cuda.current_stream().cuda_stream
+    # 64 rows x 8 heads at a 1M-token context needs far more than 8 MiB of partials: refused, nothing runs
+    assert fn(*args, 64, nq, nkv, hd, 1 << 20, out.data_ptr(), stream) == 1
+    assert fn(*args, 2, nq, nkv, 128, 200, out.data_ptr(), stream) == 2
+    assert fn(None, *args[1:], 2, nq, nkv, hd, 200, out.data_ptr(), stream) == 2
+    torch.cuda.synchronize()
