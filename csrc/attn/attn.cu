@@ -201,23 +201,158 @@ attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
     }
 }
 
-__global__ void attn_merge_kernel(const float* __restrict__ partial, int n_split, const int* __restrict__ positions,
-                                  const __nv_bfloat16* __restrict__ gate_buf, int nq, __nv_bfloat16* __restrict__ out) {
-    const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+// Decode-class split: one CTA per (row, kv head, 128-key split).  The split's K and V rows are staged in
+// shared memory with 16-byte asynchronous copies that are all in flight at once (one memory round
+// trip per split), then each warp (= one query head of the group) visits the keys in the same fixed
+// order as attn_rows_kernel: ascending groups of 32, lane j scoring key j, one butterfly per group.
+constexpr int kKStride = kHD + 8;          // padded K row (elements): conflict-free 16-byte reads down a column of rows
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(512)
+attn_split_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                  const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ positions,
+                  const int* __restrict__ row_slot, const int* __restrict__ block_table, int max_pages, int nq, int nkv,
+                  float scale, float* __restrict__ partial, int n_split) {
+    extern __shared__ __align__(16) uint8_t smem_attn[];
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_attn);                  // [128][264]
+    __nv_bfloat16* Vs = Ks + kSplit * kKStride;                                       // [128][256]
+    float* q_s = reinterpret_cast<float*>(Vs + kSplit * kHD);                         // [group][256]
+    const int row = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int group = nq / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = kvh * group + warp;
+    const int len = positions[row] + 1;
+    const int k0 = split * kSplit;
+    if (k0 >= len) return;
+    const int nk = min(kSplit, len - k0);
+    const int* table = block_table + static_cast<long long>(row_slot[row]) * max_pages;
+    const int page0 = table[k0 / kPage];
+    const int page1 = (nk > kPage) ? table[k0 / kPage + 1] : page0;
+    const long long row_stride = static_cast<long long>(nkv) * kHD;
+    for (int idx = threadIdx.x; idx < nk * (kHD / 8); idx += blockDim.x) {
+        const int key = idx >> 5, c = idx & 31;
+        const long long at = (static_cast<long long>(key < kPage ? page0 : page1) * kPage + (key & (kPage - 1))) * row_stride
+                           + static_cast<long long>(kvh) * kHD + c * 8;
+        cp_async16(Ks + key * kKStride + c * 8, k_pages + at);
+        cp_async16(Vs + key * kHD + c * 8, v_pages + at);
+    }
+    {
+        float qv[8];
+        unpack8(*reinterpret_cast<const uint4*>(q + (static_cast<long long>(row) * nq + head) * kHD + lane * 8), qv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q_s[warp * kHD + lane * 8 + i] = qv[i] * scale;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const float4* qs4 = reinterpret_cast<const float4*>(q_s + warp * kHD);
+    float m = -FLT_MAX, l = 0.f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int kb = 0; kb < nk; kb += 32) {
+        const bool live = kb + lane < nk;
+        float s = -FLT_MAX;
+        if (live) {
+            const uint4* kr = reinterpret_cast<const uint4*>(Ks + (kb + lane) * kKStride);
+            float s0 = 0.f, s1 = 0.f;              // even / odd 8-column pieces, joined once at the end
+#pragma unroll 8
+            for (int c = 0; c < kHD / 8; ++c) {
+                float kf[8];
+                unpack8(kr[c], kf);
+                const float4 qa = qs4[2 * c], qb = qs4[2 * c + 1];
+                float& t = (c & 1) ? s1 : s0;
+                t += qa.x * kf[0]; t += qa.y * kf[1]; t += qa.z * kf[2]; t += qa.w * kf[3];
+                t += qb.x * kf[4]; t += qb.y * kf[5]; t += qb.z * kf[6]; t += qb.w * kf[7];
+            }
+            s = s0 + s1;
+        }
+        float gm = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+        const float mn = fmaxf(m, gm);
+        const float corr = __expf(m - mn);
+        const float p = live ? __expf(s - mn) : 0.f;
+        float ps = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l = l * corr + ps;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        m = mn;
+        const int cnt = min(32, nk - kb);
+        const __nv_bfloat16* vr = Vs + kb * kHD + lane * 8;
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            if (j < cnt) {
+                float vf[8];
+                unpack8(*reinterpret_cast<const uint4*>(vr + j * kHD), vf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += pj * vf[i];
+            }
+        }
+    }
+    float* dst = partial + ((static_cast<long long>(row) * nq + head) * n_split + split) * (kHD + 2);
+    if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[2 + lane * 8 + i] = acc[i];
+}
+
+// Joins the split partials of one (row, head) in a fixed order: 1024 threads = 4 split classes
+// (s mod 4) x 256 dims; the four class sums are added as (c0 + c1) + (c2 + c3).
+__global__ void __launch_bounds__(1024)
+attn_merge_kernel(const float* __restrict__ partial, int n_split, const int* __restrict__ positions,
+                  const __nv_bfloat16* __restrict__ gate_buf, int nq, __nv_bfloat16* __restrict__ out) {
+    extern __shared__ float sm_merge[];            // e[n_split], then 32 reduction words, then 4 x 256 class sums
+    const int row = blockIdx.x, head = blockIdx.y;
+    const int tid = threadIdx.x, cls = tid >> 8, d = tid & 255, lane = tid & 31, warp = tid >> 5;
     const int used = (positions[row] + kSplit) / kSplit;          // ceil((pos + 1) / split)
     const float* src = partial + (static_cast<long long>(row) * nq + head) * n_split * (kHD + 2);
-    float M = -FLT_MAX;
-#pragma unroll 8
-    for (int s = 0; s < used; ++s) M = fmaxf(M, src[s * (kHD + 2)]);
-    float L = 0.f, o = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < used; ++s) {
-        const float e = __expf(src[s * (kHD + 2)] - M);
-        L += src[s * (kHD + 2) + 1] * e;
-        o += src[s * (kHD + 2) + 2 + d] * e;
+    float* e_s = sm_merge;
+    float* red = sm_merge + n_split;
+    float* cls_sum = red + 32;
+    // pass 1: block max of m_s
+    float mx = -FLT_MAX;
+    for (int s = tid; s < used; s += 1024) { const float v = src[s * (kHD + 2)]; e_s[s] = v; mx = fmaxf(mx, v); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    float M = red[0];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) M = fmaxf(M, red[i]);
+    __syncthreads();
+    // pass 2: weights e_s = exp(m_s - M) and L = sum_s l_s * e_s (thread-strided, then fixed tree)
+    float lp = 0.f;
+    for (int s = tid; s < used; s += 1024) { const float e = __expf(e_s[s] - M); e_s[s] = e; lp += src[s * (kHD + 2) + 1] * e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lp += __shfl_xor_sync(0xffffffffu, lp, o);
+    if (lane == 0) red[warp] = lp;
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) L += red[i];
+    // pass 3: weighted sum of the accumulators, splits of class cls in ascending order
+    float o = 0.f;
+    int s = cls;
+    for (; s + 28 < used; s += 32) {
+        float a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) a[u] = src[(s + 4 * u) * (kHD + 2) + 2 + d];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) o += a[u] * e_s[s + 4 * u];
     }
-    const float gate = __bfloat162float(gate_buf[(static_cast<long long>(row) * nq + head) * kHD + d]);
-    out[(static_cast<long long>(row) * nq + head) * kHD + d] = __float2bfloat16_rn(o / L * sigmoidf_(gate));
+    for (; s < used; s += 4) o += src[s * (kHD + 2) + 2 + d] * e_s[s];
+    cls_sum[cls * kHD + d] = o;
+    __syncthreads();
+    if (cls == 0) {
+        const float tot = (cls_sum[d] + cls_sum[kHD + d]) + (cls_sum[2 * kHD + d] + cls_sum[3 * kHD + d]);
+        const float gate = __bfloat162float(gate_buf[(static_cast<long long>(row) * nq + head) * kHD + d]);
+        out[(static_cast<long long>(row) * nq + head) * kHD + d] = __float2bfloat16_rn(tot / L * sigmoidf_(gate));
+    }
 }
 
 const char* attn_prep(const void* qkv, bool parts, int n_parts, long long part_stride, int ld, int rows, int nq, int nkv, int hd,
@@ -249,9 +384,19 @@ const char* attn_rows(const void* q, const void* gate, const void* k_pages, cons
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
     const size_t sm = group * kHD * sizeof(float);
     if (split) {
-        attn_rows_kernel<true><<<dim3(rows, nkv, n_split), group * 32, sm, s>>>(qp, gp, kp, vp, positions, row_slot, block_table,
-                                                                               max_pages, nq, nkv, scale, partial, n_split, o);
-        attn_merge_kernel<<<dim3(rows, nq), kHD, 0, s>>>(partial, n_split, positions, gp, nq, o);
+        const size_t sm_split = static_cast<size_t>(kSplit) * (kKStride + kHD) * 2 + sm;
+        const size_t sm_merge = (static_cast<size_t>(n_split) + 32 + 4 * kHD) * sizeof(float);
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+                cudaFuncSetAttribute(attn_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+                return "cannot raise shared memory limit";
+            configured = true;
+        }
+        if (sm_merge > 64 * 1024) return "context too long for the split merge";
+        attn_split_kernel<<<dim3(rows, nkv, n_split), group * 32, sm_split, s>>>(qp, kp, vp, positions, row_slot, block_table,
+                                                                                max_pages, nq, nkv, scale, partial, n_split);
+        attn_merge_kernel<<<dim3(rows, nq), 1024, sm_merge, s>>>(partial, n_split, positions, gp, nq, o);
     } else {
         attn_rows_kernel<false><<<dim3(rows, nkv, 1), group * 32, sm, s>>>(qp, gp, kp, vp, positions, row_slot, block_table,
                                                                           max_pages, nq, nkv, scale, partial, 1, o);

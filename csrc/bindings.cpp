@@ -73,7 +73,7 @@ void fold_add_norm(torch::Tensor parts, int64_t n_parts, int64_t part_stride, to
 
 void combine_add_norm(torch::Tensor y, torch::Tensor slot_row, torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, int64_t k,
                       int64_t ns, torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> h, double eps) {
-    need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 32 && x.size(1) % 8 == 0, "combine arguments");
+    need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 32 && x.size(1) % 8 == 0 && x.size(1) <= 8192, "combine arguments");
     c10::cuda::CUDAGuard guard(x.device());
     vade::combine_add_norm(y.data_ptr(), slot_row.data_ptr<int>(), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
                            static_cast<int>(k), static_cast<int>(ns), x.data_ptr<float>(), ptr<float>(w),
@@ -171,12 +171,16 @@ void swiglu_fold(torch::Tensor parts, torch::Tensor meta, torch::Tensor mid) {
                       static_cast<int>(parts.size(1)), static_cast<int>(mid.size(1)), stream_of(parts));
 }
 
-void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id) {
+void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id,
+                 c10::optional<torch::Tensor> chunk_val, c10::optional<torch::Tensor> chunk_idx) {
     need(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 && best_id.scalar_type() == torch::kInt64, "argmax arguments");
     c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t chunks = (logits.size(1) + vade::argmax_chunk() - 1) / vade::argmax_chunk();
+    const bool two = chunk_val.has_value() && chunk_idx.has_value() && chunk_val->numel() >= logits.size(0) * chunks &&
+                     chunk_idx->numel() >= logits.size(0) * chunks;
     vade::argmax_rows(logits.data_ptr<float>(), logits.stride(0), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
                       static_cast<int>(id0), best_val.data_ptr<float>(), reinterpret_cast<long long*>(best_id.data_ptr<int64_t>()),
-                      stream_of(logits));
+                      two ? chunk_val->data_ptr<float>() : nullptr, two ? chunk_idx->data_ptr<int>() : nullptr, stream_of(logits));
 }
 
 }  // namespace
@@ -196,4 +200,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attn_rows", &attn_rows);
     m.def("argmax_rows", &argmax_rows);
     m.def("attn_split_keys", &vade::attn_split_keys);
+    m.def("argmax_chunk", &vade::argmax_chunk);
 }

@@ -102,7 +102,7 @@ fold_add_norm_kernel(const float* __restrict__ parts, long long part_stride, flo
 // Lanes of warp 0 rank the routed slots by expert id in parallel; every thread then owns 8
 // contiguous columns and loads all slots' pieces before the ordered adds.
 constexpr int kMaxSlots = 32;
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(1024)
 combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_row,
                         const int* __restrict__ ids, const float* __restrict__ wts, const float* __restrict__ sg,
                         int k, int ns, float* __restrict__ x, const float* __restrict__ w,
@@ -123,20 +123,27 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restri
         else if (lane < slots) { ow[lane] = wt; orow[lane] = r; }
     }
     __syncthreads();
+    // one 8-column piece per thread (the launcher sizes the block to H / 8 threads); the piece stays in
+    // registers from the ordered adds through the norm, and the slots' loads go out eight at a time
+    const int v = threadIdx.x;
+    const bool mine = v < H / 8;
+    float xs8[8];
     float ss = 0.f;
-    for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    if (mine) {
         float acc[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-        for (int j0 = 0; j0 < slots; j0 += 4) {
-            uint4 q[4];
+        float* xp = x + t * H + v * 8;
+        const float4 xa = *reinterpret_cast<const float4*>(xp), xb = *reinterpret_cast<const float4*>(xp + 4);
+        for (int j0 = 0; j0 < slots; j0 += 8) {
+            uint4 q[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int r = j0 + u < slots ? orow[j0 + u] : -1;
                 q[u] = r >= 0 ? *reinterpret_cast<const uint4*>(y + static_cast<long long>(r) * H + v * 8) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 if (j0 + u < slots && orow[j0 + u] >= 0) {
                     const float wj = ow[j0 + u];
                     const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
@@ -149,19 +156,28 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restri
                 }
             }
         }
-        float* xp = x + t * H + v * 8;
-        float4 a = *reinterpret_cast<float4*>(xp), b = *reinterpret_cast<float4*>(xp + 4);
-        a.x += acc[0]; a.y += acc[1]; a.z += acc[2]; a.w += acc[3];
-        b.x += acc[4]; b.y += acc[5]; b.z += acc[6]; b.w += acc[7];
-        *reinterpret_cast<float4*>(xp) = a;
-        *reinterpret_cast<float4*>(xp + 4) = b;
-        ss += a.x * a.x; ss += a.y * a.y; ss += a.z * a.z; ss += a.w * a.w;
-        ss += b.x * b.x; ss += b.y * b.y; ss += b.z * b.z; ss += b.w * b.w;
+        xs8[0] = xa.x + acc[0]; xs8[1] = xa.y + acc[1]; xs8[2] = xa.z + acc[2]; xs8[3] = xa.w + acc[3];
+        xs8[4] = xb.x + acc[4]; xs8[5] = xb.y + acc[5]; xs8[6] = xb.z + acc[6]; xs8[7] = xb.w + acc[7];
+        *reinterpret_cast<float4*>(xp) = make_float4(xs8[0], xs8[1], xs8[2], xs8[3]);
+        *reinterpret_cast<float4*>(xp + 4) = make_float4(xs8[4], xs8[5], xs8[6], xs8[7]);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) ss += xs8[c] * xs8[c];
     }
     if (w == nullptr) return;
+    const float4 wa = mine ? *reinterpret_cast<const float4*>(w + v * 8) : make_float4(0, 0, 0, 0);
+    const float4 wb = mine ? *reinterpret_cast<const float4*>(w + v * 8 + 4) : make_float4(0, 0, 0, 0);
     const float inv = rsqrtf(block_sum(ss, red) / H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-        h[t * H + i] = __float2bfloat16_rn(x[t * H + i] * inv * (1.f + w[i]));
+    if (mine) {
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(xs8[2 * c] * inv * (1.f + wv[2 * c]), xs8[2 * c + 1] * inv * (1.f + wv[2 * c + 1]));
+            op[c] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(h + t * H + v * 8) = o;
+    }
 }
 
 // rows of xs = rows of x picked by row_token (the MoE dispatch gather into expert-sorted order)
@@ -219,7 +235,8 @@ void fold_add_norm(const float* parts, long long part_stride, int n_parts, float
 }
 void combine_add_norm(const void* y, const int* slot_row, const int* ids, const float* wts, const float* sg, int k, int ns,
                       float* x, const float* w, void* h, int rows, int H, float eps, cudaStream_t s) {
-    combine_add_norm_kernel<<<rows, kRowThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(y), slot_row, ids, wts, sg, k, ns, x, w,
+    const int threads = ((H / 8 + 31) / 32) * 32;          // one 8-column piece per thread, H <= 8192
+    combine_add_norm_kernel<<<rows, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(y), slot_row, ids, wts, sg, k, ns, x, w,
                                                         static_cast<__nv_bfloat16*>(h), H, eps);
 }
 void gather_rows(const void* x, const int* row_token, const int* n_rows, void* xs, int max_rows, int H, cudaStream_t s) {

@@ -231,6 +231,9 @@ class CudaOps:
         logits = self.head_logits(h, lm_head)
         val = torch.empty(h.shape[0], dtype=torch.float32, device=self.device)
         idx = torch.empty(h.shape[0], dtype=torch.int64, device=self.device)
-        self.launches += 1
-        self.ext.argmax_rows(logits, vocab0, val, idx)
+        chunks = -(-logits.shape[1] // self.ext.argmax_chunk())
+        cv = torch.empty(h.shape[0] * chunks, dtype=torch.float32, device=self.device)
+        ci = torch.empty(h.shape[0] * chunks, dtype=torch.int32, device=self.device)
+        self.launches += 2 if chunks > 1 else 1
+        self.ext.argmax_rows(logits, vocab0, val, idx, cv, ci)
         return val, idx
