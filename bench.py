@@ -91,6 +91,8 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="tensor/expert-parallel exchanges: fused into the kernels over peer memory, or NCCL collectives (baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -115,7 +117,7 @@ def main() -> None:
     dev = f"cuda:{local}"
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(dev))
-    par = make_parallel(tp=world, pp=1, int_device=dev)
+    par = make_parallel(tp=world, pp=1, int_device=dev, fused=(args.comm == "fused"))
 
     cfg = NAMED_CONFIGS[args.model]("nvfp4")
     total_len = args.prompt_len + args.warmup + 2 * args.steps + 16
@@ -261,6 +263,7 @@ def main() -> None:
             "data": "synthetic: random-init weights generated on device, uniform-random prompt ids (seed 1)",
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
                        "parallelism": f"tp{n}+ep{n}" if n > 1 else "single", "cuda_graph": graph is not None,
+                       "exchanges": (args.comm if n > 1 else "none"),
                        "l2": "each step streams >2 GB of weights, larger than the 126 MB L2"},
             "ttft_s": round(ttft_s, 4), "ttft_vs_baseline": round(BASELINE_TTFT_S.get(n, 1.933) / ttft_s, 2),
             "e2e": {"value": round(args.steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 8},
@@ -271,7 +274,9 @@ def main() -> None:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)      # tearing NCCL down under a live captured graph can block
 
 
 if __name__ == "__main__":

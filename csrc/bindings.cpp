@@ -3,6 +3,8 @@
 #include <torch/extension.h>
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <cstring>
+#include <vector>
 
 #include "attn/attn.h"
 #include "gdn/gdn_scan.h"
@@ -30,7 +32,8 @@ T* ptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? static_ca
 void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tensor out, int64_t k, int64_t n_out, bool nvfp4,
           int64_t epilogue, int64_t bn, int64_t ranges, int64_t tokens, int64_t ldo, int64_t out_range_stride,
           c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
-          c10::optional<torch::Tensor> status) {
+          c10::optional<torch::Tensor> status, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
+          int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from) {
     need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows on the GPU");
     need(w.is_cuda() && w.is_contiguous() && row_scale.is_cuda() && row_scale.scalar_type() == torch::kFloat32, "bad weights");
     need(out.is_cuda(), "bad output");
@@ -45,6 +48,18 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
         a.tasks = tasks->data_ptr<int>(); a.num_tasks = meta->data_ptr<int>(); a.max_tasks = static_cast<int>(max_tasks);
     }
     a.status = status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+    if (!peer_out.empty()) {
+        need(peer_out.size() <= 8 && peer_out.size() == peer_flags.size() && peer_local != 0, "peer exchange arguments");
+        a.peers = static_cast<int>(peer_out.size());
+        for (size_t i = 0; i < peer_out.size(); ++i) {
+            a.peer_out[i] = reinterpret_cast<void*>(peer_out[i]);
+            a.peer_flags[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+        }
+        a.peer_local = reinterpret_cast<uint32_t*>(peer_local);
+        a.peer_half_stride = peer_half_stride;
+        a.peer_self = static_cast<int>(peer_self);
+        a.peer_local_only_from = static_cast<int>(peer_local_only_from);
+    }
     check(vade::umma_gemm(a, stream_of(x)));
 }
 
@@ -62,29 +77,43 @@ void rmsnorm(torch::Tensor x, torch::Tensor w, torch::Tensor h, double eps, int6
                   static_cast<int>(x.size(1)), static_cast<float>(eps), static_cast<int>(ldh), static_cast<int>(h_off), stream_of(x));
 }
 
+vade::ExchangeWait make_wait(int64_t flags, int64_t ranks, int64_t self, int64_t half_stride, const c10::optional<torch::Tensor>& status) {
+    vade::ExchangeWait w;
+    w.flags = reinterpret_cast<const uint32_t*>(flags);
+    w.status = status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+    w.half_stride = half_stride;
+    w.ranks = static_cast<int>(ranks);
+    w.self = static_cast<int>(self);
+    return w;
+}
+
 void fold_add_norm(torch::Tensor parts, int64_t n_parts, int64_t part_stride, torch::Tensor x, c10::optional<torch::Tensor> w,
-                   c10::optional<torch::Tensor> h, double eps) {
+                   c10::optional<torch::Tensor> h, double eps, int64_t wait_flags, int64_t ranks, int64_t self, int64_t half_stride,
+                   c10::optional<torch::Tensor> status) {
     need(parts.scalar_type() == torch::kFloat32 && x.scalar_type() == torch::kFloat32 && x.is_contiguous(), "fold dtypes");
     c10::cuda::CUDAGuard guard(x.device());
+    const vade::ExchangeWait wt = make_wait(wait_flags, ranks, self, half_stride, status);
     vade::fold_add_norm(parts.data_ptr<float>(), part_stride, static_cast<int>(n_parts), x.data_ptr<float>(), ptr<float>(w),
                         h.has_value() ? h->data_ptr() : nullptr, static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
-                        static_cast<float>(eps), stream_of(x));
+                        static_cast<float>(eps), &wt, stream_of(x));
 }
 
 void combine_add_norm(torch::Tensor y, torch::Tensor slot_row, torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, int64_t k,
-                      int64_t ns, torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> h, double eps) {
+                      int64_t ns, torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> h, double eps,
+                      int64_t wait_flags, int64_t ranks, int64_t self, int64_t half_stride, c10::optional<torch::Tensor> status) {
     need(y.scalar_type() == torch::kBFloat16 && x.scalar_type() == torch::kFloat32 && k + ns <= 32 && x.size(1) % 8 == 0 && x.size(1) <= 8192, "combine arguments");
     c10::cuda::CUDAGuard guard(x.device());
+    const vade::ExchangeWait wt = make_wait(wait_flags, ranks, self, half_stride, status);
     vade::combine_add_norm(y.data_ptr(), slot_row.data_ptr<int>(), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
                            static_cast<int>(k), static_cast<int>(ns), x.data_ptr<float>(), ptr<float>(w),
                            h.has_value() ? h->data_ptr() : nullptr, static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
-                           static_cast<float>(eps), stream_of(x));
+                           static_cast<float>(eps), &wt, stream_of(x));
 }
 
 void gather_rows(torch::Tensor x, torch::Tensor row_token, torch::Tensor meta, torch::Tensor xs, int64_t max_rows) {
     need(x.scalar_type() == torch::kBFloat16 && xs.scalar_type() == torch::kBFloat16 && x.size(1) % 8 == 0, "gather arguments");
     c10::cuda::CUDAGuard guard(x.device());
-    vade::gather_rows(x.data_ptr(), row_token.data_ptr<int>(), meta.data_ptr<int>() + 1, xs.data_ptr(), static_cast<int>(max_rows),
+    vade::gather_rows(x.data_ptr(), row_token.data_ptr<int>(), meta.data_ptr<int>(), xs.data_ptr(), static_cast<int>(max_rows),
                       static_cast<int>(x.size(1)), stream_of(x));
 }
 
@@ -172,16 +201,59 @@ void swiglu_fold(torch::Tensor parts, torch::Tensor meta, torch::Tensor mid) {
 }
 
 void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id,
-                 c10::optional<torch::Tensor> chunk_val, c10::optional<torch::Tensor> chunk_idx) {
+                 c10::optional<torch::Tensor> cand, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
+                 int64_t peer_half_stride, int64_t peer_self, c10::optional<torch::Tensor> status) {
     need(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 && best_id.scalar_type() == torch::kInt64, "argmax arguments");
     c10::cuda::CUDAGuard guard(logits.device());
     const int64_t chunks = (logits.size(1) + vade::argmax_chunk() - 1) / vade::argmax_chunk();
-    const bool two = chunk_val.has_value() && chunk_idx.has_value() && chunk_val->numel() >= logits.size(0) * chunks &&
-                     chunk_idx->numel() >= logits.size(0) * chunks;
+    uint32_t* st = status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+    vade::HeadExchange hx;
+    const bool peers = !peer_out.empty();
+    if (peers) {
+        need(peer_out.size() <= 8 && peer_out.size() == peer_flags.size() && peer_local != 0, "peer exchange arguments");
+        hx.ranks = static_cast<int>(peer_out.size());
+        for (size_t i = 0; i < peer_out.size(); ++i) {
+            hx.out[i] = reinterpret_cast<void*>(peer_out[i]);
+            hx.flags[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+        }
+        hx.local = reinterpret_cast<uint32_t*>(peer_local);
+        hx.half_stride = peer_half_stride;
+        hx.self = static_cast<int>(peer_self);
+    }
+    const bool two = cand.has_value() && cand->numel() * cand->element_size() >= logits.size(0) * chunks * 8;
     vade::argmax_rows(logits.data_ptr<float>(), logits.stride(0), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
                       static_cast<int>(id0), best_val.data_ptr<float>(), reinterpret_cast<long long*>(best_id.data_ptr<int64_t>()),
-                      two ? chunk_val->data_ptr<float>() : nullptr, two ? chunk_idx->data_ptr<int>() : nullptr, stream_of(logits));
+                      two ? cand->data_ptr() : nullptr, peers ? &hx : nullptr, st, stream_of(logits));
 }
+
+// ---- symmetric (peer-mapped) device memory over CUDA IPC
+torch::Tensor symm_alloc(int64_t nbytes, int64_t device) {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    void* p = nullptr;
+    need(cudaMalloc(&p, static_cast<size_t>(nbytes)) == cudaSuccess, "cudaMalloc of a symmetric buffer failed");
+    need(cudaMemset(p, 0, static_cast<size_t>(nbytes)) == cudaSuccess, "cudaMemset failed");
+    auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, static_cast<c10::DeviceIndex>(device));
+    return torch::from_blob(p, {nbytes}, [](void* q) { cudaFree(q); }, opts);
+}
+
+py::bytes symm_handle(torch::Tensor t) {
+    cudaIpcMemHandle_t h;
+    need(cudaIpcGetMemHandle(&h, t.data_ptr()) == cudaSuccess, "cudaIpcGetMemHandle failed");
+    return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+
+int64_t symm_open(py::bytes handle, int64_t device) {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    std::string raw = handle;
+    need(raw.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, raw.data(), sizeof(h));
+    void* p = nullptr;
+    need(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess, "cudaIpcOpenMemHandle failed");
+    return reinterpret_cast<int64_t>(p);
+}
+
+void symm_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
 
 }  // namespace
 
@@ -201,4 +273,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax_rows", &argmax_rows);
     m.def("attn_split_keys", &vade::attn_split_keys);
     m.def("argmax_chunk", &vade::argmax_chunk);
+    m.def("symm_alloc", &symm_alloc);
+    m.def("symm_handle", &symm_handle);
+    m.def("symm_open", &symm_open);
+    m.def("symm_close", &symm_close);
 }

@@ -147,6 +147,65 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// ------------------------------------------------------------------ cross-GPU exchanges
+// One exchange = every rank of a group writes its part of a buffer into EVERY rank's copy of the
+// buffer (plain peer stores), then publishes a sequence number in each destination's flag word
+// flags[source rank].  Buffers are double-buffered by the parity of the sequence number.  Every
+// rank runs the same exchanges in the same order, and a rank's consumer of exchange n precedes its
+// producer of exchange n + 1 in stream order, so a writer can never be more than one exchange
+// ahead of a reader and two halves suffice.
+constexpr int kMaxPeers = 8;
+struct PeerExchange {
+    void* out[kMaxPeers];           // each rank's copy of the exchange buffer (index = rank)
+    uint32_t* flags[kMaxPeers];     // each rank's flag array of this exchange kind [ranks]
+    uint32_t* local;                // this rank: [0] sequence number of the last finished exchange, [1] CTAs arrived
+    long long half_stride;          // elements between the two halves of the buffer
+    int n;                          // ranks (0 = no exchange, plain local output)
+    int self;
+    int local_only_from;            // grouped GEMM: tasks of experts >= this index are stored locally only
+};
+
+__device__ __forceinline__ uint32_t exchange_parity(const PeerExchange& px) {
+    return (*reinterpret_cast<volatile uint32_t*>(px.local) + 1u) & 1u;
+}
+
+// Called by ONE thread per CTA after a CTA-wide barrier that follows the CTA's peer stores (each
+// storing thread ran __threadfence_system() before the barrier).  The last CTA to arrive publishes.
+__device__ __forceinline__ void exchange_arrive(const PeerExchange& px, uint32_t total_ctas) {
+    __threadfence_system();
+    const uint32_t prev = atomicAdd(px.local + 1, 1u);
+    if (prev == total_ctas - 1) {
+        __threadfence_system();
+        const uint32_t v = *reinterpret_cast<volatile uint32_t*>(px.local) + 1u;
+        px.local[1] = 0;
+        px.local[0] = v;
+        __threadfence_system();
+        for (int d = 0; d < px.n; ++d) st_release_sys(px.flags[d] + px.self, v);
+    }
+}
+
+// Consumer side, called by the first warp of a CTA: lane s waits until rank s has published the
+// exchange this rank's own producer just finished (flags[self]).  Bounded: after `limit_ns` the
+// status word is raised and the caller proceeds (its output is then invalid, the GPU stays usable).
+// Returns the buffer half (0/1) to read.
+__device__ __forceinline__ uint32_t exchange_wait(const uint32_t* flags, int n, int self, uint32_t* status,
+                                                  unsigned long long limit_ns = 5000000000ull) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t v = ld_acquire_sys(flags + self);
+    if (lane < n && lane != self) {
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(flags + lane) - v) < 0) {
+            if ((++spins & 1023u) == 0 && globaltimer_ns() - t0 > limit_ns) {
+                if (status != nullptr) atomicMax(status, 100u + static_cast<uint32_t>(lane));
+                break;
+            }
+        }
+    }
+    __syncwarp();
+    return v & 1u;
+}
+
 // ------------------------------------------------------------------ small math
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }

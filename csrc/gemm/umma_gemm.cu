@@ -48,6 +48,7 @@ struct GemmDev {
     int kb_per_range;
     int tokens;
     int ldo;
+    PeerExchange px;                // px.n > 0: the epilogue stores into every rank's buffer and signals
 };
 
 template <int BN, int STAGES, bool NVFP4, int EPI>
@@ -59,7 +60,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     int expert = 0, row0, nrows, orow0;
     if (a.tasks != nullptr) {
-        if (static_cast<int>(blockIdx.y) >= *a.num_tasks) return;
+        if (static_cast<int>(blockIdx.y) >= *a.num_tasks) {
+            if (a.px.n > 0 && threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
+            return;
+        }
         const int4 t = a.tasks[blockIdx.y];
         expert = t.x; row0 = t.y; nrows = t.z; orow0 = t.w;
     } else {
@@ -200,6 +204,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const bool ok = mbar_wait(tmem_full, 0) && (*abort_flag == 0);
         if (!ok) fail(5);
         tc_fence_after_sync();
+        const long long px_base = a.px.n > 0 ? static_cast<long long>(exchange_parity(a.px)) * a.px.half_stride : 0;
+        const bool px_all = expert < a.px.local_only_from;
         if (ok) {
             const float rs = (m < a.n_out) ? a.row_scale[static_cast<long long>(expert) * a.rs_expert_stride + m] : 0.f;
             constexpr int kColsPerSet = BN >= 32 ? BN / 2 : BN;
@@ -219,16 +225,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         if ((lane & 1) == 0 && c + j < nrows && m < a.n_out)
                             reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + (m >> 1)] = __float2bfloat16_rn(siluf_(yb) * other);
                     } else if (c + j < nrows && m < a.n_out) {
-                        if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
-                        else reinterpret_cast<float*>(a.out)[range * a.out_range_stride + tok * a.ldo + m] = y;
+                        if (a.px.n == 0) {
+                            if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
+                            else reinterpret_cast<float*>(a.out)[range * a.out_range_stride + tok * a.ldo + m] = y;
+                        } else {
+                            const long long at = px_base + (EPI == 0 ? 0 : range * a.out_range_stride) + tok * a.ldo + m;
+                            if (px_all) {
+                                for (int d = 0; d < a.px.n; ++d) {
+                                    if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[d])[at] = __float2bfloat16_rn(y);
+                                    else reinterpret_cast<float*>(a.px.out[d])[at] = y;
+                                }
+                            } else {
+                                if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[a.px.self])[at] = __float2bfloat16_rn(y);
+                                else reinterpret_cast<float*>(a.px.out[a.px.self])[at] = y;
+                            }
+                        }
                     }
                 }
             }
         }
     }
+    if (a.px.n > 0) __threadfence_system();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
+    if (a.px.n > 0 && threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
 }
 
 // ------------------------------------------------------------------------------------- host side
@@ -318,6 +339,20 @@ const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
     d.kb_per_range = d.kb_total / h.ranges;
     d.tokens = h.tokens;
     d.ldo = h.ldo;
+    d.px = PeerExchange{};
+    d.px.local_only_from = 0x7fffffff;
+    if (h.peers > 0) {
+        if (h.peers > kMaxPeers || h.epilogue == 2) return "bad peer exchange arguments";
+        for (int i = 0; i < h.peers; ++i) {
+            d.px.out[i] = h.peer_out[i];
+            d.px.flags[i] = h.peer_flags[i];
+        }
+        d.px.local = h.peer_local;
+        d.px.half_stride = h.peer_half_stride;
+        d.px.n = h.peers;
+        d.px.self = h.peer_self;
+        if (h.peer_local_only_from >= 0) d.px.local_only_from = h.peer_local_only_from;
+    }
     const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + h.bn - 1) / h.bn;
     if (y <= 0) return "empty grid";
     dim3 grid(m_tiles, y, h.ranges);

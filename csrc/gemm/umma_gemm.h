@@ -30,6 +30,15 @@ struct GemmArgs {
     const int* num_tasks = nullptr;
     int max_tasks = 0;
     uint32_t* status = nullptr;             // device word, raised (atomicMax) on a wait timeout
+    // fused all-gather of the output (peers > 0): the epilogue stores every element into each rank's copy
+    // of a double-buffered exchange buffer and the last CTA publishes a sequence number to every rank
+    int peers = 0;
+    int peer_self = 0;
+    void* peer_out[8] = {};
+    uint32_t* peer_flags[8] = {};
+    uint32_t* peer_local = nullptr;         // [0] last finished exchange, [1] arrived CTAs
+    long long peer_half_stride = 0;         // elements between the two buffer halves
+    int peer_local_only_from = -1;          // grouped: experts >= this index are stored to this rank only
 };
 
 // Returns nullptr on success or a static error text.

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cfloat>
+#include "../common/ptx.cuh"
 #include "head.h"
 
 namespace vade {
@@ -36,12 +37,16 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, long long l
     }
 }
 
-// Two-stage form for wide vocabularies: stage 1 reduces chunks of 4096 logits (one CTA each, 16 loads
-// per thread issued together), stage 2 joins the chunk winners of a row in ascending chunk order.
+// Two-stage form for wide or vocabulary-parallel heads: stage 1 reduces chunks of 4096 logits (one CTA
+// each, 16 loads per thread issued together) to (value, global id) pairs; with a peer exchange the pairs
+// go to every rank's copy of the candidate table [rank][row][chunk].  Stage 2 joins a row's candidates
+// in ascending (rank, chunk) order: larger value wins, ties to the lower id, so every rank picks the
+// same token.
 constexpr int kChunk = 4096;
 
 __global__ void __launch_bounds__(256)
-argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, float* __restrict__ cval, int* __restrict__ cidx, int n_chunks) {
+argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, int id0, uint2* __restrict__ cand, int n_chunks,
+                     int rows, const PeerExchange px) {
     __shared__ float sv[8];
     __shared__ int si[8];
     const long long row = blockIdx.y;
@@ -66,40 +71,62 @@ argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, floa
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w)
             if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-        cval[row * n_chunks + blockIdx.x] = bv;
-        cidx[row * n_chunks + blockIdx.x] = bi;
+        const uint2 c = make_uint2(__float_as_uint(bv), static_cast<uint32_t>(bi + id0));
+        if (px.n == 0) {
+            cand[row * n_chunks + blockIdx.x] = c;
+        } else {
+            const long long at = static_cast<long long>(exchange_parity(px)) * px.half_stride
+                               + (static_cast<long long>(px.self) * rows + row) * n_chunks + blockIdx.x;
+            for (int d = 0; d < px.n; ++d) reinterpret_cast<uint2*>(px.out[d])[at] = c;
+            __threadfence_system();
+            exchange_arrive(px, gridDim.x * gridDim.y);
+        }
     }
 }
 
 __global__ void __launch_bounds__(32)
-argmax_join_kernel(const float* __restrict__ cval, const int* __restrict__ cidx, int n_chunks, int id0,
-                   float* __restrict__ best_val, long long* __restrict__ best_id) {
+argmax_join_kernel(const uint2* __restrict__ cand_in, int n_cand_per_rank, int ranks, const uint32_t* flags, int self,
+                   long long half_stride, uint32_t* status, float* __restrict__ best_val, long long* __restrict__ best_id) {
     const long long row = blockIdx.x;
+    const int rows = gridDim.x;
+    const uint2* cand = cand_in;
+    if (flags != nullptr) cand += static_cast<long long>(exchange_wait(flags, ranks, self, status)) * half_stride;
     float bv = -FLT_MAX;
-    int bi = 0x7fffffff;
-    for (int c = threadIdx.x; c < n_chunks; c += 32) {
-        const float v = cval[row * n_chunks + c];
-        const int i = cidx[row * n_chunks + c];
+    long long bi = 0x7fffffffffffll;
+    for (int c = threadIdx.x; c < ranks * n_cand_per_rank; c += 32) {
+        const int r = c / n_cand_per_rank, ch = c % n_cand_per_rank;
+        const uint2 u = cand[(static_cast<long long>(r) * rows + row) * n_cand_per_rank + ch];
+        const float v = __uint_as_float(u.x);
+        const long long i = u.y;
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (threadIdx.x == 0) { best_val[row] = bv; best_id[row] = static_cast<long long>(bi) + id0; }
+    if (threadIdx.x == 0) { best_val[row] = bv; best_id[row] = bi; }
 }
 
 void argmax_rows(const float* logits, long long ld, int rows, int n, int id0, float* best_val, long long* best_id,
-                 float* chunk_val, int* chunk_idx, cudaStream_t s) {
-    if (chunk_val == nullptr || n <= kChunk) {
+                 void* cand, const HeadExchange* hx, uint32_t* status, cudaStream_t s) {
+    if (cand == nullptr && hx == nullptr) {
         argmax_rows_kernel<<<rows, 1024, 0, s>>>(logits, ld, n, id0, best_val, best_id);
         return;
     }
     const int n_chunks = (n + kChunk - 1) / kChunk;
-    argmax_chunks_kernel<<<dim3(n_chunks, rows), 256, 0, s>>>(logits, ld, n, chunk_val, chunk_idx, n_chunks);
-    argmax_join_kernel<<<rows, 32, 0, s>>>(chunk_val, chunk_idx, n_chunks, id0, best_val, best_id);
+    PeerExchange px{};
+    if (hx != nullptr) {
+        for (int i = 0; i < hx->ranks; ++i) { px.out[i] = hx->out[i]; px.flags[i] = hx->flags[i]; }
+        px.local = hx->local; px.half_stride = hx->half_stride; px.n = hx->ranks; px.self = hx->self; px.local_only_from = 0x7fffffff;
+    }
+    argmax_chunks_kernel<<<dim3(n_chunks, rows), 256, 0, s>>>(logits, ld, n, id0, static_cast<uint2*>(cand), n_chunks, rows, px);
+    if (hx != nullptr)
+        argmax_join_kernel<<<rows, 32, 0, s>>>(static_cast<const uint2*>(hx->out[hx->self]), n_chunks, hx->ranks, hx->flags[hx->self],
+                                              hx->self, hx->half_stride, status, best_val, best_id);
+    else
+        argmax_join_kernel<<<rows, 32, 0, s>>>(static_cast<const uint2*>(cand), n_chunks, 1, nullptr, 0, 0, status, best_val, best_id);
 }
 
 int argmax_chunk() { return kChunk; }

@@ -2,18 +2,22 @@
 // row layout the grouped GEMM consumes.  Router logits may arrive as several K-range partials
 // (fp32 [parts][T][ld]); they are added in ascending part order before the softmax.
 //
+// The row layout is GLOBAL: it covers every expert of the model and is a pure function of the routing,
+// so every rank of an expert-parallel group computes the same layout, runs tasks only for the experts
+// it holds, and finds every other rank's outputs at the same row numbers after the exchange.
+//
 // Large passes (prompt tiles):
-//   route_count   one warp per token; each selected pair of a LOCAL expert takes a position inside
-//                 its expert with an integer atomic (positions only decide which row of the gathered
-//                 matrix a pair occupies, never any arithmetic)
-//   scan_tasks    one CTA: prefix sums over local + shared experts, task table {expert, first row,
-//                 rows, first output row}, totals; re-zeroes the counters for the next call
-//   scatter_rows  one thread per (token, slot): row_token[] (gather list) and slot_row[][] (where the
-//                 combine finds each slot's output; -1 when another rank owns the expert)
+//   route_topk       one warp per token: ids, weights, shared gate
+//   route_positions  one CTA per expert: the position of each (token, slot) pair inside its expert is
+//                    the number of earlier pairs (token-major order) of that expert: a stable count,
+//                    no atomics, identical on every rank
+//   scan_tasks       one CTA: prefix sums over all experts + shared virtual experts, task table
+//                    {local expert, first row, rows, first output row} for the experts this rank holds
+//   scatter_rows     one thread per (token, slot): row_token[] (gather list) and slot_row[][]
 // Small passes (decode / verify, T <= 16):
-//   route_small   one CTA does all of it without a gather: every ACTIVE expert (ascending id) becomes
-//                 one task over all T token rows (the token tile is 16 wide anyway); outputs of
-//                 tokens that did not pick the expert are never read.
+//   route_small      one CTA does all of it without a gather: every ACTIVE expert (ascending id) gets
+//                    a 16-row block and, on the rank that holds it, one task over all T token rows (the
+//                    token tile is 16 wide anyway); outputs of tokens that did not pick it are never read.
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cfloat>
@@ -79,9 +83,8 @@ __device__ __forceinline__ void warp_topk(const float* __restrict__ logits, long
 }
 
 template <int PER>
-__global__ void route_count_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E,
-                                   int k, int renorm, int e0, int n_local, int* __restrict__ ids, float* __restrict__ wts,
-                                   float* __restrict__ sg, int* __restrict__ counts, int* __restrict__ pos) {
+__global__ void route_topk_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E,
+                                  int k, int renorm, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sg) {
     const int warps_per_block = blockDim.x >> 5;
     const int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -92,10 +95,31 @@ __global__ void route_count_kernel(const float* __restrict__ logits, long long p
     if (lane < k) {
         ids[t * k + lane] = e;
         wts[t * k + lane] = w;
-        const int le = e - e0;
-        pos[t * k + lane] = (le >= 0 && le < n_local) ? atomicAdd(&counts[le], 1) : -1;
     }
     if (lane == 0) sg[t] = sigmoidf_(gl);
+}
+
+// pos[p] = number of pairs p' < p with ids[p'] == ids[p]; counts[e] = pairs of expert e.
+__global__ void __launch_bounds__(256)
+route_positions_kernel(const int* __restrict__ ids, int P, int* __restrict__ pos, int* __restrict__ counts) {
+    __shared__ int wsum[8];
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int running = 0;
+    for (int base = 0; base < P; base += 256) {
+        const int p = base + threadIdx.x;
+        const bool match = p < P && ids[p] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, match);
+        if (lane == 0) wsum[warp] = __popc(bal);
+        __syncthreads();
+        int woff = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { const int c = wsum[w]; if (w < warp) woff += c; total += c; }
+        if (match) pos[p] = running + woff + __popc(bal & ((1u << lane) - 1u));
+        running += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = running;
 }
 
 // Inclusive scan of two integers across the block (1024 threads), fixed order.
@@ -122,26 +146,31 @@ __device__ __forceinline__ void block_scan2(int& a, int& b, int* sa, int* sb) {
     __syncthreads();
 }
 
+// meta: [0] tasks of this rank, [1] rows of the global layout, [2] tasks wanted (> max_tasks: the host
+// bound was wrong), [4] first and [5] end row of this rank's routed experts, [6] first shared row.
 __global__ void __launch_bounds__(1024, 1)
-scan_tasks_kernel(int* __restrict__ counts, int n_local, int ns, int T, int bn,
+scan_tasks_kernel(const int* __restrict__ counts, int E, int e0, int n_local, int ns, int T, int bn,
                   int* __restrict__ offsets, int4* __restrict__ tasks, int* __restrict__ meta, int max_tasks) {
-    // meta[0] = number of tasks, meta[1] = number of rows, meta[2] = tasks wanted (> max_tasks means the host bound was wrong)
     __shared__ int sa[32], sb[32];
-    const int ne = n_local + ns;
+    const int ne = E + ns;
     int carry_rows = 0, carry_tasks = 0;
     for (int base = 0; base < ne; base += 1024) {
         const int e = base + threadIdx.x;
-        const int c = e < ne ? (e < n_local ? counts[e] : T) : 0;
-        const int nt = (c + bn - 1) / bn;
+        const bool local = e < ne && ((e >= e0 && e < e0 + n_local) || e >= E);
+        const int c = e < ne ? (e < E ? counts[e] : T) : 0;
+        const int nt = local ? (c + bn - 1) / bn : 0;
         int ic = c, it = nt;
         block_scan2(ic, it, sa, sb);
         const int row_off = carry_rows + ic - c, task_off = carry_tasks + it - nt;
         if (e < ne) {
             offsets[e] = row_off;
+            const int le = e < E ? e - e0 : n_local + (e - E);
             for (int r = 0; r < nt; ++r)
                 if (task_off + r < max_tasks)
-                    tasks[task_off + r] = make_int4(e, row_off + r * bn, min(bn, c - r * bn), row_off + r * bn);
-            if (e < n_local) counts[e] = 0;
+                    tasks[task_off + r] = make_int4(le, row_off + r * bn, min(bn, c - r * bn), row_off + r * bn);
+            if (e == e0) meta[4] = row_off;
+            if (e == e0 + n_local - 1) meta[5] = row_off + c;
+            if (e == E) meta[6] = row_off;
         }
         carry_rows += sa[31];
         carry_tasks += sb[31];
@@ -151,24 +180,20 @@ scan_tasks_kernel(int* __restrict__ counts, int n_local, int ns, int T, int bn,
         meta[0] = min(carry_tasks, max_tasks);
         meta[1] = carry_rows;
         meta[2] = carry_tasks;
+        if (ns == 0) meta[6] = carry_rows;
+        if (n_local == 0) { meta[4] = 0; meta[5] = 0; }
     }
 }
 
 __global__ void scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const int* __restrict__ offsets,
-                                    int T, int k, int ns, int e0, int n_local, int* __restrict__ row_token, int* __restrict__ slot_row) {
+                                    int T, int k, int ns, int E, int* __restrict__ row_token, int* __restrict__ slot_row) {
     const int slots = k + ns;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * slots) return;
     const int t = idx / slots, j = idx % slots;
-    int row = -1;
-    if (j < k) {
-        const int p = pos[t * k + j];
-        if (p >= 0) row = offsets[ids[t * k + j] - e0] + p;
-    } else {
-        row = offsets[n_local + (j - k)] + t;
-    }
+    const int row = j < k ? offsets[ids[t * k + j]] + pos[t * k + j] : offsets[E + (j - k)] + t;
     slot_row[idx] = row;
-    if (row >= 0) row_token[row] = t;
+    row_token[row] = t;
 }
 
 // T <= 16 rows, n_local <= 1024 experts, one CTA of 1024 threads.
@@ -211,65 +236,60 @@ route_small_kernel(const float* __restrict__ logits, long long part_stride, int 
             ids[warp * k + lane] = e;
             wts[warp * k + lane] = w;
             sel[warp * 32 + lane] = e;
-            const int le = e - e0;
-            if (le >= 0 && le < n_local) present[le] = 1;
+            present[e] = 1;
         }
         if (lane == 0) sg[warp] = sigmoidf_(gl);
     }
     __syncthreads();
-    const int mine = threadIdx.x < n_local ? present[threadIdx.x] : 0;
-    int inc = mine, dummy = 0;
-    block_scan2(inc, dummy, sa, sb);
-    const int n_active = sa[31];
+    // global block index of every active expert (ascending id); this rank's tasks are the active experts it holds
+    const int mine = threadIdx.x < E ? present[threadIdx.x] : 0;
+    const int local = (mine && static_cast<int>(threadIdx.x) >= e0 && static_cast<int>(threadIdx.x) < e0 + n_local) ? 1 : 0;
+    int inc = mine, inc_local = local;
+    block_scan2(inc, inc_local, sa, sb);
+    const int n_active = sa[31], n_active_local = sb[31];
     const int idx = inc - mine;
     index_of[threadIdx.x] = idx;
-    if (mine) {
-        tasks_up[idx] = make_int4(threadIdx.x, 0, T, idx * 16);
-        tasks_down[idx] = make_int4(threadIdx.x, idx * 16, T, idx * 16);
+    if (local) {
+        const int li = inc_local - 1;
+        tasks_up[li] = make_int4(threadIdx.x - e0, 0, T, idx * 16);
+        tasks_down[li] = make_int4(threadIdx.x - e0, idx * 16, T, idx * 16);
     }
     if (threadIdx.x < ns) {
-        const int i = n_active + threadIdx.x;
-        tasks_up[i] = make_int4(n_local + threadIdx.x, 0, T, i * 16);
-        tasks_down[i] = make_int4(n_local + threadIdx.x, i * 16, T, i * 16);
+        const int li = n_active_local + threadIdx.x, blk = n_active + threadIdx.x;
+        tasks_up[li] = make_int4(n_local + threadIdx.x, 0, T, blk * 16);
+        tasks_down[li] = make_int4(n_local + threadIdx.x, blk * 16, T, blk * 16);
     }
     if (threadIdx.x == 0) {
-        meta[0] = n_active + ns;
+        meta[0] = n_active_local + ns;
         meta[1] = (n_active + ns) * 16;
-        meta[2] = n_active + ns;
+        meta[2] = n_active_local + ns;
     }
     __syncthreads();
     const int slots = k + ns;
     for (int i = threadIdx.x; i < T * slots; i += blockDim.x) {
         const int t = i / slots, j = i % slots;
-        int row = -1;
-        if (j < k) {
-            const int le = sel[t * 32 + j] - e0;
-            if (le >= 0 && le < n_local) row = index_of[le] * 16 + t;
-        } else {
-            row = (n_active + (j - k)) * 16 + t;
-        }
-        slot_row[i] = row;
+        slot_row[i] = (j < k ? index_of[sel[t * 32 + j]] : n_active + (j - k)) * 16 + t;
     }
 }
 
 template <int PER>
-static void route_large(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
-                        int n_local, int* ids, float* wts, float* sg, int* counts, int* pos, cudaStream_t s) {
+static void route_large(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm,
+                        int* ids, float* wts, float* sg, cudaStream_t s) {
     const int wpb = 4;
-    route_count_kernel<PER><<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>(logits, part_stride, n_parts, ld, T, E, k, renorm ? 1 : 0, e0,
-                                                                     n_local, ids, wts, sg, counts, pos);
+    route_topk_kernel<PER><<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>(logits, part_stride, n_parts, ld, T, E, k, renorm ? 1 : 0, ids, wts, sg);
 }
 
 const char* moe_route(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
                       int n_local, int ns, int bn, int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks,
                       int* meta, int max_tasks, int* row_token, int* slot_row, cudaStream_t s) {
     if (E > 1024 || k > 32) return "router supports up to 1024 experts and top-32";
-    if (E <= 128) route_large<4>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
-    else if (E <= 512) route_large<16>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
-    else route_large<32>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ids, wts, sg, counts, pos, s);
-    scan_tasks_kernel<<<1, 1024, 0, s>>>(counts, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
+    if (E <= 128) route_large<4>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
+    else if (E <= 512) route_large<16>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
+    else route_large<32>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
+    route_positions_kernel<<<E, 256, 0, s>>>(ids, T * k, pos, counts);
+    scan_tasks_kernel<<<1, 1024, 0, s>>>(counts, E, e0, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
     const int total = T * (k + ns);
-    scatter_rows_kernel<<<(total + 255) / 256, 256, 0, s>>>(ids, pos, offsets, T, k, ns, e0, n_local, row_token, slot_row);
+    scatter_rows_kernel<<<(total + 255) / 256, 256, 0, s>>>(ids, pos, offsets, T, k, ns, E, row_token, slot_row);
     return cudaGetLastError() == cudaSuccess ? nullptr : "route launch failed";
 }
 

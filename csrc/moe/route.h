@@ -6,8 +6,11 @@ namespace vade {
 
 // logits fp32 [n_parts][T][ld] (K-range partials, added in ascending order) with E router columns
 // followed by the shared-expert gate column.
-// Outputs: ids/wts [T][k], sg [T], tasks int4 [max_tasks], meta {tasks, rows, tasks wanted},
-// row_token [rows], slot_row [T][k + ns].  counts [n_local] must be zero on entry and is zero on exit.
+// The row layout covers ALL E experts (identical on every rank); tasks are emitted for experts
+// [e0, e0 + n_local) and the ns shared virtual experts only.
+// Outputs: ids/wts [T][k], sg [T], counts [E], pos [T][k], offsets [E + ns], tasks int4 [max_tasks],
+// meta[8] {tasks, rows, tasks wanted, -, first local row, end local row, first shared row},
+// row_token [T * (k + ns)], slot_row [T][k + ns].
 const char* moe_route(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
                       int n_local, int ns, int bn, int* ids, float* wts, float* sg, int* counts, int* pos, int* offsets, int* tasks,
                       int* meta, int max_tasks, int* row_token, int* slot_row, cudaStream_t s);

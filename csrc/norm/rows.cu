@@ -28,6 +28,25 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// Consumer side of a cross-GPU exchange: wait (bounded) until every rank has published, then return
+// the element offset of the buffer half to read.  flags == nullptr means a plain local buffer.
+struct ExchangeIn {
+    const uint32_t* flags;
+    uint32_t* status;
+    long long half_stride;
+    int n;
+    int self;
+};
+__device__ __forceinline__ long long exchange_base(const ExchangeIn& ex, long long* slot) {
+    if (ex.flags == nullptr) return 0;
+    if (threadIdx.x < 32) {
+        const uint32_t half = exchange_wait(ex.flags, ex.n, ex.self, ex.status);
+        if (threadIdx.x == 0) *slot = static_cast<long long>(half) * ex.half_stride;
+    }
+    __syncthreads();
+    return *slot;
+}
+
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ tokens,
                              float* __restrict__ x, int H) {
     const long long row = blockIdx.x;
@@ -56,9 +75,11 @@ __global__ void rmsnorm_kernel(const TIn* __restrict__ x, const float* __restric
 // costs about one memory round trip.
 template <int NP>
 __global__ void __launch_bounds__(kRowThreads)
-fold_add_norm_kernel(const float* __restrict__ parts, long long part_stride, float* __restrict__ x,
-                     const float* __restrict__ w, __nv_bfloat16* __restrict__ h, int H, float eps) {
+fold_add_norm_kernel(const float* __restrict__ parts_in, long long part_stride, float* __restrict__ x,
+                     const float* __restrict__ w, __nv_bfloat16* __restrict__ h, int H, float eps, const ExchangeIn ex) {
     __shared__ float red[32];
+    __shared__ long long ex_slot;
+    const float* parts = parts_in + exchange_base(ex, &ex_slot);
     const long long row = blockIdx.x;
     float ss = 0.f;
     for (int v = threadIdx.x; v < H / 4; v += blockDim.x) {
@@ -103,15 +124,17 @@ fold_add_norm_kernel(const float* __restrict__ parts, long long part_stride, flo
 // contiguous columns and loads all slots' pieces before the ordered adds.
 constexpr int kMaxSlots = 32;
 __global__ void __launch_bounds__(1024)
-combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_row,
+combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y_in, const int* __restrict__ slot_row,
                         const int* __restrict__ ids, const float* __restrict__ wts, const float* __restrict__ sg,
                         int k, int ns, float* __restrict__ x, const float* __restrict__ w,
-                        __nv_bfloat16* __restrict__ h, int H, float eps) {
+                        __nv_bfloat16* __restrict__ h, int H, float eps, const ExchangeIn ex) {
     __shared__ float red[32];
+    __shared__ long long ex_slot;
     __shared__ float ow[kMaxSlots];
     __shared__ int orow[kMaxSlots];
     const long long t = blockIdx.x;
     const int slots = k + ns;
+    const __nv_bfloat16* y = y_in + exchange_base(ex, &ex_slot);
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         const int id = lane < k ? ids[t * k + lane] : 0x7fffffff;
@@ -182,9 +205,10 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restri
 
 // rows of xs = rows of x picked by row_token (the MoE dispatch gather into expert-sorted order)
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
-                                   const int* __restrict__ n_rows, __nv_bfloat16* __restrict__ xs, int H) {
+                                   const int* __restrict__ meta, __nv_bfloat16* __restrict__ xs, int H) {
+    // meta: [1] rows of the layout, [4]..[5] rows of this rank's routed experts, [6] first shared row
     const int r = blockIdx.x;
-    if (r >= *n_rows) return;
+    if (r >= meta[1] || !((r >= meta[4] && r < meta[5]) || r >= meta[6])) return;
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(row_token[r]) * H);
     uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<long long>(r) * H);
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
@@ -223,24 +247,31 @@ void rmsnorm(const void* x, bool x_is_bf16, const float* w, void* h, int rows, i
     else
         rmsnorm_kernel<float><<<rows, kRowThreads, 0, s>>>(static_cast<const float*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
 }
+static ExchangeIn make_ex(const ExchangeWait* e) {
+    ExchangeIn ex{nullptr, nullptr, 0, 0, 0};
+    if (e != nullptr && e->flags != nullptr) ex = ExchangeIn{e->flags, e->status, e->half_stride, e->ranks, e->self};
+    return ex;
+}
+
 void fold_add_norm(const float* parts, long long part_stride, int n_parts, float* x, const float* w, void* h,
-                   int rows, int H, float eps, cudaStream_t s) {
+                   int rows, int H, float eps, const ExchangeWait* wait, cudaStream_t s) {
     __nv_bfloat16* hb = static_cast<__nv_bfloat16*>(h);
+    const ExchangeIn ex = make_ex(wait);
     switch (n_parts) {
-        case 1: fold_add_norm_kernel<1><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
-        case 2: fold_add_norm_kernel<2><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
-        case 4: fold_add_norm_kernel<4><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
-        default: fold_add_norm_kernel<8><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps); break;
+        case 1: fold_add_norm_kernel<1><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
+        case 2: fold_add_norm_kernel<2><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
+        case 4: fold_add_norm_kernel<4><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
+        default: fold_add_norm_kernel<8><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
     }
 }
 void combine_add_norm(const void* y, const int* slot_row, const int* ids, const float* wts, const float* sg, int k, int ns,
-                      float* x, const float* w, void* h, int rows, int H, float eps, cudaStream_t s) {
+                      float* x, const float* w, void* h, int rows, int H, float eps, const ExchangeWait* wait, cudaStream_t s) {
     const int threads = ((H / 8 + 31) / 32) * 32;          // one 8-column piece per thread, H <= 8192
     combine_add_norm_kernel<<<rows, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(y), slot_row, ids, wts, sg, k, ns, x, w,
-                                                        static_cast<__nv_bfloat16*>(h), H, eps);
+                                                        static_cast<__nv_bfloat16*>(h), H, eps, make_ex(wait));
 }
-void gather_rows(const void* x, const int* row_token, const int* n_rows, void* xs, int max_rows, int H, cudaStream_t s) {
-    gather_rows_kernel<<<max_rows, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), row_token, n_rows, static_cast<__nv_bfloat16*>(xs), H);
+void gather_rows(const void* x, const int* row_token, const int* meta, void* xs, int max_rows, int H, cudaStream_t s) {
+    gather_rows_kernel<<<max_rows, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), row_token, meta, static_cast<__nv_bfloat16*>(xs), H);
 }
 
 }  // namespace vade

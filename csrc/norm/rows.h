@@ -2,16 +2,30 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
 namespace vade {
+
+// Consumer side of a cross-GPU exchange (see PeerExchange in common/ptx.cuh): the kernel first waits,
+// bounded, until every rank has published the exchange this rank's producer finished last, then reads
+// the buffer half named by the sequence number's parity.  flags == nullptr: plain local input.
+struct ExchangeWait {
+    const uint32_t* flags = nullptr;    // this rank's flag array of the exchange kind [ranks]
+    uint32_t* status = nullptr;         // raised to 100 + rank when that rank never published
+    long long half_stride = 0;          // elements between the two halves of the input buffer
+    int ranks = 0;
+    int self = 0;
+};
 
 void embed(const void* table_bf16, const long long* tokens, float* x, int rows, int H, cudaStream_t s);
 void rmsnorm(const void* x, bool x_is_bf16, const float* w, void* h_bf16, int rows, int H, float eps, int ldh, int h_off, cudaStream_t s);
 void fold_add_norm(const float* parts, long long part_stride, int n_parts, float* x, const float* w, void* h_bf16,
-                   int rows, int H, float eps, cudaStream_t s);
+                   int rows, int H, float eps, const ExchangeWait* wait, cudaStream_t s);
 void combine_add_norm(const void* y_bf16, const int* slot_row, const int* ids, const float* wts, const float* sg, int k, int ns,
-                      float* x, const float* w, void* h_bf16, int rows, int H, float eps, cudaStream_t s);
+                      float* x, const float* w, void* h_bf16, int rows, int H, float eps, const ExchangeWait* wait, cudaStream_t s);
 // SwiGLU over fp32 K-range partials [n_parts][rows][2 * I] of interleaved gate/up columns (n_parts <= 8).
 void swiglu_fold(const float* parts, long long part_stride, int n_parts, const int* n_rows, void* mid_bf16, int max_rows, int I, cudaStream_t s);
-void gather_rows(const void* x_bf16, const int* row_token, const int* n_rows, void* xs_bf16, int max_rows, int H, cudaStream_t s);
+// Rows of this rank's routed experts and of the shared experts only (meta from the routing kernels).
+void gather_rows(const void* x_bf16, const int* row_token, const int* meta, void* xs_bf16, int max_rows, int H, cudaStream_t s);
 
 }  // namespace vade

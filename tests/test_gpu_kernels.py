@@ -113,11 +113,11 @@ def test_rmsnorm_embed_argmax():
     logits[2, 100] = logits[2, 4000] = 50.0
     val = torch.empty(5, device=DEV)
     idx = torch.empty(5, dtype=torch.int64, device=DEV)
-    ops.ext.argmax_rows(logits, 7, val, idx, None, None)
+    ops.ext.argmax_rows(logits, 7, val, idx, None, [], [], 0, 0, 0, None)
     assert torch.equal(idx, R.argmax_lowest(logits) + 7) and int(idx[2]) == 107
-    cv, ci = torch.empty(10, device=DEV), torch.empty(10, dtype=torch.int32, device=DEV)
+    cand = torch.empty(10, dtype=torch.int64, device=DEV)
     idx2 = torch.empty_like(idx)
-    ops.ext.argmax_rows(logits, 7, val, idx2, cv, ci)
+    ops.ext.argmax_rows(logits, 7, val, idx2, cand, [], [], 0, 0, 0, None)
     assert torch.equal(idx2, idx)
 
 

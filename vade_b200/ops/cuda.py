@@ -27,10 +27,11 @@ class CudaOps:
     name = "cuda"
     act = torch.bfloat16
 
-    def __init__(self, cfg: ModelConfig, device, tp: int = 1):
+    def __init__(self, cfg: ModelConfig, device, tp: int = 1, symm=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.tp = tp
+        self.symm = symm            # parallel.symm.SymmArena: fused exchanges; None = plain outputs (baseline collectives)
         self.ext = _ext.load()
         if cfg.head_dim != 256 or cfg.linear_key_head_dim != 128 or cfg.linear_value_head_dim != 128:
             raise ValueError("the sm_100a kernels handle attention head_dim 256 and GDN head dims 128")
@@ -53,11 +54,18 @@ class CudaOps:
                          "max_len": max(p + (e - s) for p, s, e in zip(batch.seq_pos0, batch.seq_start, batch.seq_start[1:]))}
         return batch.dev
 
-    def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0):
+    def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0,
+              ex=None, ex_offset: int = 0, local_only_from: int = -1):
+        """ex: parallel.symm.Exchange -> the epilogue stores into every rank's buffer (+ ex_offset bytes)."""
         nv = q.kind == "nvfp4"
         self.launches += 1
-        self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                      range_stride, tasks, meta, max_tasks, self.status)
+        if ex is None:
+            self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
+                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1)
+        else:
+            self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
+                          range_stride, tasks, meta, max_tasks, self.status, [p + ex_offset for p in ex.out], ex.flags,
+                          ex.local, ex.half_stride, ex.self_rank, local_only_from)
 
     # ---- basic
     def embed(self, w, tokens):
@@ -96,7 +104,16 @@ class CudaOps:
         return out
 
     def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
+        """Row-parallel product as canonical-range partials.  With a symmetric arena this is the fused
+        GEMM -> all-gather: the epilogue stores this rank's ranges into every rank's [8, T, n] block."""
         T = h.shape[0]
+        if self.symm is not None:
+            ex = self.symm.ex["parts"]
+            if 8 * T * q.n > ex.half_stride:
+                raise ValueError("pass has more rows than the symmetric partial buffer was sized for")
+            first = ex.self_rank * n_ranges                       # first global range this rank owns
+            self._gemm(h, q, ex.buffer, 1, _bn_for(T), n_ranges, T, q.n, T * q.n, ex=ex, ex_offset=first * T * q.n * 4)
+            return SimpleNamespace(ex=ex, T=T, n=q.n)
         out = torch.empty(n_ranges, T, q.n, dtype=torch.float32, device=self.device)
         self._gemm(h, q, out, 1, _bn_for(T), n_ranges, T, q.n, T * q.n)
         return out
@@ -104,7 +121,12 @@ class CudaOps:
     def fold_add_norm(self, parts, x, w):
         h = torch.empty(x.shape[0], x.shape[1], dtype=torch.bfloat16, device=self.device) if w is not None else None
         self.launches += 1
-        self.ext.fold_add_norm(parts, parts.shape[0], parts.stride(0), x, w, h, self.cfg.rms_norm_eps)
+        if isinstance(parts, SimpleNamespace):                     # fused exchange: wait for every rank, then fold
+            ex = parts.ex
+            self.ext.fold_add_norm(ex.buffer, 8, parts.T * parts.n, x, w, h, self.cfg.rms_norm_eps,
+                                   ex.flags[ex.self_rank], ex.ranks, ex.self_rank, ex.half_stride, self.status)
+        else:
+            self.ext.fold_add_norm(parts, parts.shape[0], parts.stride(0), x, w, h, self.cfg.rms_norm_eps, 0, 0, 0, 0, None)
         return x, h
 
     # ---- token mixers
@@ -158,13 +180,13 @@ class CudaOps:
         dev, i32 = self.device, torch.int32
         r = SimpleNamespace(
             ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
-            sg=torch.empty(T, dtype=torch.float32, device=dev), meta=torch.zeros(4, dtype=i32, device=dev),
-            slot_row=torch.empty(T, slots, dtype=i32, device=dev), T=T, k=k, ns=ns)
+            sg=torch.empty(T, dtype=torch.float32, device=dev), meta=torch.zeros(8, dtype=i32, device=dev),
+            slot_row=torch.empty(T, slots, dtype=i32, device=dev), T=T, k=k, ns=ns, E=E, n_local=mw.n_local)
         if T <= 16:
-            # small pass: one task per active expert over all T rows, no gather
+            # small pass: a 16-row block per active expert of the whole model, tasks for the experts held here, no gather
             r.small, r.bn = True, 16
             r.max_tasks = min(mw.n_local, T * k) + ns
-            r.max_rows = r.max_tasks * 16
+            r.max_rows = (min(E, T * k) + ns) * 16
             r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
             r.tasks_down = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
             self.launches += 1
@@ -175,20 +197,22 @@ class CudaOps:
         r.bn = bn = 32 if T <= 64 else 64
         r.max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
         r.max_rows = T * slots
-        counts = self._moe_ws.get((mw.n_local, "counts"))
-        if counts is None:
-            counts = self._moe_ws[(mw.n_local, "counts")] = torch.zeros(max(1, mw.n_local), dtype=i32, device=dev)
+        counts = torch.empty(E, dtype=i32, device=dev)
         r.pos = torch.empty(T, k, dtype=i32, device=dev)
-        r.offsets = torch.empty(mw.n_local + ns, dtype=i32, device=dev)
+        r.offsets = torch.empty(E + ns, dtype=i32, device=dev)
         r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
         r.tasks_down = r.tasks
         r.row_token = torch.empty(r.max_rows, dtype=i32, device=dev)
-        self.launches += 3
+        self.launches += 4
         self.ext.moe_route(logits, n_parts, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, bn, r.ids, r.wts, r.sg, counts,
                            r.pos, r.offsets, r.tasks, r.meta, r.max_tasks, r.row_token, r.slot_row)
         return r
 
     def moe_experts(self, mw, h, r, phase: str = "prefill"):
+        """Expert outputs y (bf16) in the global row layout.  With a symmetric arena the down-projection
+        epilogue stores the rows of this rank's routed experts into every rank's buffer (shared-expert
+        rows stay local) and the combine kernel waits for all ranks; otherwise y is a plain tensor and
+        ``owned`` tells the baseline collective which rows this rank produced."""
         H, I2 = mw.down.n, mw.gate_up.n
         if r.small:
             xs = h
@@ -205,22 +229,30 @@ class CudaOps:
             self.ext.swiglu_fold(gu, r.meta, mid)
         else:
             self._gemm(xs, mw.gate_up, mid, 2, r.bn, 1, r.max_rows, I2 // 2, 0, r.tasks, r.meta, r.max_tasks)
+        if self.symm is not None:
+            ex = self.symm.ex["pairs"]
+            if r.max_rows * H > ex.half_stride:
+                raise ValueError("pass has more (token, expert) rows than the symmetric pair buffer was sized for")
+            self._gemm(mid, mw.down, ex.buffer, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks,
+                       ex=ex, local_only_from=mw.n_local)
+            r.ex = ex
+            return ex.buffer, None
         y = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
         self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks)
-        if self.tp == 1:
-            return y, None
-        # dense [T, slots, H] layout for the exchange between expert-parallel ranks
-        owned = r.slot_row >= 0
-        dense = torch.zeros(r.T, r.k + r.ns, H, dtype=torch.bfloat16, device=self.device)
-        dense[owned] = y[r.slot_row[owned].long()]
-        r.slot_row = torch.arange(r.T * (r.k + r.ns), dtype=torch.int32, device=self.device).view(r.T, r.k + r.ns)
-        return dense, owned
+        r.ex = None
+        return y, (None if self.tp == 1 else r)
 
     def combine_add_norm(self, pair_out, r, x, norm_w):
         H = x.shape[1]
         h = torch.empty(x.shape[0], H, dtype=torch.bfloat16, device=self.device) if norm_w is not None else None
         self.launches += 1
-        self.ext.combine_add_norm(pair_out.view(-1, H), r.slot_row, r.ids, r.wts, r.sg, r.k, r.ns, x, norm_w, h, self.cfg.rms_norm_eps)
+        ex = getattr(r, "ex", None)
+        if ex is not None:
+            self.ext.combine_add_norm(ex.buffer, r.slot_row, r.ids, r.wts, r.sg, r.k, r.ns, x, norm_w, h, self.cfg.rms_norm_eps,
+                                      ex.flags[ex.self_rank], ex.ranks, ex.self_rank, ex.half_stride, self.status)
+        else:
+            self.ext.combine_add_norm(pair_out.view(-1, H), r.slot_row, r.ids, r.wts, r.sg, r.k, r.ns, x, norm_w, h,
+                                      self.cfg.rms_norm_eps, 0, 0, 0, 0, None)
         return x, h
 
     # ---- head
@@ -228,12 +260,21 @@ class CudaOps:
         return self.linear(h, lm_head, out_fp32=True)
 
     def head_argmax(self, h, lm_head, vocab0: int):
+        """Greedy ids.  With a symmetric arena every rank exchanges its chunk winners and ends with the
+        same global winners (the caller's merge is then the identity)."""
         logits = self.head_logits(h, lm_head)
-        val = torch.empty(h.shape[0], dtype=torch.float32, device=self.device)
-        idx = torch.empty(h.shape[0], dtype=torch.int64, device=self.device)
+        rows = h.shape[0]
+        val = torch.empty(rows, dtype=torch.float32, device=self.device)
+        idx = torch.empty(rows, dtype=torch.int64, device=self.device)
         chunks = -(-logits.shape[1] // self.ext.argmax_chunk())
-        cv = torch.empty(h.shape[0] * chunks, dtype=torch.float32, device=self.device)
-        ci = torch.empty(h.shape[0] * chunks, dtype=torch.int32, device=self.device)
-        self.launches += 2 if chunks > 1 else 1
-        self.ext.argmax_rows(logits, vocab0, val, idx, cv, ci)
+        if self.symm is not None:
+            ex = self.symm.ex["head"]
+            if rows > self.symm.head_rows or chunks > self.symm.head_chunks:
+                raise ValueError("greedy head pass larger than the symmetric candidate table")
+            self.launches += 2
+            self.ext.argmax_rows(logits, vocab0, val, idx, None, ex.out, ex.flags, ex.local, ex.half_stride, ex.self_rank, self.status)
+            return val, idx
+        cand = torch.empty(rows * chunks, dtype=torch.int64, device=self.device)
+        self.launches += 2
+        self.ext.argmax_rows(logits, vocab0, val, idx, cand, [], [], 0, 0, 0, self.status)
         return val, idx

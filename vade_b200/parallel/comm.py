@@ -65,10 +65,20 @@ class TorchComm(LocalComm):
         self.calls["gather_partials"] += 1
         return torch.cat(self._all_gather(parts), 0)
 
-    def gather_pairs(self, pair_out: torch.Tensor, owned: torch.Tensor) -> torch.Tensor:
+    def gather_pairs(self, pair_out: torch.Tensor, owned) -> torch.Tensor:
         """pair_out [T, slots, H] holds valid rows where ``owned`` [T, slots] is true on this rank
-        (exactly one rank owns each routed slot; replicated slots are owned by every rank)."""
+        (exactly one rank owns each routed slot; replicated slots are owned by every rank).
+        On the GPU path ``owned`` is the routing record and pair_out is in the global row layout
+        [rows, H]: the rank that holds a slot's expert produced its row."""
         self.calls["gather_pairs"] += 1
+        if not isinstance(owned, torch.Tensor):
+            r = owned
+            every = torch.stack(self._all_gather(pair_out))                       # [tp, rows, H]
+            owner = (r.ids.long() // r.n_local).clamp_(max=self.tp - 1)           # [T, k]
+            owner = torch.cat([owner, torch.full((r.T, r.ns), self.rank, dtype=torch.int64, device=owner.device)], 1)
+            dense = every[owner, r.slot_row.long()]                               # [T, slots, H]
+            r.slot_row = torch.arange(r.T * (r.k + r.ns), dtype=torch.int32, device=dense.device).view(r.T, r.k + r.ns)
+            return dense
         outs = self._all_gather(pair_out)
         masks = self._all_gather(owned.to(torch.uint8))
         full = pair_out.clone()
@@ -100,3 +110,18 @@ class TorchComm(LocalComm):
 
     def barrier(self) -> None:
         dist.barrier(group=self.group)
+
+
+class FusedComm(TorchComm):
+    """Group whose hot exchanges are fused into the kernels (parallel/symm.py): the GEMM epilogues
+    store into every rank's buffers and the consumer kernels wait, so the three exchanges are
+    identities here.  Full-logit gathers (host sampling) still use the process group."""
+
+    def gather_partials(self, parts):
+        return parts
+
+    def gather_pairs(self, pair_out, owned):
+        return pair_out
+
+    def merge_argmax(self, val, idx):
+        return val, idx

@@ -13,11 +13,11 @@ from .cache import Cache
 from .engine import Engine
 
 
-def make_ops(cfg: ModelConfig, device, act: torch.dtype, reference: bool = False, tp: int = 1):
+def make_ops(cfg: ModelConfig, device, act: torch.dtype, reference: bool = False, tp: int = 1, symm=None):
     dev = torch.device(device)
     if dev.type == "cuda" and not reference:
         from ..ops.cuda import CudaOps
-        return CudaOps(cfg, dev, tp)
+        return CudaOps(cfg, dev, tp, symm)
     return RefOps(cfg, act)
 
 
@@ -38,8 +38,15 @@ def build_engine(cfg: ModelConfig, source=None, *, device="cpu", act: torch.dtyp
             from ..checkpoint.synth import synth_state_dict, DictSource
             source = DictSource(synth_state_dict(cfg, seed))
         weights = W.load_weights(cfg, source, plan, act, dev, with_mtp, keep_rowmajor)
-    ops = make_ops(cfg, dev, act, reference_ops, tp)
     comm = comm or LocalComm()
+    symm = None
+    from ..parallel.comm import FusedComm
+    if isinstance(comm, FusedComm):
+        from ..parallel.symm import SymmArena
+        rows = max(prefill_chunk, 64)
+        symm = SymmArena(comm.group, dev, cfg.hidden_size, rows,
+                         cfg.num_experts_per_tok + cfg.shared_expert_intermediate_size // cfg.moe_intermediate_size)
+    ops = make_ops(cfg, dev, act, reference_ops, tp, symm)
     model = HybridModel(cfg, weights, plan, ops, comm)
     if pages is None:
         pages = slots * (-(-max_seq // 64))

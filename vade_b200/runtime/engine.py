@@ -66,25 +66,36 @@ class Engine:
         return x, h
 
     # ------------------------------------------------------------------ prompt
-    def prefill(self, seq: Sequence, ids: list):
+    def prefill(self, seq: Sequence, ids: list, mtp: bool = False):
         """Append prompt tokens ``ids`` to the sequence in 64-aligned tiles; returns (x, h) of the
-        LAST row only (None on non-final pipeline stages)."""
+        LAST row only (None on non-final pipeline stages).  With ``mtp`` the draft block's KV is
+        filled too: its position p holds the pair (token p + 1, trunk residual p), so each tile
+        feeds the pairs it completes, including the one that straddles the previous tile."""
         pos = len(seq.tokens)
         x = h = None
         done = 0
+        feed = mtp and self.model.w.mtp is not None and self.model.plan.last_stage
         while done < len(ids):
             room = self.prefill_chunk - (pos % self.prefill_chunk)
             n = min(room, len(ids) - done)
             self.cache.ensure(seq.slot, pos + n)
-            batch = Batch.make([(seq.slot, pos, ids[done:done + n])], self.device, "prefill")
+            tile = ids[done:done + n]
+            batch = Batch.make([(seq.slot, pos, tile)], self.device, "prefill")
             x, h = self._run(batch)
+            if feed:
+                xs, toks, p0 = x[:n - 1], list(tile[1:]), pos
+                if seq.last_x is not None and pos > 0:
+                    xs, toks, p0 = torch.cat([seq.last_x, xs], 0), [tile[0]] + toks, pos - 1
+                if toks:
+                    self.mtp_prefill(seq, toks, xs, p0)
+            if x is not None:
+                seq.last_x = x[n - 1:n].clone()
             pos += n
             done += n
-        seq.tokens += list(ids)
+            seq.tokens += list(tile)
         self.cache.length[seq.slot] = pos
         if h is None:
             return None, None
-        seq.last_x = x[-1:].clone()
         return x[-1:], h[-1:]
 
     # ------------------------------------------------------------------ decode rows
@@ -142,7 +153,7 @@ class Engine:
         can_draft = draft_depth > 0 and seq.sampling.plain_greedy and self.cfg.mtp_num_hidden_layers > 0
         use_mtp = can_draft and last and self.model.w.mtp is not None
         if use_mtp:
-            x_last, h_last = self._prefill_with_mtp(seq, prompt)
+            x_last, h_last = self.prefill(seq, prompt, mtp=True)
         else:
             x_last, h_last = self.prefill(seq, prompt)
         out = []
@@ -202,32 +213,6 @@ class Engine:
         if self.pp is None:
             return list(values)
         return self.pp.broadcast_ints(values)
-
-    def _prefill_with_mtp(self, seq: Sequence, prompt: list):
-        """Prompt pass that also fills the draft block's KV with (token p+1, residual p) pairs."""
-        pos = 0
-        x = h = None
-        pend_x = None            # residual of the last row of the previous tile
-        done = 0
-        while done < len(prompt):
-            room = self.prefill_chunk - (pos % self.prefill_chunk)
-            n = min(room, len(prompt) - done)
-            self.cache.ensure(seq.slot, pos + n)
-            batch = Batch.make([(seq.slot, pos, prompt[done:done + n])], self.device, "prefill")
-            x, h = self._run(batch)
-            # pairs inside this tile: positions pos..pos+n-2 get token at p+1; plus the pending one
-            xs, ids, p0 = x[:n - 1], prompt[done + 1:done + n], pos
-            if pend_x is not None:
-                xs, ids, p0 = torch.cat([pend_x, xs], 0), [prompt[done]] + ids, pos - 1
-            if ids:
-                self.mtp_prefill(seq, ids, xs, p0)
-            pend_x = x[n - 1:n].clone()
-            pos += n
-            done += n
-        seq.tokens += list(prompt)
-        self.cache.length[seq.slot] = pos
-        seq.last_x = pend_x
-        return x[-1:], h[-1:]
 
     def _mtp_catch_up(self, seq: Sequence, rows: list, prev_x: torch.Tensor, xs: torch.Tensor) -> None:
         """After accepting ``rows`` the draft block must hold the true pair of every trunk position

@@ -1,0 +1,402 @@
+"""Continuous-batching scheduler: the loop of the one thread that touches the GPU.
+
+Every turn ("tick") of the loop
+  1. drops cancelled / expired work,
+  2. admits queued requests (FIFO, with bounded backfill: a younger request may start only if the
+     oldest waiter would still fit beside it; priority 255 may use the reserved foreground slot),
+     charging each request the KV pages of prompt + max_tokens before it starts,
+  3. advances AT MOST ONE prompt by one 64-aligned slice (so decoding chats keep their cadence),
+  4. runs ONE decode pass over all decoding chats (one row each, or 1 + depth rows for a chat that
+     drafts with the MTP block), samples on the host, emits tokens,
+  5. finishes requests (EOS, stop ids, stop strings, max tokens), checkpoints their prompt prefix
+     into the prefix cache and releases their slot.
+
+Exactness: prompt rows always run in the prefill class and decode rows in the decode class, each
+row's arithmetic is independent of the rows beside it, and the sampler is keyed by (seed, absolute
+position), so a chat's tokens do not depend on what else is running or on prefix-cache hits.
+Parity: engine/crates/serve/src/scheduler/dispatch.rs (tick loop, admission, backfill, time
+slices), serve/src/cache.rs (prefix cache), serve/src/budget.rs (reservations).
+"""
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+from collections import OrderedDict, deque
+from dataclasses import dataclass, field
+
+import torch
+
+from ..utils import events
+from .cache import PAGE, OutOfPages
+from .engine import Engine, Sequence
+from .sampler import Sampling, sample
+
+
+@dataclass
+class SchedulerConfig:
+    max_active: int = 16                 # decoding chats per pass
+    prefill_slice: int = 2048            # rows one prompt advances per tick (multiple of 64)
+    reserve_foreground: int = 1          # slots only priority-255 requests may take
+    prefix_cache_entries: int = 16
+    prefix_cache_min_tokens: int = 64
+    request_timeout_s: float = 600.0
+    draft_depth: int = 3                 # default MTP depth when a request asks for drafting
+    max_queue: int = 256
+
+
+@dataclass
+class Request:
+    prompt: list
+    max_tokens: int = 128
+    sampling: Sampling = field(default_factory=Sampling)
+    stop_ids: tuple = ()
+    stop_strings: tuple = ()
+    ignore_eos: bool = False
+    draft: str = "plain"                 # plain | strict (exact greedy drafting)
+    mtp_depth: int = 0
+    cache: bool = False                  # opt in to the prefix cache (read and write)
+    cache_salt: str = ""
+    priority: int = 0
+    id: int = 0
+    # --- filled by the scheduler
+    state: str = "queued"                # queued | prefill | decode | done
+    seq: Sequence | None = None
+    done_prompt: int = 0
+    cached_tokens: int = 0
+    output: list = field(default_factory=list)
+    finish_reason: str | None = None
+    error: str | None = None
+    next_token: int | None = None
+    created: float = field(default_factory=time.monotonic)
+    first_token_at: float | None = None
+    drafted: int = 0
+    accepted: int = 0
+    events: deque = field(default_factory=deque)        # ("token", id) / ("done", reason) / ("error", text)
+    wake: threading.Event = field(default_factory=threading.Event)
+    cancelled: bool = False
+    pages_reserved: int = 0
+    text_tail: str = ""
+
+    def push(self, ev) -> None:
+        self.events.append(ev)
+        self.wake.set()
+
+
+class PrefixCache:
+    """Exact prompt-prefix checkpoints at 64-token boundaries: the KV pages below the boundary are
+    shared by reference, the recurrent state at the boundary is a copy.  Keys are the actual tokens
+    (plus the request's salt), compared in full before reuse."""
+
+    def __init__(self, engine: Engine, entries: int):
+        self.engine, self.capacity = engine, entries
+        self.items: OrderedDict = OrderedDict()         # (salt, tuple(tokens)) -> (donor slot, snapshot, last_x)
+        self.hits = self.misses = 0
+
+    def lookup(self, salt: str, prompt: list):
+        best = None
+        for (s, toks), val in self.items.items():
+            n = len(toks)
+            if s == salt and n <= len(prompt) - 1 and (best is None or n > len(best[0][1])) and tuple(prompt[:n]) == toks:
+                best = ((s, toks), val)
+        if best is None:
+            self.misses += 1
+            return None
+        self.items.move_to_end(best[0])
+        self.hits += 1
+        return best[0][1], best[1]
+
+    def store(self, salt: str, tokens: list, slot: int, snapshot, last_x) -> bool:
+        key = (salt, tuple(tokens))
+        if key in self.items:
+            self.items.move_to_end(key)
+            return False
+        while len(self.items) >= self.capacity:
+            self.evict_one()
+        self.items[key] = (slot, snapshot, last_x)
+        return True
+
+    def evict_one(self) -> bool:
+        if not self.items:
+            return False
+        _, (slot, _, _) = self.items.popitem(last=False)
+        self.engine.cache.free_slot(slot)
+        return True
+
+    def stats(self) -> dict:
+        return {"entries": len(self.items), "hits": self.hits, "misses": self.misses}
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, config: SchedulerConfig | None = None, eos_id: int | None = None, detokenize=None):
+        self.engine = engine
+        self.cfg = config or SchedulerConfig()
+        assert self.cfg.prefill_slice % PAGE == 0
+        self.eos_id = eos_id
+        self.detokenize = detokenize
+        self.queue: deque = deque()
+        self.active: list = []
+        self.lock = threading.Lock()
+        self.ids = itertools.count(1)
+        self.prefix = PrefixCache(engine, self.cfg.prefix_cache_entries)
+        self.stop_flag = False
+        self.ticks = 0
+        self.fatal: str | None = None
+
+    # ------------------------------------------------------------------ client side (any thread)
+    def submit(self, req: Request) -> Request:
+        req.sampling.validate()
+        limit = self.engine.cache.max_pages * PAGE
+        if len(req.prompt) < 1:
+            raise ValueError("empty prompt")
+        if len(req.prompt) + req.max_tokens > limit:
+            raise ValueError(f"prompt ({len(req.prompt)}) plus max_tokens ({req.max_tokens}) exceeds the context limit {limit}")
+        with self.lock:
+            if len(self.queue) >= self.cfg.max_queue:
+                raise OverflowError("server overloaded: request queue is full")
+            req.id = next(self.ids)
+            self.queue.append(req)
+        events.note("request_queued")
+        return req
+
+    def cancel(self, req_id: int) -> bool:
+        with self.lock:
+            for r in list(self.queue) + self.active:
+                if r.id == req_id:
+                    r.cancelled = True
+                    return True
+        return False
+
+    def snapshot(self) -> dict:
+        c = self.engine.cache
+        return {"active": len(self.active), "queued": len(self.queue), "free_slots": len(c.free_slots),
+                "free_pages": c.alloc.available, "total_pages": c.alloc.total, "prefix_cache": self.prefix.stats(),
+                "ticks": self.ticks}
+
+    # ------------------------------------------------------------------ engine thread
+    def run_forever(self, idle_sleep: float = 0.001) -> None:
+        try:
+            while not self.stop_flag:
+                if not self.tick():
+                    time.sleep(idle_sleep)
+        except Exception as e:                              # a failed pass invalidates every participant
+            self.fatal = f"{type(e).__name__}: {e}"
+            events.note("engine_fatal", self.fatal)
+            for r in list(self.active) + list(self.queue):
+                r.error = self.fatal
+                r.push(("error", self.fatal))
+            raise
+
+    def stop(self) -> None:
+        self.stop_flag = True
+
+    def tick(self) -> bool:
+        self.ticks += 1
+        self._reap()
+        self._admit()
+        worked = self._prefill_one()
+        worked = self._decode_pass() or worked
+        return worked
+
+    # ---- 1. cancellations and deadlines
+    def _reap(self) -> None:
+        now = time.monotonic()
+        for r in list(self.active):
+            if r.cancelled:
+                self._finish(r, "cancelled")
+            elif now - r.created > self.cfg.request_timeout_s:
+                self._finish(r, "deadline")
+        with self.lock:
+            for r in list(self.queue):
+                if r.cancelled:
+                    self.queue.remove(r)
+                    r.finish_reason = "cancelled"
+                    r.push(("done", "cancelled"))
+
+    # ---- 2. admission
+    def _pages_for(self, r: Request) -> int:
+        return -(-(len(r.prompt) + r.max_tokens + 1) // PAGE)
+
+    def _fits(self, r: Request, slots_free: int, pages_free: int) -> bool:
+        reserve = 0 if r.priority >= 255 else self.cfg.reserve_foreground
+        return slots_free - reserve >= 1 and pages_free >= self._pages_for(r)
+
+    def _admit(self) -> None:
+        c = self.engine.cache
+        while True:
+            with self.lock:
+                if not self.queue or len(self.active) >= self.cfg.max_active:
+                    return
+                head = self.queue[0]
+                slots_free = len(c.free_slots)
+                pages_free = c.alloc.available - sum(max(0, x.pages_reserved - self._pages_used(x)) for x in self.active)
+                pick = None
+                if self._fits(head, slots_free, pages_free):
+                    pick = head
+                else:
+                    # reclaim retained prefixes first, then bounded backfill behind the head
+                    if self.prefix.evict_one():
+                        continue
+                    need_s, need_p = 1, self._pages_for(head)
+                    for cand in list(self.queue)[1:]:
+                        if self._fits(cand, slots_free - need_s, pages_free - need_p):
+                            pick = cand
+                            break
+                if pick is None:
+                    return
+                self.queue.remove(pick)
+            self._start(pick)
+
+    def _pages_used(self, r: Request) -> int:
+        return -(-len(r.seq.tokens) // PAGE) if r.seq is not None else 0
+
+    def _start(self, r: Request) -> None:
+        c = self.engine.cache
+        r.seq = Sequence(c.new_slot(), [], len(r.prompt), r.sampling)
+        r.pages_reserved = self._pages_for(r)
+        r.state = "prefill"
+        hit = self.prefix.lookup(r.cache_salt, r.prompt) if r.cache else None
+        if hit is not None:
+            toks, (donor, snap, last_x) = hit
+            c.share_prefix(donor, r.seq.slot, len(toks))
+            for i, st in snap.gdn.items():
+                c.gdn_state[i][r.seq.slot].copy_(st)
+            for i, hh in snap.conv.items():
+                c.conv_hist[i][r.seq.slot].copy_(hh)
+            r.seq.tokens = list(toks)
+            r.seq.last_x = last_x
+            r.done_prompt = r.cached_tokens = len(toks)
+            events.note("prefix_cache_hit")
+        self.active.append(r)
+        events.note("request_admitted")
+
+    # ---- 3. one prompt slice
+    def _prefill_one(self) -> bool:
+        for r in self.active:
+            if r.state != "prefill":
+                continue
+            eng = self.engine
+            pos = r.done_prompt
+            total = len(r.prompt)
+            # cut at the slice grid and at the last 64-boundary below the prompt end (the checkpoint)
+            boundary = (total - 1) // PAGE * PAGE
+            end = min(total, (pos // self.cfg.prefill_slice + 1) * self.cfg.prefill_slice)
+            if pos < boundary < end:
+                end = boundary
+            ids = r.prompt[pos:end]
+            x, h = eng.prefill(r.seq, ids, mtp=(r.draft == "strict"))
+            r.done_prompt = end
+            if end == boundary and r.cache and boundary >= self.cfg.prefix_cache_min_tokens and r.cached_tokens < boundary:
+                self._checkpoint(r, boundary)
+            if end == total:
+                r.next_token = eng.choose(r.seq, h, total)
+                r.state = "decode"
+                r.first_token_at = time.monotonic()
+            return True
+        return False
+
+    def _checkpoint(self, r: Request, boundary: int) -> None:
+        """Keep the prompt prefix [0, boundary): a retained donor slot shares the KV pages, the
+        recurrent state is copied."""
+        c = self.engine.cache
+        try:
+            donor = c.new_slot()
+        except OutOfPages:
+            return
+        c.share_prefix(r.seq.slot, donor, boundary)
+        snap = c.snapshot(r.seq.slot)
+        last_x = r.seq.last_x.clone() if r.seq.last_x is not None else None
+        if not self.prefix.store(r.cache_salt, r.prompt[:boundary], donor, snap, last_x):
+            c.free_slot(donor)
+
+    # ---- 4. one decode pass
+    def _decode_pass(self) -> bool:
+        rows_of = [r for r in self.active if r.state == "decode"]
+        if not rows_of:
+            return False
+        eng = self.engine
+        # emit the tokens chosen last turn; requests that end here leave before the pass
+        for r in list(rows_of):
+            if self._emit(r, r.next_token):
+                rows_of.remove(r)
+        if not rows_of:
+            return True
+        solo_draft = (len(rows_of) == 1 and rows_of[0].draft == "strict" and rows_of[0].sampling.plain_greedy
+                      and eng.model.w.mtp is not None)
+        if solo_draft:
+            self._draft_cycle(rows_of[0])
+            return True
+        x, h = eng.step([r.seq for r in rows_of], [[r.next_token] for r in rows_of])
+        greedy = None
+        if all(r.sampling.plain_greedy for r in rows_of):
+            greedy = [int(t) for t in eng.model.greedy(h)]
+        for i, r in enumerate(rows_of):
+            r.seq.tokens.append(r.next_token)
+            eng.cache.length[r.seq.slot] = len(r.seq.tokens)
+            r.seq.last_x = x[i:i + 1]
+            if greedy is not None:
+                r.next_token = greedy[i]
+            else:
+                r.next_token = eng.choose(r.seq, h[i:i + 1], len(r.seq.tokens))
+        return True
+
+    def _draft_cycle(self, r: Request) -> None:
+        """Exact greedy drafting for a lone chat: MTP proposes, the trunk verifies, the longest
+        matching prefix is kept (engine/crates/engine/src/draft.rs:822-828)."""
+        eng = self.engine
+        seq = r.seq
+        remaining = r.max_tokens - len(r.output)
+        depth = max(0, min(r.mtp_depth or self.cfg.draft_depth, remaining - 1))
+        drafts = eng.propose(seq, r.next_token, depth) if depth > 0 else []
+        rows = [r.next_token] + drafts
+        snap = eng.cache.snapshot(seq.slot) if drafts else None
+        x, h = eng.step([seq], [rows])
+        targets = [int(t) for t in eng.model.greedy(h)]
+        keep = 1
+        while keep < len(rows) and rows[keep] == targets[keep - 1]:
+            keep += 1
+        if keep < len(rows):
+            eng.cache.restore(seq.slot, snap)
+            x, h = eng.step([seq], [rows[:keep]])
+        prev_x = seq.last_x
+        seq.tokens += rows[:keep]
+        eng.cache.length[seq.slot] = len(seq.tokens)
+        eng._mtp_catch_up(seq, rows[:keep], prev_x, x[:keep])
+        seq.last_x = x[keep - 1:keep].clone()
+        r.drafted += len(drafts)
+        r.accepted += keep - 1
+        for t in rows[1:keep]:
+            if self._emit(r, t):
+                return
+        r.next_token = targets[keep - 1]
+
+    # ---- 5. emit / finish
+    def _emit(self, r: Request, tok: int) -> bool:
+        """Hands one token to the client; returns True when the request finished."""
+        is_eos = self.eos_id is not None and tok == self.eos_id and not r.ignore_eos
+        if is_eos or tok in r.stop_ids:
+            self._finish(r, "stop")
+            return True
+        r.output.append(tok)
+        r.push(("token", tok))
+        if r.stop_strings and self.detokenize is not None:
+            r.text_tail = (r.text_tail + self.detokenize([tok]))[-256:]
+            if any(s and s in r.text_tail for s in r.stop_strings):
+                self._finish(r, "stop")
+                return True
+        if len(r.output) >= r.max_tokens:
+            self._finish(r, "length")
+            return True
+        return False
+
+    def _finish(self, r: Request, reason: str) -> None:
+        if r.state == "done":
+            return
+        r.state = "done"
+        r.finish_reason = reason
+        if r in self.active:
+            self.active.remove(r)
+        if r.seq is not None:
+            self.engine.cache.free_slot(r.seq.slot)
+        r.push(("done", reason))
+        events.note("request_finished")

@@ -1,0 +1,51 @@
+"""Environment switches, read once with strict parsing: an invalid value is a start-up error,
+never a silent default (engine/crates/engine/src/flash/draft_stack.rs:40-108)."""
+from __future__ import annotations
+
+import os
+
+_cache: dict = {}
+
+
+class EnvError(ValueError):
+    pass
+
+
+def _get(name: str, parse, default):
+    if name in _cache:
+        return _cache[name]
+    raw = os.environ.get(name)
+    if raw is None:
+        val = default
+    else:
+        try:
+            val = parse(raw.strip())
+        except (ValueError, KeyError):
+            raise EnvError(f"{name}={raw!r} is not a valid value") from None
+    _cache[name] = val
+    return val
+
+
+def flag(name: str, default: bool = False) -> bool:
+    return _get(name, lambda s: {"1": True, "0": False, "true": True, "false": False}[s.lower()], default)
+
+
+def integer(name: str, default: int, lo: int | None = None, hi: int | None = None) -> int:
+    def parse(s):
+        v = int(s)
+        if (lo is not None and v < lo) or (hi is not None and v > hi):
+            raise ValueError
+        return v
+    return _get(name, parse, default)
+
+
+def choice(name: str, options: tuple, default: str) -> str:
+    def parse(s):
+        if s not in options:
+            raise ValueError
+        return s
+    return _get(name, parse, default)
+
+
+def clear_cache() -> None:
+    _cache.clear()
