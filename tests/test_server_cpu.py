@@ -1,0 +1,101 @@
+"""The real HTTP server + scheduler on loopback, driving the tiny fp32 model on CPU."""
+import json
+import threading
+import urllib.request
+
+import pytest
+import torch
+
+from vade_b200.config import tiny_config
+from vade_b200.checkpoint.synth import write_checkpoint
+from vade_b200.runtime.build import load_engine
+from vade_b200.runtime.scheduler import Scheduler, SchedulerConfig
+from vade_b200.serve.http import ApiServer
+
+
+@pytest.fixture(scope="module")
+def server(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("ckpt"))
+    write_checkpoint(tiny_config(), root, seed=0, dtype=torch.float32)
+    eng, tok, receipt = load_engine(root, slots=8, max_seq=512, prefill_chunk=64)
+    sched = Scheduler(eng, SchedulerConfig(prefill_slice=64, max_active=6), eos_id=tok.eos_id, detokenize=tok.decode)
+    api = ApiServer(sched, tok, "tiny", {"checkpoint": receipt["fingerprint"], "world": 1})
+    port = api.start()
+    yield api, port, eng, tok
+    api.stop()
+
+
+def _post(port, path, obj, stream=False):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", json.dumps(obj).encode(), {"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        raw = r.read().decode()
+    if not stream:
+        return json.loads(raw)
+    return [json.loads(l[6:]) for l in raw.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+
+
+def _ids(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 4000, (n,), generator=g).tolist()
+
+
+def test_completion_matches_engine_and_streams_token_ids(server):
+    api, port, eng, tok = server
+    prompt = _ids(70, 1)
+    body = {"prompt": prompt, "max_tokens": 12, "ignore_eos": True, "draft": "plain"}
+    out = _post(port, "/v1/completions", body)
+    got = out["choices"][0]["token_ids"]
+    assert len(got) == 12 and out["usage"]["completion_tokens"] == 12
+    assert out["vade"]["sampling"]["temperature"] == 0.0 and out["vade"]["greedy_if_unsampled"]
+    chunks = _post(port, "/v1/completions", {**body, "stream": True}, stream=True)
+    assert [c["choices"][0]["token_id"] for c in chunks if c["choices"] and "token_id" in c["choices"][0]] == got
+
+
+def test_concurrent_requests_match_their_solo_runs(server):
+    api, port, eng, tok = server
+    prompts = [_ids(40 + 13 * i, 10 + i) for i in range(4)]
+    solo = [_post(port, "/v1/completions", {"prompt": p, "max_tokens": 8, "ignore_eos": True, "draft": "plain"})["choices"][0]["token_ids"] for p in prompts]
+    res = [None] * 4
+
+    def run(i):
+        res[i] = _post(port, "/v1/completions", {"prompt": prompts[i], "max_tokens": 8, "ignore_eos": True, "draft": "plain"})["choices"][0]["token_ids"]
+    ts = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert res == solo
+
+
+def test_sampled_request_is_reproducible_by_seed(server):
+    api, port, eng, tok = server
+    body = {"prompt": _ids(30, 5), "max_tokens": 10, "temperature": 0.8, "top_p": 0.95, "seed": 1234, "ignore_eos": True}
+    a = _post(port, "/v1/completions", body)["choices"][0]["token_ids"]
+    b = _post(port, "/v1/completions", body)["choices"][0]["token_ids"]
+    assert a == b
+
+
+def test_prefix_cache_hit_and_drafting_keep_tokens(server):
+    api, port, eng, tok = server
+    prompt = _ids(150, 7)
+    base = {"prompt": prompt, "max_tokens": 10, "ignore_eos": True}
+    cold = _post(port, "/v1/completions", {**base, "draft": "plain", "cache": True})
+    hit = _post(port, "/v1/completions", {**base, "draft": "plain", "cache": True})
+    assert hit["usage"]["prompt_tokens_details"]["cached_tokens"] == 128
+    assert hit["choices"][0]["token_ids"] == cold["choices"][0]["token_ids"]
+    spec = _post(port, "/v1/completions", {**base, "draft": "strict"})
+    assert spec["choices"][0]["token_ids"] == cold["choices"][0]["token_ids"]
+    assert spec["vade"]["draft_used"] and spec["vade"]["drafted"] > 0
+
+
+def test_chat_route_health_and_errors(server):
+    api, port, eng, tok = server
+    out = _post(port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4})
+    assert out["choices"][0]["message"]["role"] == "assistant" and out["usage"]["completion_tokens"] <= 4
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=10) as r:
+        health = json.loads(r.read())
+    assert health["status"] == "ok" and "free_pages" in health
+    with pytest.raises(urllib.error.HTTPError) as e:
+        _post(port, "/v1/completions", {"prompt": [1, 2], "max_tokens": 4, "temperature": -1})
+    assert e.value.code == 400 and "error" in json.loads(e.value.read())
+    with pytest.raises(urllib.error.HTTPError) as e:
+        _post(port, "/v1/nope", {})
+    assert e.value.code == 404

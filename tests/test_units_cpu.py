@@ -1,0 +1,226 @@
+"""Host-side unit tests: number formats, checkpoint files, ownership plan, sampler, routing policy."""
+import json
+import os
+
+import pytest
+import torch
+
+from vade_b200.checkpoint import manifest, safetensors as st
+from vade_b200.checkpoint.synth import write_checkpoint, synth_state_dict, tensor_inventory
+from vade_b200.config import ModelConfig, tiny_config, qwen3_next_80b_config, RANGES
+from vade_b200.models import weights as W
+from vade_b200.ops import reference as R
+from vade_b200.parallel.plan import make_plan, partition
+from vade_b200.quant import codecs
+from vade_b200.runtime import sampler as S
+from vade_b200.serve import protocol as P
+from vade_b200.serve.gateway import affinity_key
+from vade_b200.serve.tokenizer import ByteTokenizer, StreamDecoder, render_chat, TokenizerError
+
+
+def test_e2m1_codes_round_trip_and_ties_go_to_even():
+    codes = torch.arange(16, dtype=torch.uint8)
+    vals = codecs.e2m1_decode(codes)
+    back = codecs.e2m1_encode(vals)
+    assert torch.equal(back[1:8], codes[1:8]) and torch.equal(back[9:], codes[9:])
+    # ties: 0.25 -> 0, 0.75 -> 1.0, 1.25 -> 1.0, 1.75 -> 2.0, 2.5 -> 2, 3.5 -> 4, 5 -> 4
+    got = codecs.e2m1_decode(codecs.e2m1_encode(torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 100.0])))
+    assert got.tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0]
+
+
+def test_nvfp4_block_values_are_exact_in_bf16_and_scale_order():
+    w = torch.randn(64, 128) * 0.05
+    p, s, g = codecs.nvfp4_quantize(w)
+    bv = codecs.nvfp4_block_values(p, s)
+    assert torch.equal(bv.to(torch.bfloat16).float(), bv)              # <= 6 significant bits
+    deq = codecs.nvfp4_dequantize(p, s, g)
+    assert torch.equal(deq, bv * g)                                    # block scale first, tensor scale second
+    assert (deq - w).abs().max() < 0.3 * w.abs().max()
+
+
+def test_fp8_block_and_activation_quant():
+    w = torch.randn(130, 260)
+    q, sc = codecs.fp8_block_quantize_weight(w)
+    assert sc.shape == (2, 3)
+    assert (codecs.fp8_block_dequantize_weight(q, sc) - w).abs().max() < 0.08 * w.abs().max()
+    x = torch.randn(3, 256)
+    x[1, :128] = 0
+    qa, sa = codecs.fp8_quantize_activation(x)
+    assert sa[1, 0] == 0 and (codecs.fp8_dequantize_activation(qa, sa) - x).abs().max() < 0.07 * x.abs().max()
+
+
+def test_mxfp8_and_ue8m0():
+    assert codecs.ue8m0_decode(torch.tensor([127, 128, 126], dtype=torch.uint8)).tolist() == [1.0, 2.0, 0.5]
+    vals = codecs.e4m3_encode(torch.ones(2, 32))
+    assert torch.equal(codecs.mxfp8_dequantize(vals, torch.tensor([[128], [126]], dtype=torch.uint8)), torch.cat([torch.full((1, 32), 2.0), torch.full((1, 32), 0.5)]))
+
+
+def test_pack_tiles_round_trip_cpu():
+    p = torch.randint(0, 256, (3, 200, 64), dtype=torch.uint8)
+    s = torch.randint(0, 256, (3, 200, 8), dtype=torch.uint8)
+    tiles = W.pack_tiles(p, s)
+    assert tiles.shape == (3, 2, 2, W.TILE_BYTES)
+    p2, s2 = W.unpack_tiles(tiles, 200)
+    assert torch.equal(p, p2) and torch.equal(s, s2)
+
+
+def test_safetensors_limits_and_range_reads(tmp_path):
+    path = str(tmp_path / "a.safetensors")
+    t = {"x": torch.arange(24, dtype=torch.float32).view(6, 4), "y": torch.ones(3, dtype=torch.bfloat16), "z": torch.tensor(2.5)}
+    st.save_file(t, path, {"k": "v"})
+    f = st.TensorFile(path)
+    assert torch.equal(f.read_range("x", 2, 4), t["x"][2:4]) and f.read("z").item() == 2.5 and f.header.metadata == {"k": "v"}
+    with pytest.raises(st.SafetensorsError):
+        f.read_range("x", 5, 9)
+    with pytest.raises(st.SafetensorsError):
+        st.Header.read(path, st.Limits(header_bytes=8))
+    raw = open(path, "rb").read()
+    bad = str(tmp_path / "bad.safetensors")
+    open(bad, "wb").write(raw[:-4])
+    with pytest.raises(st.SafetensorsError):
+        st.Header.read(bad)
+
+
+def test_checkpoint_directory_manifest_and_inventory(tmp_path):
+    cfg = tiny_config()
+    root = write_checkpoint(cfg, str(tmp_path / "ck"), dtype=torch.float32)
+    assert ModelConfig.load(os.path.join(root, "config.json")).hidden_size == cfg.hidden_size
+    idx = st.Index.parse(root)
+    assert all(idx.has(n) for n in tensor_inventory(cfg))
+    r1 = manifest.verify(root)
+    r2 = manifest.verify(root)
+    assert r1["hashed"] == r1["files"] and r2["cached"] == r2["files"] and r1["fingerprint"] == r2["fingerprint"]
+    shard = os.path.join(root, idx.shards[0])
+    with open(shard, "r+b") as f:
+        f.seek(-1, 2)
+        b = f.read(1)
+        f.seek(-1, 2)
+        f.write(bytes([b[0] ^ 1]))
+    with pytest.raises(manifest.ManifestError):
+        manifest.verify(root)
+
+
+def test_quantized_synth_checkpoint_has_sidecars():
+    cfg = tiny_config()
+    cfg.quant.method = "nvfp4"
+    sd = synth_state_dict(cfg)
+    n = "model.language_model.layers.0.mlp.experts.0.gate_proj.weight"
+    assert sd[n].dtype == torch.uint8 and n + "_scale" in sd and sd[n + "_scale_2"].dim() == 0
+    assert sd["model.language_model.layers.0.mlp.gate.weight"].dtype == torch.float32      # router stays plain
+
+
+def test_plan_ownership():
+    cfg = qwen3_next_80b_config()
+    assert partition(10, 3, 0) == (0, 4) and partition(10, 3, 2) == (7, 10)
+    for tp in (1, 2, 4, 8):
+        plans = [make_plan(cfg, tp, r) for r in range(tp)]
+        assert [p.q_heads for p in plans][-1][1] == cfg.num_attention_heads
+        assert sum(p.experts[1] - p.experts[0] for p in plans) == cfg.num_experts
+        assert sum(p.ranges[1] - p.ranges[0] for p in plans) == RANGES
+        for p in plans:       # a rank's query heads sit under the KV head(s) it holds
+            g = cfg.num_attention_heads // cfg.num_key_value_heads
+            assert p.kv_heads[0] <= p.q_heads[0] // g and (p.q_heads[1] - 1) // g < p.kv_heads[1]
+    with pytest.raises(ValueError):
+        make_plan(cfg, 3, 0)
+    pp = [make_plan(cfg, 1, 0, 4, s).layers for s in range(4)]
+    assert pp[0][0] == 0 and pp[-1][1] == 48 and all(a[1] == b[0] for a, b in zip(pp, pp[1:]))
+
+
+def test_fold_tree_is_the_fixed_pair_tree():
+    p = torch.randn(8, 5)
+    want = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]))
+    assert torch.equal(R.fold_tree(p), want)
+
+
+def test_chunked_gdn_equals_token_recurrence():
+    T, kh, vh, d = 150, 2, 4, 16
+    g = torch.Generator().manual_seed(0)
+    q = R.l2norm(torch.randn(T, kh, d, generator=g)) * d ** -0.5
+    k = R.l2norm(torch.randn(T, kh, d, generator=g))
+    v = torch.randn(T, vh, d, generator=g)
+    beta = torch.sigmoid(torch.randn(T, vh, generator=g))
+    gg = -torch.rand(T, vh, generator=g) * 0.5
+    s1, s2 = torch.zeros(1, vh, d, d), torch.zeros(1, vh, d, d)
+    o1 = R.gdn_recurrent(q, k, v, beta, gg, s1, [0], [0, T])
+    o2 = R.gdn_chunked(q, k, v, beta, gg, s2, [0], [0, T], [0])
+    assert torch.allclose(o1, o2, atol=2e-5) and torch.allclose(s1, s2, atol=2e-5)
+    # any cut at multiples of 64 gives the same bytes as one call
+    s3 = torch.zeros(1, vh, d, d)
+    o3 = torch.cat([R.gdn_chunked(q[:64], k[:64], v[:64], beta[:64], gg[:64], s3, [0], [0, 64], [0]),
+                    R.gdn_chunked(q[64:], k[64:], v[64:], beta[64:], gg[64:], s3, [0], [0, T - 64], [64])])
+    assert torch.equal(o2, o3) and torch.equal(s2, s3)
+
+
+def test_route_ties_and_ordered_combine():
+    logits = torch.zeros(1, 8)
+    logits[0, 5] = logits[0, 2] = 1.0
+    ids, w = R.route_topk(logits, 3, True)
+    assert ids.tolist() == [[2, 5, 0]] and abs(float(w.sum()) - 1) < 1e-6
+    y = torch.randn(1, 3, 4)
+    out = R.moe_combine(y, torch.tensor([[7, 1, 4]]), torch.tensor([[0.5, 0.25, 0.25]]))
+    want = ((torch.zeros(4) + 0.25 * y[0, 1]) + 0.25 * y[0, 2]) + 0.5 * y[0, 0]
+    assert torch.equal(out[0], want)
+
+
+def test_sampler_is_position_keyed_and_batch_invariant():
+    assert S.uniform(1, 5) == S.uniform(1, 5) != S.uniform(1, 6)
+    assert 0.0 <= S.uniform(2 ** 63, 10 ** 9) < 1.0
+    logits = torch.randn(1000)
+    s = S.Sampling(temperature=0.8, top_k=50, top_p=0.9, seed=7)
+    a = [S.sample(logits, s, p) for p in range(20)]
+    b = [S.sample(logits, s, p) for p in reversed(range(20))][::-1]
+    assert a == b and len(set(a)) > 1
+    tie = torch.zeros(10)
+    tie[3] = tie[7] = 2.0
+    assert S.sample(tie, S.Sampling(), 0) == 3
+    ids, w = S.candidates(torch.tensor([0.0, 3.0, 3.0, 1.0]), S.Sampling(temperature=1.0, top_k=3))
+    assert ids.tolist() == [1, 2, 3] and float(w[0]) == 1.0
+    with pytest.raises(ValueError):
+        S.Sampling(top_p=0.0).validate()
+    pen = S.apply_penalties(torch.tensor([2.0, -2.0, 1.0]), [0, 0, 1], S.Sampling(repetition_penalty=2.0, frequency_penalty=0.5))
+    assert pen.tolist() == [0.0, -4.5, 1.0]
+
+
+def test_protocol_policy_and_parsers():
+    d = S.Sampling(temperature=0.7, top_p=0.8)
+    r = P.parse_request("/v1/completions", json.dumps({"prompt": "hi"}).encode(), d, 100)
+    assert r.sampling.temperature == 0.0 and not r.sampled and r.max_tokens == 100
+    r = P.parse_request("/v1/chat/completions", json.dumps({"messages": [{"role": "user", "content": "x"}], "top_p": 0.5, "max_tokens": 7,
+                                                             "stop": "END", "draft": "plain"}).encode(), d, 100)
+    assert r.sampling.temperature == 0.7 and r.sampling.top_p == 0.5 and r.max_tokens == 7 and r.stop == ("END",) and r.sampled
+    for bad in ({"prompt": 5}, {"prompt": "x", "stop": ["a"] * 5}, {"prompt": "x", "temperature": "hot"}, {"prompt": "x", "draft": "maybe"}):
+        with pytest.raises(P.ApiError):
+            P.parse_request("/v1/completions", json.dumps(bad).encode(), d, 100)
+    with pytest.raises(P.ApiError) as e:
+        P.parse_request("/v1/none", b"{}", d, 100)
+    assert e.value.status == 404
+    p = P.ChatOutputParser()
+    out = []
+    for piece in ["<thi", "nk>plan</think>Hello <tool", "_call>{\"name\": \"f\", \"arguments\": {\"a\": 1}}</tool_call> bye <tool_call>oops</tool_call>"]:
+        out += p.feed(piece)
+    out += p.feed("", final=True)
+    kinds = [k for k, _ in out]
+    assert kinds[0] == "reasoning" and ("tool_call", {"name": "f", "arguments": "{\"a\": 1}"}) in out
+    assert any(k == "content" and "oops" in v for k, v in out)       # malformed call stays ordinary content
+
+
+def test_tokenizer_chat_template_and_stream_decoder():
+    tok = ByteTokenizer(4096, {"<|im_start|>": 4092, "<|im_end|>": 4093, "<think>": 4095})
+    text = render_chat([{"role": "system", "content": "s"}, {"role": "user", "content": "héllo"}], tok)
+    ids = tok.encode(text)
+    assert ids[0] == 4092 and tok.decode(ids) == text and text.endswith("<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    with pytest.raises(TokenizerError):
+        render_chat([{"role": "wizard", "content": "x"}], tok)
+    with pytest.raises(TokenizerError):
+        render_chat([{"role": "user", "content": "x"}], ByteTokenizer(300, {}))
+    dec = StreamDecoder(tok)
+    pieces = [dec.feed(b) for b in "é€".encode()]
+    assert "".join(pieces) + dec.flush() == "é€" and pieces[0] == ""
+
+
+def test_gateway_affinity_key():
+    a = affinity_key(json.dumps({"prompt_cache_key": "chat-1", "prompt": "x"}).encode())
+    assert a == affinity_key(json.dumps({"prompt_cache_key": "chat-1", "prompt": "y"}).encode())
+    m1 = affinity_key(json.dumps({"messages": [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}, {"role": "user", "content": "later"}]}).encode())
+    m2 = affinity_key(json.dumps({"messages": [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}]}).encode())
+    assert m1 == m2 and affinity_key(b"{\"prompt\": \"short\"}") is None

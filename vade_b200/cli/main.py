@@ -1,0 +1,247 @@
+"""``python -m vade_b200.cli.main <command>``: the operator's tool.
+
+    synth    write a random-init checkpoint directory of a named configuration
+    inspect  validate a checkpoint directory header-first and print its contract summary
+    serve    start the OpenAI-compatible server on one process (one GPU, or CPU for tiny models)
+    verify   exactness check against a running server: n runs x {drafting off, on}, every token id
+    bench    TTFT / decode rate / concurrent-chat throughput of a running server, over HTTP
+    doctor   environment report (GPU, extension, peer access)
+    gateway  loopback relay in front of several replicas with prefix-affinity routing
+
+Parity: cli/README.md:24-53 (command set), cli/src/verify/mod.rs:53-84,284-480 (verify),
+engine/tools/bench/README.md:24-70 (bench).
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+import urllib.error
+import urllib.request
+
+
+def _post(url: str, obj: dict, timeout: float = 600.0, key: str | None = None):
+    hdr = {"Content-Type": "application/json"}
+    if key:
+        hdr["Authorization"] = "Bearer " + key
+    req = urllib.request.Request(url, json.dumps(obj).encode(), hdr)
+    return urllib.request.urlopen(req, timeout=timeout)
+
+
+def _stream_ids(url: str, body: dict, key: str | None = None):
+    """Posts a streaming completion; returns (token ids, seconds to first token, total seconds, last chunk)."""
+    t0 = time.perf_counter()
+    ttft, ids, last = None, [], {}
+    with _post(url, {**body, "stream": True}, key=key) as r:
+        for raw in r:
+            line = raw.decode().strip()
+            if not line.startswith("data: ") or line == "data: [DONE]":
+                continue
+            ch = json.loads(line[6:])
+            last = ch
+            for c in ch.get("choices", []):
+                if "token_id" in c:
+                    if ttft is None:
+                        ttft = time.perf_counter() - t0
+                    ids.append(c["token_id"])
+    return ids, ttft, time.perf_counter() - t0, last
+
+
+# ------------------------------------------------------------------ commands
+def cmd_synth(a) -> int:
+    import torch
+    from ..checkpoint.synth import write_checkpoint
+    from ..config import NAMED_CONFIGS
+    cfg = NAMED_CONFIGS[a.config](a.quant) if a.config != "tiny" else NAMED_CONFIGS["tiny"]()
+    write_checkpoint(cfg, a.out, seed=a.seed, dtype=torch.float32 if a.config == "tiny" else torch.bfloat16)
+    print(f"wrote {a.out}")
+    return 0
+
+
+def cmd_inspect(a) -> int:
+    from ..checkpoint import manifest
+    from ..checkpoint.safetensors import Index
+    from ..checkpoint.synth import tensor_inventory, is_quantized
+    from ..config import ModelConfig
+    cfg = ModelConfig.load(os.path.join(a.root, "config.json"))
+    idx = Index.parse(a.root)
+    idx.inspect_shards()
+    inv = tensor_inventory(cfg)
+    missing = [n for n in inv if not idx.has(n)]
+    wrong = []
+    for n, (shape, kind) in inv.items():
+        if idx.has(n) and not is_quantized(cfg, n, kind) and tuple(idx.info(n).shape) != tuple(shape):
+            wrong.append((n, tuple(idx.info(n).shape), tuple(shape)))
+    out = {"model_type": cfg.model_type, "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size, "experts": cfg.num_experts,
+           "quant": cfg.quant.method, "tensors": len(list(idx.names())), "shards": len(idx.shards), "missing": missing[:5],
+           "wrong_shape": wrong[:5]}
+    if os.path.exists(os.path.join(a.root, manifest.MANIFEST)):
+        out["manifest"] = manifest.verify(a.root)
+    print(json.dumps(out, indent=1))
+    return 1 if (missing or wrong) else 0
+
+
+def cmd_serve(a) -> int:
+    import torch
+    from ..runtime.build import load_engine
+    from ..runtime.scheduler import Scheduler, SchedulerConfig
+    from ..serve.http import ApiServer
+    from ..ops import _ext
+    device = a.device or ("cuda:0" if torch.cuda.is_available() else "cpu")
+    eng, tok, receipt = load_engine(a.model, device=device, slots=a.slots + 1 + a.cache_entries, max_seq=a.context,
+                                    prefill_chunk=a.prefill_chunk)
+    sched = Scheduler(eng, SchedulerConfig(max_active=a.slots, prefill_slice=a.prefill_chunk, prefix_cache_entries=a.cache_entries),
+                      eos_id=tok.eos_id, detokenize=tok.decode)
+    key = open(a.api_key_file).read().strip() if a.api_key_file else None
+    info = {"checkpoint": {"sha256": receipt.get("fingerprint")}, "world": 1, "device": device,
+            "numerics": {"path": eng.model.ops.name, "weights": eng.cfg.quant.method},
+            "build": {"extension": os.path.basename(_ext.so_path()) if device != "cpu" else None}}
+    api = ApiServer(sched, tok, os.path.basename(os.path.abspath(a.model)), info, max_output=a.max_output, api_key=key)
+    port = api.start(a.host, a.port, allow_remote=a.allow_remote, run_engine=False)
+    print(f"listening on http://{a.host}:{port}", flush=True)
+    try:
+        sched.run_forever()          # the engine loop owns the main thread
+    except KeyboardInterrupt:
+        pass
+    finally:
+        api.stop()
+    return 0
+
+
+def cmd_verify(a) -> int:
+    """Same request, same settings => identical token ids: drafting OFF is the reference run, every
+    other run (OFF again, ON) must equal it; the ON runs must really have drafted."""
+    url = a.url.rstrip("/") + "/v1/completions"
+    body = {"prompt": a.prompt, "max_tokens": a.max_tokens, "temperature": 0, "ignore_eos": True, "cache": False}
+    first, runs, drafted_runs, diff = None, 0, 0, None
+    for run in range(1, a.runs + 1):
+        for mode in ("plain", "strict"):
+            ids, _, _, last = _stream_ids(url, {**body, "draft": mode, "stream_options": {"include_usage": True}}, a.api_key)
+            runs += 1
+            if mode == "strict" and (last.get("vade") or {}).get("draft_used"):
+                drafted_runs += 1
+            if first is None:
+                first = ids
+            elif ids != first and diff is None:
+                at = next((i for i, (x, y) in enumerate(zip(ids, first)) if x != y), min(len(ids), len(first)))
+                diff = (run, mode, at)
+    digest = hashlib.sha256(b"".join(int(t).to_bytes(4, "little") for t in (first or []))).hexdigest()
+    ok = diff is None and (drafted_runs > 0 or a.allow_undrafted)
+    line = (f"IDENTICAL: {runs}/{runs} runs, {len(first or [])} tokens, drafted in {drafted_runs} runs" if diff is None
+            else f"DIFFERENT at run {diff[0]} ({diff[1]}) token {diff[2]}")
+    if diff is None and drafted_runs == 0 and not a.allow_undrafted:
+        line += " -- FAILED: drafting was never used"
+    print(line)
+    if a.receipt:
+        tmp = a.receipt + ".tmp"
+        with open(os.open(tmp, os.O_WRONLY | os.O_CREAT | os.O_TRUNC, 0o600), "w") as f:
+            json.dump({"identical": diff is None, "runs": runs, "drafted_runs": drafted_runs, "tokens": len(first or []),
+                       "token_ids_sha256": digest, "when": time.time()}, f)
+        os.replace(tmp, a.receipt)
+    return 0 if ok else 1
+
+
+def cmd_bench(a) -> int:
+    url = a.url.rstrip("/") + "/v1/completions"
+    import random
+    rng = random.Random(20260905)
+    prompt = [rng.randrange(0, a.vocab) for _ in range(a.prompt_tokens)]
+    out = {}
+    # one chat: TTFT (uncached prompt) and decode rate
+    rates, ttfts = [], []
+    for _ in range(a.repeats):
+        ids, ttft, total, _ = _stream_ids(url, {"prompt": prompt, "max_tokens": a.max_tokens, "temperature": 0, "ignore_eos": True,
+                                                "draft": a.draft, "cache": False}, a.api_key)
+        if len(ids) != a.max_tokens:
+            print("early stop: run void", file=sys.stderr)
+            return 1
+        ttfts.append(ttft)
+        rates.append((len(ids) - 1) / max(total - ttft, 1e-9))
+    out["ttft_s"] = statistics.median(ttfts)
+    out["decode_tok_s"] = statistics.median(rates)
+    out["token_ids_sha256"] = hashlib.sha256(",".join(map(str, ids)).encode()).hexdigest()
+    # cohorts: N chats at once, total tokens / wall time
+    for n in a.cohorts:
+        res = [None] * n
+        short = [[rng.randrange(0, a.vocab) for _ in range(64)] for _ in range(n)]
+
+        def run(i):
+            res[i] = _stream_ids(url, {"prompt": short[i], "max_tokens": a.cohort_tokens, "temperature": 0, "ignore_eos": True,
+                                       "draft": "plain", "cache": False}, a.api_key)
+        t0 = time.perf_counter()
+        ts = [threading.Thread(target=run, args=(i,)) for i in range(n)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        wall = time.perf_counter() - t0
+        if any(r is None or len(r[0]) != a.cohort_tokens for r in res):
+            print(f"cohort {n}: early stop, void", file=sys.stderr)
+            return 1
+        out[f"C{n}_tok_s"] = n * a.cohort_tokens / wall
+    print(json.dumps(out))
+    return 0
+
+
+def cmd_doctor(a) -> int:
+    import torch
+    rep = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available()}
+    try:
+        from ..ops import _ext
+        rep["extension"] = os.path.exists(_ext.so_path())
+    except Exception as e:      # noqa: BLE001
+        rep["extension_error"] = str(e)
+    if torch.cuda.is_available():
+        n = torch.cuda.device_count()
+        rep["gpus"] = [torch.cuda.get_device_name(i) for i in range(n)]
+        rep["capability"] = list(torch.cuda.get_device_capability(0))
+        rep["peer_access"] = all(torch.cuda.can_device_access_peer(0, j) for j in range(1, n)) if n > 1 else None
+        rep["sm_100a_ok"] = rep["capability"][0] == 10
+    print(json.dumps(rep, indent=1))
+    return 0
+
+
+def cmd_gateway(a) -> int:
+    from ..serve.gateway import Gateway
+    gw = Gateway(a.upstream)
+    port = gw.start(a.host, a.port)
+    print(f"gateway on http://{a.host}:{port} -> {a.upstream}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        gw.stop()
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="vade_b200", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("synth"); p.add_argument("out"); p.add_argument("--config", default="tiny"); p.add_argument("--quant", default="nvfp4")
+    p.add_argument("--seed", type=int, default=0); p.set_defaults(fn=cmd_synth)
+    p = sub.add_parser("inspect"); p.add_argument("root"); p.set_defaults(fn=cmd_inspect)
+    p = sub.add_parser("serve"); p.add_argument("model"); p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--device", default=None); p.add_argument("--slots", type=int, default=16); p.add_argument("--context", type=int, default=32768)
+    p.add_argument("--prefill-chunk", type=int, default=2048); p.add_argument("--cache-entries", type=int, default=16)
+    p.add_argument("--max-output", type=int, default=16384); p.add_argument("--allow-remote", action="store_true")
+    p.add_argument("--api-key-file", default=None); p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("verify"); p.add_argument("--url", default="http://127.0.0.1:8000"); p.add_argument("--runs", type=int, default=2)
+    p.add_argument("--max-tokens", type=int, default=128); p.add_argument("--prompt", default="Write a short story about a lighthouse keeper.")
+    p.add_argument("--receipt", default=None); p.add_argument("--api-key", default=None); p.add_argument("--allow-undrafted", action="store_true")
+    p.set_defaults(fn=cmd_verify)
+    p = sub.add_parser("bench"); p.add_argument("--url", default="http://127.0.0.1:8000"); p.add_argument("--prompt-tokens", type=int, default=8192)
+    p.add_argument("--max-tokens", type=int, default=256); p.add_argument("--vocab", type=int, default=150000); p.add_argument("--repeats", type=int, default=3)
+    p.add_argument("--cohorts", type=int, nargs="*", default=[1, 4, 8]); p.add_argument("--cohort-tokens", type=int, default=256)
+    p.add_argument("--draft", default="plain"); p.add_argument("--api-key", default=None); p.set_defaults(fn=cmd_bench)
+    p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("gateway"); p.add_argument("upstream", nargs="+"); p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080); p.set_defaults(fn=cmd_gateway)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -52,3 +52,22 @@ def build_engine(cfg: ModelConfig, source=None, *, device="cpu", act: torch.dtyp
         pages = slots * (-(-max_seq // 64))
     cache = Cache(cfg, plan, slots, pages, max_seq, act, dev, mtp=with_mtp)
     return Engine(model, cache, prefill_chunk, pp_comm)
+
+
+def load_engine(root: str, **kw) -> tuple:
+    """Engine + tokenizer + checkpoint receipt from a checkpoint directory: config.json, safetensors
+    index and shards (validated header-first), sha256 manifest (verified, cached receipt), tokenizer."""
+    import os
+    from ..checkpoint import manifest
+    from ..checkpoint.safetensors import Index
+    from ..checkpoint.synth import IndexSource, tensor_inventory
+    from ..serve.tokenizer import load_tokenizer
+    cfg = ModelConfig.load(os.path.join(root, "config.json"))
+    receipt = manifest.verify(root) if os.path.exists(os.path.join(root, manifest.MANIFEST)) else {"fingerprint": None}
+    index = Index.parse(root)
+    index.inspect_shards()
+    missing = [n for n in tensor_inventory(cfg) if not index.has(n)]
+    if missing:
+        raise ValueError(f"checkpoint lacks {len(missing)} tensors, first: {missing[0]}")
+    eng = build_engine(cfg, IndexSource(index), **kw)
+    return eng, load_tokenizer(root), receipt

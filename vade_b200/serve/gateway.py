@@ -1,0 +1,132 @@
+"""Loopback relay in front of several engine replicas (data parallelism).
+
+Each replica is an independent server (one GPU or one tensor-parallel group).  The gateway relays
+requests opaquely (bodies and streams pass through unchanged) and picks the upstream by cache
+affinity: requests that carry the same ``prompt_cache_key``, or else share the same opening of
+their prompt, go to the same replica so its prefix cache keeps hitting; everything else goes to the
+replica with the fewest requests in flight.  ``GET /_vade/gateway/stats`` reports per-upstream
+counters.  Parity: harness/docs/gateway-routing.md:12-50, cli/src/app/replicas.rs:1-50.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import threading
+import urllib.error
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+
+def affinity_key(body: bytes) -> str | None:
+    try:
+        obj = json.loads(body)
+    except ValueError:
+        return None
+    if not isinstance(obj, dict):
+        return None
+    if obj.get("prompt_cache_key"):
+        return "k:" + str(obj["prompt_cache_key"])
+    if isinstance(obj.get("messages"), list) and obj["messages"]:
+        head = json.dumps(obj["messages"][:2], sort_keys=True)[:2048]
+        return "m:" + hashlib.sha256(head.encode()).hexdigest()
+    p = obj.get("prompt")
+    if isinstance(p, str) and len(p) >= 256:
+        return "p:" + hashlib.sha256(p[:1024].encode()).hexdigest()
+    if isinstance(p, list) and len(p) >= 64:
+        return "t:" + hashlib.sha256(json.dumps(p[:256]).encode()).hexdigest()
+    return None
+
+
+class Gateway:
+    def __init__(self, upstreams: list):
+        self.upstreams = [u.rstrip("/") for u in upstreams]
+        self.inflight = [0] * len(upstreams)
+        self.served = [0] * len(upstreams)
+        self.affinity_hits = 0
+        self.errors = 0
+        self.lock = threading.Lock()
+        self.httpd = None
+
+    def pick(self, body: bytes) -> int:
+        key = affinity_key(body)
+        with self.lock:
+            if key is not None:
+                self.affinity_hits += 1
+                i = int(hashlib.sha256(key.encode()).hexdigest(), 16) % len(self.upstreams)
+            else:
+                i = min(range(len(self.upstreams)), key=lambda j: (self.inflight[j], j))
+            self.inflight[i] += 1
+            self.served[i] += 1
+            return i
+
+    def stats(self) -> dict:
+        with self.lock:
+            return {"upstreams": [{"url": u, "in_flight": f, "served": s} for u, f, s in zip(self.upstreams, self.inflight, self.served)],
+                    "affinity_routed": self.affinity_hits, "errors": self.errors}
+
+    def start(self, host: str = "127.0.0.1", port: int = 0) -> int:
+        gw = self
+
+        class H(BaseHTTPRequestHandler):
+            protocol_version = "HTTP/1.1"
+
+            def log_message(self, *a):
+                pass
+
+            def _relay(self, method: str):
+                if self.path == "/_vade/gateway/stats":
+                    body = json.dumps(gw.stats()).encode()
+                    self.send_response(200); self.send_header("Content-Type", "application/json")
+                    self.send_header("Content-Length", str(len(body))); self.send_header("Connection", "close"); self.end_headers()
+                    self.wfile.write(body); self.close_connection = True
+                    return
+                n = int(self.headers.get("Content-Length", "0") or 0)
+                body = self.rfile.read(n) if n else b""
+                i = gw.pick(body) if method == "POST" else 0
+                try:
+                    hdr = {k: v for k, v in self.headers.items() if k.lower() in ("content-type", "authorization", "x-api-key", "x-session-capability")}
+                    req = urllib.request.Request(gw.upstreams[i] + self.path, body if method == "POST" else None, hdr, method=method)
+                    try:
+                        up = urllib.request.urlopen(req, timeout=900)
+                    except urllib.error.HTTPError as e:
+                        up = e
+                    self.send_response(up.status if hasattr(up, "status") else up.code)
+                    for k in ("Content-Type", "X-Sampling-Seed", "X-Request-Id", "Cache-Control"):
+                        if up.headers.get(k):
+                            self.send_header(k, up.headers[k])
+                    self.send_header("Connection", "close")
+                    self.end_headers()
+                    self.close_connection = True
+                    while True:
+                        chunk = up.read1(65536) if hasattr(up, "read1") else up.read(65536)
+                        if not chunk:
+                            break
+                        self.wfile.write(chunk)
+                        self.wfile.flush()
+                except (OSError, urllib.error.URLError):
+                    with gw.lock:
+                        gw.errors += 1
+                    try:
+                        self.send_response(502); self.send_header("Content-Length", "0"); self.send_header("Connection", "close"); self.end_headers()
+                    except OSError:
+                        pass
+                finally:
+                    if method == "POST":
+                        with gw.lock:
+                            gw.inflight[i] -= 1
+
+            def do_GET(self):
+                self._relay("GET")
+
+            def do_POST(self):
+                self._relay("POST")
+
+        self.httpd = ThreadingHTTPServer((host, port), H)
+        self.httpd.daemon_threads = True
+        threading.Thread(target=self.httpd.serve_forever, daemon=True).start()
+        return self.httpd.server_address[1]
+
+    def stop(self) -> None:
+        if self.httpd is not None:
+            self.httpd.shutdown()
+            self.httpd.server_close()

@@ -1,0 +1,311 @@
+"""OpenAI-compatible HTTP/1.1 server with server-sent events.
+
+One request per connection (``Connection: close``), ``Content-Length`` bodies only.  Connection
+threads parse, render the chat template and tokenize (the "prepare" side); the single engine thread
+runs the scheduler loop and is the only thread that touches the GPU.  Loopback bind unless remote
+access is allowed explicitly, in which case an API key is mandatory.
+Routes: POST /v1/chat/completions, /v1/completions, /v1/responses, /v1/messages,
+/v1/messages/count_tokens, /v1/admission, /v1/cancel, /v1/kv/release; GET /v1/models,
+/v1/capabilities, /v1/events, /health.
+Parity: engine/crates/serve/src/http.rs:579-582, auth.rs:150-185, scheduler.rs:121-139,
+generation.rs (stop strings, usage), docs/openai-api.md.
+"""
+from __future__ import annotations
+
+import hmac
+import json
+import threading
+import time
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+from ..runtime.sampler import Sampling
+from ..runtime.scheduler import Request, Scheduler
+from ..utils import events
+from . import protocol as P
+from .tokenizer import StreamDecoder, TokenizerError, render_chat
+
+
+class ApiServer:
+    def __init__(self, scheduler: Scheduler, tokenizer, model_name: str = "vade-b200", info: dict | None = None,
+                 defaults: Sampling | None = None, max_output: int = 16384, api_key: str | None = None):
+        self.sched, self.tok, self.model_name = scheduler, tokenizer, model_name
+        self.info = info or {}
+        self.defaults = defaults or Sampling()
+        self.max_output = max_output
+        self.api_key = api_key
+        self.httpd = None
+        self.engine_thread = None
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self, host: str = "127.0.0.1", port: int = 0, allow_remote: bool = False, run_engine: bool = True) -> int:
+        if host not in ("127.0.0.1", "localhost", "::1") and not allow_remote:
+            raise ValueError("refusing a non-loopback bind without allow_remote")
+        if allow_remote and not self.api_key:
+            raise ValueError("remote access needs an API key")
+        server = self
+
+        class Handler(BaseHTTPRequestHandler):
+            protocol_version = "HTTP/1.1"
+
+            def log_message(self, *a):
+                pass
+
+            def do_GET(self):
+                server.handle(self, "GET")
+
+            def do_POST(self):
+                server.handle(self, "POST")
+
+        self.httpd = ThreadingHTTPServer((host, port), Handler)
+        self.httpd.daemon_threads = True
+        threading.Thread(target=self.httpd.serve_forever, daemon=True).start()
+        if run_engine:
+            self.engine_thread = threading.Thread(target=self.sched.run_forever, daemon=True)
+            self.engine_thread.start()
+        events.log("serve_ready", port=self.httpd.server_address[1], model=self.model_name)
+        return self.httpd.server_address[1]
+
+    def stop(self) -> None:
+        self.sched.stop()
+        if self.httpd is not None:
+            self.httpd.shutdown()
+            self.httpd.server_close()
+
+    # ------------------------------------------------------------------ plumbing
+    @staticmethod
+    def _send(h, status: int, obj, headers: dict | None = None) -> None:
+        body = json.dumps(obj).encode()
+        h.send_response(status)
+        h.send_header("Content-Type", "application/json")
+        h.send_header("Content-Length", str(len(body)))
+        h.send_header("Connection", "close")
+        for k, v in (headers or {}).items():
+            h.send_header(k, v)
+        h.end_headers()
+        h.wfile.write(body)
+        h.close_connection = True
+
+    def _authorized(self, h) -> bool:
+        if not self.api_key:
+            return True
+        got = h.headers.get("Authorization", "")
+        key = got[7:] if got.startswith("Bearer ") else h.headers.get("x-api-key", "")
+        return hmac.compare_digest(key.encode(), self.api_key.encode())
+
+    def health(self) -> dict:
+        st = self.sched.snapshot()
+        return {"status": "failed" if self.sched.fatal else "ok", "model": self.model_name, **st,
+                "events": events.counts(), "vade": self.info, "error": self.sched.fatal}
+
+    def handle(self, h, method: str) -> None:
+        path = h.path.split("?", 1)[0]
+        try:
+            if not self._authorized(h):
+                raise P.ApiError(401, "missing or wrong API key", "authentication_error")
+            if method == "GET":
+                if path == "/health":
+                    return self._send(h, 503 if self.sched.fatal else 200, self.health())
+                if path == "/v1/models":
+                    return self._send(h, 200, {"object": "list", "data": [{"id": self.model_name, "object": "model", "owned_by": "vade-b200"}]})
+                if path == "/v1/capabilities":
+                    return self._send(h, 200, {"apis": ["chat", "completions", "responses", "messages"], "draft": ["plain", "strict"],
+                                               "context": self.sched.engine.cache.max_pages * 64, "max_output": self.max_output,
+                                               "prefix_cache": True, "token_ids": True})
+                if path == "/v1/events":
+                    return self._send(h, 200, json.loads(events.counts_json()))
+                raise P.ApiError(404, f"no route {path}", "not_found_error")
+            n = int(h.headers.get("Content-Length", "-1"))
+            if n < 0:
+                raise P.ApiError(400, "Content-Length is required")
+            if n > P.LIMIT_BODY:
+                raise P.ApiError(413, "request body too large")
+            body = h.rfile.read(n)
+            if path == "/v1/cancel":
+                rid = json.loads(body or b"{}").get("id")
+                return self._send(h, 200, {"cancelled": bool(rid is not None and self.sched.cancel(int(rid)))})
+            if path == "/v1/kv/release":
+                freed = 0
+                while self.sched.prefix.items and self.sched.prefix.evict_one():
+                    freed += 1
+                return self._send(h, 200, {"released": freed})
+            if path == "/v1/admission":
+                obj = json.loads(body or b"{}")
+                need = -(-(int(obj.get("prompt_tokens", 0)) + int(obj.get("max_tokens", 0)) + 1) // 64)
+                st = self.sched.snapshot()
+                return self._send(h, 200, {"fits": need <= st["free_pages"] and st["free_slots"] > 0, "pages_needed": need, **st})
+            if path == "/v1/messages/count_tokens":
+                req = P.parse_request("/v1/messages", json.dumps({**json.loads(body), "max_tokens": 1}).encode(), self.defaults, self.max_output)
+                return self._send(h, 200, {"input_tokens": len(self._prompt_ids(req))})
+            req = P.parse_request(path, body, self.defaults, self.max_output)
+            self._generate(h, req)
+        except P.ApiError as e:
+            self._send(h, e.status, e.body())
+        except TokenizerError as e:
+            self._send(h, 400, P.ApiError(400, str(e)).body())
+        except OverflowError as e:
+            self._send(h, 503, P.ApiError(503, str(e), "overloaded_error").body())
+        except (BrokenPipeError, ConnectionResetError):
+            pass
+        except Exception as e:                               # noqa: BLE001 - the server must answer
+            events.note("http_500", f"{type(e).__name__}: {e}")
+            try:
+                self._send(h, 500, P.ApiError(500, f"{type(e).__name__}: {e}", "server_error").body())
+            except OSError:
+                pass
+
+    # ------------------------------------------------------------------ generation
+    def _prompt_ids(self, req: P.GenRequest) -> list:
+        if req.prompt_ids is not None:
+            vocab = self.sched.engine.cfg.vocab_size
+            if any(t < 0 or t >= vocab for t in req.prompt_ids):
+                raise P.ApiError(400, "token id outside the vocabulary")
+            return req.prompt_ids
+        if req.messages is not None:
+            text = render_chat(req.messages, self.tok, True, req.enable_thinking, req.tools)
+            return self.tok.encode(text, allow_special=True)
+        ids = self.tok.encode(req.prompt_text or "", allow_special=False)
+        if not ids:
+            raise P.ApiError(400, "empty prompt")
+        return ids
+
+    def _generate(self, h, req: P.GenRequest) -> None:
+        ids = self._prompt_ids(req)
+        req.n_prompt = len(ids)
+        draft = req.draft
+        if draft == "auto":
+            draft = "strict" if (req.sampling.plain_greedy and self.sched.engine.model.w.mtp is not None) else "plain"
+        if draft == "strict" and not req.sampling.plain_greedy:
+            draft = "plain"
+        sr = Request(prompt=ids, max_tokens=req.max_tokens, sampling=req.sampling, stop_strings=req.stop,
+                     ignore_eos=req.ignore_eos, draft=draft, mtp_depth=req.mtp_depth, cache=req.cache,
+                     cache_salt=req.cache_salt + "|" + req.prompt_cache_key, priority=req.priority)
+        try:
+            self.sched.submit(sr)
+        except ValueError as e:
+            raise P.ApiError(400, str(e)) from None
+        created = int(time.time())
+        rid = P.new_id({"chat": "chatcmpl-", "completions": "cmpl-", "responses": "resp_", "messages": "msg_"}[req.api])
+        model = req.model or self.model_name
+        dec = StreamDecoder(self.tok)
+        parser = P.ChatOutputParser() if req.api != "completions" else None
+        seed_hdr = {"X-Sampling-Seed": str(req.sampling.seed), "X-Request-Id": str(sr.id)}
+        text_all, reasoning_all, calls, token_ids = [], [], [], []
+
+        def sse(obj) -> None:
+            h.wfile.write(b"data: " + json.dumps(obj).encode() + b"\n\n")
+            h.wfile.flush()
+
+        if req.stream:
+            h.send_response(200)
+            h.send_header("Content-Type", "text/event-stream")
+            h.send_header("Cache-Control", "no-cache")
+            h.send_header("Connection", "close")
+            for k, v in seed_hdr.items():
+                h.send_header(k, v)
+            h.end_headers()
+            h.close_connection = True
+            if req.api == "chat":
+                sse(P.chat_chunk(rid, model, {"role": "assistant", "content": ""}, None, None, created))
+        finish = None
+        last_beat = time.monotonic()
+        try:
+            while finish is None:
+                if not sr.events:
+                    sr.wake.wait(0.25)
+                    sr.wake.clear()
+                    if req.stream and not sr.events and time.monotonic() - last_beat > 0.25:
+                        h.wfile.write(b": heartbeat\n\n")
+                        h.wfile.flush()
+                        last_beat = time.monotonic()
+                    continue
+                kind, val = sr.events.popleft()
+                if kind == "error":
+                    raise P.ApiError(500, str(val), "server_error")
+                if kind == "done":
+                    finish = val
+                    piece = dec.flush()
+                else:
+                    token_ids.append(val)
+                    piece = dec.feed(val)
+                deltas = parser.feed(piece, final=(kind == "done")) if parser else ([("content", piece)] if piece else [])
+                for dk, dv in deltas:
+                    if dk == "content":
+                        text_all.append(dv)
+                    elif dk == "reasoning":
+                        reasoning_all.append(dv)
+                    else:
+                        calls.append(dv)
+                if req.stream and kind == "token":
+                    tid = val
+                    if req.api == "completions":
+                        sse(P.completion_chunk(rid, model, piece, None, tid, created))
+                    elif req.api == "chat":
+                        sent = False
+                        for dk, dv in deltas:
+                            delta = ({"content": dv} if dk == "content" else {"reasoning_content": dv} if dk == "reasoning" else
+                                     {"tool_calls": [{"index": len(calls) - 1, "id": P.new_id("call_"), "type": "function", "function": dv}]})
+                            sse(P.chat_chunk(rid, model, delta, None, tid if not sent else None, created))
+                            sent = True
+                        if not sent:
+                            sse(P.chat_chunk(rid, model, {}, None, tid, created))
+                    elif req.api == "messages":
+                        for dk, dv in deltas:
+                            if dk == "content":
+                                sse({"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": dv}})
+                    else:
+                        for dk, dv in deltas:
+                            if dk == "content":
+                                sse({"type": "response.output_text.delta", "delta": dv})
+        except (BrokenPipeError, ConnectionResetError):
+            self.sched.cancel(sr.id)
+            return
+        reason = {"stop": "stop", "length": "length", "cancelled": "stop", "deadline": "length"}.get(finish, "stop")
+        if finish == "cancelled":
+            raise P.ApiError(409, "request was cancelled", "client_cancelled")
+        if finish == "deadline" and not req.stream:
+            raise P.ApiError(504, "generation deadline exceeded", "generation_deadline")
+        if calls:
+            reason = "tool_calls"
+        use = P.usage(req.n_prompt, len(token_ids), sr.cached_tokens)
+        vade = P.receipt(req, self.info, sr.drafted, sr.accepted, sr.drafted > 0)
+        text, reasoning = "".join(text_all), "".join(reasoning_all)
+        if req.stream:
+            if req.api == "chat":
+                sse(P.chat_chunk(rid, model, {}, reason, None, created))
+                if req.include_usage:
+                    sse({"id": rid, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [], "usage": use, "vade": vade})
+                h.wfile.write(b"data: [DONE]\n\n")
+            elif req.api == "completions":
+                last = P.completion_chunk(rid, model, "", reason, None, created)
+                last["usage"], last["vade"] = use, vade
+                sse(last)
+                h.wfile.write(b"data: [DONE]\n\n")
+            elif req.api == "messages":
+                sse({"type": "message_delta", "delta": {"stop_reason": "end_turn" if reason == "stop" else "max_tokens"},
+                     "usage": {"output_tokens": len(token_ids)}})
+                sse({"type": "message_stop"})
+            else:
+                sse({"type": "response.completed", "response": {"id": rid, "status": "completed", "usage": use, "vade": vade}})
+            h.wfile.flush()
+            return
+        if req.api == "chat":
+            msg = {"role": "assistant", "content": text}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
+            if calls:
+                msg["tool_calls"] = [{"id": P.new_id("call_"), "type": "function", "function": c} for c in calls]
+            out = {"id": rid, "object": "chat.completion", "created": created, "model": model,
+                   "choices": [{"index": 0, "message": msg, "finish_reason": reason, "token_ids": token_ids}], "usage": use, "vade": vade}
+        elif req.api == "completions":
+            out = {"id": rid, "object": "text_completion", "created": created, "model": model,
+                   "choices": [{"index": 0, "text": text, "finish_reason": reason, "logprobs": None, "token_ids": token_ids}],
+                   "usage": use, "vade": vade}
+        elif req.api == "messages":
+            out = {"id": rid, "type": "message", "role": "assistant", "model": model, "content": [{"type": "text", "text": text}],
+                   "stop_reason": "end_turn" if reason == "stop" else "max_tokens",
+                   "usage": {"input_tokens": req.n_prompt, "output_tokens": len(token_ids)}, "vade": vade}
+        else:
+            out = {"id": rid, "object": "response", "status": "completed", "model": model,
+                   "output": [{"type": "message", "role": "assistant", "content": [{"type": "output_text", "text": text}]}],
+                   "usage": use, "vade": vade}
+        self._send(h, 200, out, seed_hdr)

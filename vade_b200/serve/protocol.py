@@ -1,0 +1,277 @@
+"""Request parsing and reply shapes of the HTTP API.
+
+Four request shapes are accepted and mapped onto one internal ``GenRequest``:
+Chat Completions, Completions, Responses (stateless, full history each turn) and Anthropic
+Messages.  Sampling policy: a request that names no sampling field is greedy
+(temperature 0), the rule the reference shares between engine and gateway
+(engine/crates/model/src/sampling_policy.rs:4-6).  Every reply carries a ``vade`` receipt object
+with the sampling echo (seed included), draft mode and use, build and checkpoint identity, world
+size and numerics path; streams carry ``token_id`` per chunk.  Errors use the OpenAI error shape.
+Parity: engine/crates/serve/src/protocol.rs:92-162, responses.rs, anthropic.rs, metadata.rs:30-60;
+docs/openai-api.md:116-214,326-348.
+"""
+from __future__ import annotations
+
+import json
+import os
+import secrets
+import time
+from dataclasses import dataclass, field
+
+from ..runtime.sampler import Sampling
+
+SAMPLING_FIELDS = ("temperature", "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty")
+LIMIT_MESSAGES, LIMIT_TOOLS, LIMIT_STOP, LIMIT_BODY = 4096, 64, 4, 32 << 20
+
+
+class ApiError(Exception):
+    def __init__(self, status: int, message: str, kind: str = "invalid_request_error", code: str | None = None):
+        super().__init__(message)
+        self.status, self.message, self.kind, self.code = status, message, kind, code
+
+    def body(self) -> dict:
+        return {"error": {"message": self.message, "type": self.kind, "param": None, "code": self.code}}
+
+
+@dataclass
+class GenRequest:
+    api: str                               # chat | completions | responses | messages
+    prompt_ids: list | None = None         # already tokenised prompt (completions with id arrays)
+    prompt_text: str | None = None
+    messages: list | None = None
+    tools: list | None = None
+    max_tokens: int = 256
+    stream: bool = False
+    include_usage: bool = False
+    stop: tuple = ()
+    sampling: Sampling = field(default_factory=Sampling)
+    sampled: bool = False                  # the client named a sampling field
+    draft: str = "auto"                    # auto | plain | strict
+    mtp_depth: int = 0
+    cache: bool = False
+    cache_salt: str = ""
+    prompt_cache_key: str = ""
+    ignore_eos: bool = False
+    priority: int = 0
+    enable_thinking: bool = False
+    model: str = ""
+    n_prompt: int = 0
+
+
+def _need(ok: bool, msg: str) -> None:
+    if not ok:
+        raise ApiError(400, msg)
+
+
+def _sampling(obj: dict, defaults: Sampling) -> tuple:
+    named = any(k in obj and obj[k] is not None for k in SAMPLING_FIELDS)
+    s = Sampling(**{**defaults.echo()})
+    if not named:
+        s.temperature = 0.0                                   # greedy if unsampled
+    for k in SAMPLING_FIELDS:
+        if obj.get(k) is not None:
+            v = obj[k]
+            _need(isinstance(v, (int, float)) and not isinstance(v, bool), f"{k} must be a number")
+            setattr(s, k, int(v) if k == "top_k" else float(v))
+    if obj.get("seed") is not None:
+        _need(isinstance(obj["seed"], int) and not isinstance(obj["seed"], bool), "seed must be an integer")
+        s.seed = obj["seed"] & ((1 << 64) - 1)
+    elif not s.greedy:
+        s.seed = secrets.randbits(64)
+    try:
+        s.validate()
+    except ValueError as e:
+        raise ApiError(400, str(e)) from None
+    return s, named
+
+
+def _common(obj: dict, req: GenRequest, defaults: Sampling, max_output: int) -> None:
+    req.sampling, req.sampled = _sampling(obj, defaults)
+    mt = obj.get("max_completion_tokens", obj.get("max_tokens", obj.get("max_output_tokens")))
+    if mt is not None:
+        _need(isinstance(mt, int) and not isinstance(mt, bool) and mt >= 1, "max_tokens must be a positive integer")
+        req.max_tokens = min(mt, max_output)
+    else:
+        req.max_tokens = min(req.max_tokens, max_output)
+    stop = obj.get("stop", obj.get("stop_sequences"))
+    if stop is not None:
+        stop = [stop] if isinstance(stop, str) else stop
+        _need(isinstance(stop, list) and len(stop) <= LIMIT_STOP and all(isinstance(s, str) for s in stop), f"stop takes up to {LIMIT_STOP} strings")
+        req.stop = tuple(stop)
+    req.stream = bool(obj.get("stream", False))
+    so = obj.get("stream_options") or {}
+    req.include_usage = bool(so.get("include_usage", False)) if isinstance(so, dict) else False
+    draft = obj.get("draft", "auto")
+    _need(draft in ("auto", "plain", "strict", "sampled"), "draft must be plain, strict, sampled or auto")
+    req.draft = "strict" if draft == "sampled" else draft
+    depth = obj.get("mtp_depth", 0)
+    _need(isinstance(depth, int) and 0 <= depth <= 7, "mtp_depth must be 0..7")
+    req.mtp_depth = depth
+    req.cache = bool(obj.get("cache", False)) or bool(obj.get("prompt_cache_key"))
+    req.cache_salt = str(obj.get("cache_salt", ""))
+    req.prompt_cache_key = str(obj.get("prompt_cache_key", ""))
+    req.ignore_eos = bool(obj.get("ignore_eos", False))
+    pr = obj.get("priority", 0)
+    _need(isinstance(pr, int) and 0 <= pr <= 255, "priority must be 0..255")
+    req.priority = pr
+    req.enable_thinking = bool(obj.get("enable_thinking", False)) or obj.get("reasoning_effort") in ("low", "medium", "high")
+    req.model = str(obj.get("model", ""))
+
+
+def parse_request(path: str, body: bytes, defaults: Sampling, max_output: int) -> GenRequest:
+    _need(len(body) <= LIMIT_BODY, "request body too large")
+    try:
+        obj = json.loads(body)
+    except ValueError:
+        raise ApiError(400, "request body is not valid JSON") from None
+    _need(isinstance(obj, dict), "request body must be a JSON object")
+    if path == "/v1/chat/completions":
+        req = GenRequest("chat")
+        msgs = obj.get("messages")
+        _need(isinstance(msgs, list) and 1 <= len(msgs) <= LIMIT_MESSAGES, "messages must be a non-empty list")
+        _need(all(isinstance(m, dict) for m in msgs), "each message must be an object")
+        req.messages = msgs
+        tools = obj.get("tools")
+        if tools is not None:
+            _need(isinstance(tools, list) and len(tools) <= LIMIT_TOOLS, f"at most {LIMIT_TOOLS} tools")
+            req.tools = tools
+    elif path == "/v1/completions":
+        req = GenRequest("completions")
+        p = obj.get("prompt")
+        if isinstance(p, str):
+            req.prompt_text = p
+        elif isinstance(p, list) and p and all(isinstance(t, int) and not isinstance(t, bool) for t in p):
+            req.prompt_ids = list(p)
+        elif isinstance(p, list) and len(p) == 1 and isinstance(p[0], str):
+            req.prompt_text = p[0]
+        else:
+            raise ApiError(400, "prompt must be a string, a one-string list or a list of token ids")
+    elif path == "/v1/responses":
+        req = GenRequest("responses")
+        inp = obj.get("input")
+        msgs = []
+        if obj.get("instructions"):
+            msgs.append({"role": "system", "content": str(obj["instructions"])})
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        elif isinstance(inp, list):
+            for it in inp:
+                _need(isinstance(it, dict), "input items must be objects")
+                if it.get("type", "message") == "message":
+                    msgs.append({"role": it.get("role", "user"), "content": it.get("content", "")})
+        else:
+            raise ApiError(400, "input must be a string or a list of items")
+        _need(len(msgs) >= 1, "input is empty")
+        req.messages = msgs
+    elif path == "/v1/messages":
+        req = GenRequest("messages")
+        msgs = obj.get("messages")
+        _need(isinstance(msgs, list) and msgs, "messages must be a non-empty list")
+        out = []
+        if obj.get("system"):
+            sysv = obj["system"]
+            out.append({"role": "system", "content": sysv if isinstance(sysv, str) else sysv})
+        out += msgs
+        req.messages = out
+        _need(obj.get("max_tokens") is not None, "max_tokens is required")
+    else:
+        raise ApiError(404, f"no route {path}", "not_found_error")
+    _common(obj, req, defaults, max_output)
+    return req
+
+
+# ------------------------------------------------------------------ incremental chat-output parser
+class ChatOutputParser:
+    """Splits generated text into reasoning (<think>...</think>), tool calls
+    (<tool_call>{json}</tool_call>) and ordinary content, incrementally.  A malformed tool call
+    is returned as ordinary content (HTTP 200), never an error."""
+
+    TAGS = ("<think>", "</think>", "<tool_call>", "</tool_call>")
+
+    def __init__(self):
+        self.buf = ""
+        self.mode = "content"
+        self.call_text = ""
+        self.calls = 0
+
+    def feed(self, text: str, final: bool = False) -> list:
+        """Returns deltas: ("content", s) | ("reasoning", s) | ("tool_call", {"name", "arguments"})."""
+        self.buf += text
+        out = []
+        while self.buf:
+            nxt = min(((self.buf.find(t), t) for t in self.TAGS if self.buf.find(t) >= 0), default=None)
+            if nxt is None:
+                # keep a tail that could be the start of a tag
+                keep = 0
+                if not final:
+                    for t in self.TAGS:
+                        for n in range(min(len(t) - 1, len(self.buf)), 0, -1):
+                            if self.buf.endswith(t[:n]):
+                                keep = max(keep, n)
+                                break
+                emit, self.buf = (self.buf[:len(self.buf) - keep], self.buf[len(self.buf) - keep:]) if keep else (self.buf, "")
+                self._emit(out, emit)
+                break
+            pos, tag = nxt
+            self._emit(out, self.buf[:pos])
+            self.buf = self.buf[pos + len(tag):]
+            if tag == "<think>" and self.mode == "content":
+                self.mode = "reasoning"
+            elif tag == "</think>" and self.mode == "reasoning":
+                self.mode = "content"
+            elif tag == "<tool_call>" and self.mode == "content":
+                self.mode, self.call_text = "call", ""
+            elif tag == "</tool_call>" and self.mode == "call":
+                self.mode = "content"
+                try:
+                    obj = json.loads(self.call_text)
+                    name, args = obj["name"], obj.get("arguments", {})
+                    if not isinstance(name, str):
+                        raise ValueError
+                    out.append(("tool_call", {"name": name, "arguments": args if isinstance(args, str) else json.dumps(args)}))
+                    self.calls += 1
+                except (ValueError, KeyError, TypeError):
+                    out.append(("content", "<tool_call>" + self.call_text + "</tool_call>"))
+            else:
+                self._emit(out, tag)
+        if final and self.mode == "call":
+            out.append(("content", "<tool_call>" + self.call_text))
+            self.mode = "content"
+        return [d for d in out if d[1]]
+
+    def _emit(self, out: list, s: str) -> None:
+        if not s:
+            return
+        if self.mode == "call":
+            self.call_text += s
+        else:
+            out.append((self.mode, s))
+
+
+# ------------------------------------------------------------------ replies
+def new_id(prefix: str) -> str:
+    return prefix + secrets.token_hex(12)
+
+
+def receipt(req: GenRequest, info: dict, drafted: int = 0, accepted: int = 0, draft_used: bool = False) -> dict:
+    return {"sampling": req.sampling.echo(), "greedy_if_unsampled": not req.sampled, "draft": req.draft,
+            "draft_used": draft_used, "drafted": drafted, "accepted": accepted, "thinking": req.enable_thinking, **info}
+
+
+def usage(n_prompt: int, n_out: int, cached: int) -> dict:
+    return {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out,
+            "prompt_tokens_details": {"cached_tokens": cached}}
+
+
+def chat_chunk(rid: str, model: str, delta: dict, finish: str | None, token_id: int | None, created: int) -> dict:
+    ch = {"index": 0, "delta": delta, "finish_reason": finish}
+    if token_id is not None:
+        ch["token_id"] = token_id
+    return {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [ch]}
+
+
+def completion_chunk(rid: str, model: str, text: str, finish: str | None, token_id: int | None, created: int) -> dict:
+    ch = {"index": 0, "text": text, "finish_reason": finish, "logprobs": None}
+    if token_id is not None:
+        ch["token_id"] = token_id
+    return {"id": rid, "object": "text_completion", "created": created, "model": model, "choices": [ch]}

@@ -1,0 +1,225 @@
+"""Tokenizers and chat templates.
+
+Two tokenizer kinds are read from a checkpoint's ``tokenizer.json``:
+
+* ``vade-bytes``: ids 0..255 are bytes, special tokens sit at the top of the vocabulary (what the
+  synthetic checkpoints carry);
+* HuggingFace byte-level BPE (``model.type == "BPE"`` with a ByteLevel pre-tokenizer): vocabulary,
+  merges and added tokens are read from the file and encoded with a first-party BPE loop.
+
+The chat template is ChatML (Qwen style).  It is not executed as Jinja: the renderer recognises the
+template by its marker tokens and fails closed on anything else, as the reference does
+(engine/crates/tokenizer/src/chat.rs:12-48).  Incremental decoding never emits half a UTF-8
+sequence.  Parity: engine/crates/tokenizer/src/lib.rs.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+
+
+class TokenizerError(ValueError):
+    pass
+
+
+def _bytes_to_unicode() -> dict:
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("\xa1"), ord("\xac") + 1)) + list(range(ord("\xae"), ord("\xff") + 1))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return dict(zip(bs, [chr(c) for c in cs]))
+
+
+class ByteTokenizer:
+    kind = "vade-bytes"
+
+    def __init__(self, vocab_size: int, special: dict):
+        self.vocab_size = vocab_size
+        self.special = dict(special)
+        self.special_by_id = {v: k for k, v in special.items()}
+        self._split = re.compile("(" + "|".join(re.escape(k) for k in sorted(special, key=len, reverse=True)) + ")") if special else None
+
+    def encode(self, text: str, allow_special: bool = True) -> list:
+        out = []
+        parts = self._split.split(text) if (self._split and allow_special) else [text]
+        for p in parts:
+            if not p:
+                continue
+            if allow_special and p in self.special:
+                out.append(self.special[p])
+            else:
+                out.extend(p.encode("utf-8"))
+        return out
+
+    def token_bytes(self, tok: int) -> bytes:
+        if tok in self.special_by_id:
+            return self.special_by_id[tok].encode()
+        if 0 <= tok < 256:
+            return bytes([tok])
+        return b""
+
+    def decode(self, ids: list) -> str:
+        return b"".join(self.token_bytes(t) for t in ids).decode("utf-8", errors="replace")
+
+    @property
+    def eos_id(self):
+        return self.special.get("<|im_end|>")
+
+
+class BPETokenizer:
+    kind = "bpe"
+    _PAT = re.compile(r"'s|'t|'re|'ve|'m|'ll|'d| ?[^\W\d_]+| ?\d+| ?[^\s\w]+|\s+(?!\S)|\s+", re.UNICODE)
+
+    def __init__(self, vocab: dict, merges: list, added: dict):
+        self.vocab = vocab
+        self.inv = {v: k for k, v in vocab.items()}
+        self.ranks = {tuple(m.split(" ")) if isinstance(m, str) else tuple(m): i for i, m in enumerate(merges)}
+        self.special = dict(added)
+        self.special_by_id = {v: k for k, v in added.items()}
+        self.b2u = _bytes_to_unicode()
+        self.u2b = {v: k for k, v in self.b2u.items()}
+        self.vocab_size = max(list(vocab.values()) + list(added.values())) + 1
+        self._split = re.compile("(" + "|".join(re.escape(k) for k in sorted(added, key=len, reverse=True)) + ")") if added else None
+        self._cache: dict = {}
+
+    def _bpe(self, word: str) -> list:
+        if word in self._cache:
+            return self._cache[word]
+        parts = list(word)
+        while len(parts) > 1:
+            best, at = None, -1
+            for i in range(len(parts) - 1):
+                r = self.ranks.get((parts[i], parts[i + 1]))
+                if r is not None and (best is None or r < best):
+                    best, at = r, i
+            if best is None:
+                break
+            parts[at:at + 2] = [parts[at] + parts[at + 1]]
+        if len(self._cache) < 65536:
+            self._cache[word] = parts
+        return parts
+
+    def encode(self, text: str, allow_special: bool = True) -> list:
+        out = []
+        chunks = self._split.split(text) if (self._split and allow_special) else [text]
+        for ch in chunks:
+            if not ch:
+                continue
+            if allow_special and ch in self.special:
+                out.append(self.special[ch])
+                continue
+            for piece in self._PAT.findall(ch):
+                word = "".join(self.b2u[b] for b in piece.encode("utf-8"))
+                for p in self._bpe(word):
+                    if p not in self.vocab:
+                        raise TokenizerError(f"piece {p!r} is not in the vocabulary")
+                    out.append(self.vocab[p])
+        return out
+
+    def token_bytes(self, tok: int) -> bytes:
+        if tok in self.special_by_id:
+            return self.special_by_id[tok].encode()
+        s = self.inv.get(tok)
+        return bytes(self.u2b[c] for c in s) if s is not None else b""
+
+    def decode(self, ids: list) -> str:
+        return b"".join(self.token_bytes(t) for t in ids).decode("utf-8", errors="replace")
+
+    @property
+    def eos_id(self):
+        return self.special.get("<|im_end|>", self.special.get("<|endoftext|>"))
+
+
+def load_tokenizer(root: str):
+    path = os.path.join(root, "tokenizer.json")
+    if not os.path.exists(path):
+        raise TokenizerError(f"{root}: no tokenizer.json")
+    if os.path.getsize(path) > 256 << 20:
+        raise TokenizerError("tokenizer.json is larger than the 256 MiB limit")
+    with open(path, "rb") as f:
+        obj = json.loads(f.read())
+    if obj.get("type") == "vade-bytes":
+        return ByteTokenizer(int(obj["vocab_size"]), obj.get("special_tokens", {}))
+    model = obj.get("model", {})
+    if model.get("type") != "BPE":
+        raise TokenizerError(f"unsupported tokenizer model {model.get('type')!r}")
+    added = {t["content"]: int(t["id"]) for t in obj.get("added_tokens", [])}
+    return BPETokenizer(model["vocab"], model.get("merges", []), added)
+
+
+class StreamDecoder:
+    """Turns token ids into text pieces without ever splitting a UTF-8 sequence."""
+
+    def __init__(self, tok):
+        self.tok = tok
+        self.pending = b""
+
+    def feed(self, token: int) -> str:
+        self.pending += self.tok.token_bytes(token)
+        for cut in range(len(self.pending), max(len(self.pending) - 4, -1), -1):
+            try:
+                text = self.pending[:cut].decode("utf-8")
+            except UnicodeDecodeError:
+                continue
+            self.pending = self.pending[cut:]
+            return text
+        if len(self.pending) > 8:                       # not UTF-8 at all: flush with replacement
+            text = self.pending.decode("utf-8", errors="replace")
+            self.pending = b""
+            return text
+        return ""
+
+    def flush(self) -> str:
+        text = self.pending.decode("utf-8", errors="replace")
+        self.pending = b""
+        return text
+
+
+# ------------------------------------------------------------------ chat template (ChatML)
+ROLES = ("system", "user", "assistant", "tool")
+
+
+def render_chat(messages: list, tok, add_generation_prompt: bool = True, enable_thinking: bool = False, tools: list | None = None) -> str:
+    """ChatML rendering; refuses (fails closed) when the tokenizer lacks the ChatML markers or a
+    message has an unknown role or non-text content."""
+    if "<|im_start|>" not in tok.special or "<|im_end|>" not in tok.special:
+        raise TokenizerError("the checkpoint's tokenizer has no ChatML markers; refusing to guess a chat template")
+    out = []
+    if tools:
+        decl = "\n".join(json.dumps(t, separators=(",", ":"), sort_keys=True) for t in tools)
+        out.append("<|im_start|>system\n# Tools\n\nYou may call one or more functions. Function signatures:\n<tools>\n" + decl +
+                   "\n</tools>\n\nReturn each call as <tool_call>\n{\"name\": ..., \"arguments\": ...}\n</tool_call><|im_end|>\n")
+    for m in messages:
+        role = m.get("role")
+        if role not in ROLES:
+            raise TokenizerError(f"unknown chat role {role!r}")
+        content = m.get("content")
+        if isinstance(content, list):
+            texts = []
+            for part in content:
+                if not isinstance(part, dict) or part.get("type") not in ("text", "input_text", "output_text"):
+                    raise TokenizerError("only text content parts are supported")
+                texts.append(part.get("text", ""))
+            content = "".join(texts)
+        if content is None:
+            content = ""
+        if not isinstance(content, str):
+            raise TokenizerError("message content must be text")
+        if role == "assistant" and m.get("tool_calls"):
+            for call in m["tool_calls"]:
+                fn = call.get("function", {})
+                content += "\n<tool_call>\n" + json.dumps({"name": fn.get("name"), "arguments": fn.get("arguments")}) + "\n</tool_call>"
+        if role == "tool":
+            out.append("<|im_start|>user\n<tool_response>\n" + content + "\n</tool_response><|im_end|>\n")
+        else:
+            out.append(f"<|im_start|>{role}\n{content}<|im_end|>\n")
+    if add_generation_prompt:
+        out.append("<|im_start|>assistant\n")
+        if not enable_thinking and "<think>" in tok.special:
+            out.append("<think>\n\n</think>\n\n")
+    return "".join(out)
