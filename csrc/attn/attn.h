@@ -1,6 +1,7 @@
 // Host interface of the gated paged attention kernels (see attn.cu).
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdint>
 
 namespace vade {
 
@@ -17,6 +18,13 @@ const char* attn_prep(const void* qkv, bool parts, int n_parts, long long part_s
 const char* attn_rows(const void* q, const void* gate, const void* k_pages, const void* v_pages, const int* positions,
                       const int* row_slot, const int* block_table, int max_pages, int rows, int nq, int nkv, int hd,
                       bool split, float* partial, int n_split, void* out, cudaStream_t s);
+
+// Prompt-class attention on tcgen05 (see attn_prefill_umma.cu): q, gate bf16 [rows][nq][hd]; out bf16
+// [rows][nq * hd]; seq_* describe the sequences of the pass (rows of a sequence are contiguous).
+const char* attn_prefill_umma(const void* q, const void* gate, const void* k_pages, const void* v_pages, long long n_pages,
+                              const int* block_table, int max_pages, const int* seq_slot, const int* seq_start, const int* seq_pos0,
+                              int n_seq, int rows, int max_seq_rows, int nq, int nkv, int hd, void* out, uint32_t* status,
+                              cudaStream_t s);
 
 int attn_split_keys();
 

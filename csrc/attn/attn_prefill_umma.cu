@@ -1,0 +1,332 @@
+// Causal gated attention for prompt tiles on tcgen05 tensor cores (head dimension 256, GQA, paged KV).
+//
+// One CTA = 128 query rows of one query head of one sequence.  It walks the visible keys one cache
+// page (64 keys) at a time:
+//   S = Q K^T      tcgen05.mma, M=128 x N=64 x K=256, fp32 in TMEM (two S buffers so the next page's
+//                  product overlaps this page's softmax)
+//   softmax        128 threads, one query row each (TMEM lane = row): scale, causal mask, running max
+//                  with a lazy reference (O is rescaled only when the row max grows by more than 8 in
+//                  the log2 domain), P = exp2(s - m_ref) written as bf16 into a swizzled A tile
+//   O += P V       tcgen05.mma, M=128 x N=256 x K=64, V read in place as an MN-major operand
+// K and V pages arrive by TMA straight from the paged cache (the page table gives the row coordinate).
+// The epilogue divides by the row sum, applies sigmoid(gate) and writes bf16.
+//
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (and TMEM owner), warps 2..5 softmax/epilogue.
+// Every wait is bounded; on a timeout the kernel raises the status word and leaves.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <mutex>
+#include "../common/ptx.cuh"
+#include "attn.h"
+
+namespace vade {
+
+namespace {
+
+constexpr int kHD = 256;
+constexpr int kPage = 64;
+constexpr int kQRows = 128;
+constexpr int kThreads = 192;
+constexpr int kQBytes = kQRows * kHD * 2;            // 64 KB: 4 blocks of [128][64]
+constexpr int kKVBytes = kPage * kHD * 2;            // 32 KB: 4 blocks of [64][64]
+constexpr int kPBytes = kQRows * kPage * 2;          // 16 KB
+constexpr int kStages = 2;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct PrefillArgs {
+    const __nv_bfloat16* gate;
+    __nv_bfloat16* out;
+    const int* block_table;
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_pos0;
+    uint32_t* status;
+    int max_pages, nq, nkv;
+    float scale_log2;
+};
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// MN-major operand (rows = K index, 64 contiguous N elements per 128-byte line, 128-byte swizzle):
+// 8-row groups are 1024 bytes apart along K (stride offset), 64-column blocks `lbo` bytes apart along N.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const PrefillArgs a) {
+    const int tile = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+    const int r0 = a.seq_start[b], r1 = a.seq_start[b + 1];
+    const int row0 = r0 + tile * kQRows;
+    if (row0 >= r1) return;
+    const int nvalid = min(kQRows, r1 - row0);
+    const int pos_first = a.seq_pos0[b] + tile * kQRows;            // position of query row 0 of this tile
+    const int nb = (pos_first + nvalid - 1) / kPage + 1;            // pages that hold visible keys
+    const int kvh = head / (a.nq / a.nkv);
+    const int* table = a.block_table + static_cast<long long>(a.seq_slot[b]) * a.max_pages;
+
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + kQBytes;
+    uint8_t* sV = sK + kStages * kKVBytes;
+    uint8_t* sP = sV + kStages * kKVBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;            // [2]
+    uint64_t* v_full = bars + 3;            // [2]
+    uint64_t* k_empty = bars + 5;           // [2]
+    uint64_t* v_empty = bars + 7;           // [2]
+    uint64_t* s_full = bars + 9;            // [2]
+    uint64_t* p_ready = bars + 11;
+    uint64_t* o_done = bars + 12;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+        }
+        mbar_init(p_ready, 128);
+        mbar_init(o_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    auto fail = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (a.status != nullptr) atomicMax(a.status, code);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kQBytes);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tma_load_2d(sQ + c * (kQRows * 128), &tmap_q, head * kHD + c * 64, row0, q_full);
+            for (int j = 0; j < nb; ++j) {
+                const int s = j % kStages;
+                const uint32_t ph = (j / kStages) & 1;
+                const int prow = table[j] * kPage;
+                if (!mbar_wait(&k_empty[s], ph ^ 1)) { fail(21); break; }
+                mbar_expect_tx(&k_full[s], kKVBytes);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tma_load_2d(sK + s * kKVBytes + c * (kPage * 128), &tmap_k, kvh * kHD + c * 64, prow, &k_full[s]);
+                if (!mbar_wait(&v_empty[s], ph ^ 1)) { fail(22); break; }
+                mbar_expect_tx(&v_full[s], kKVBytes);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tma_load_2d(sV + s * kKVBytes + c * (kPage * 128), &tmap_v, kvh * kHD + c * 64, prow, &v_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(kQRows, kPage);
+            constexpr uint32_t idesc_o = umma_idesc_bf16(kQRows, kHD) | (1u << 16);        // B operand (V) is MN-major
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % kStages;
+                if (!mbar_wait(&k_full[s], (j / kStages) & 1)) return false;
+                tc_fence_after_sync();
+                const uint32_t d = tmem + kColS + (j & 1) * kPage;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint64_t qd = umma_desc_sw128(smem_u32(sQ + c * (kQRows * 128)));
+                    const uint64_t kd = umma_desc_sw128(smem_u32(sK + s * kKVBytes + c * (kPage * 128)));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) umma_f16(d, qd + 2 * kk, kd + 2 * kk, idesc_s, (c | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[j & 1]);
+                umma_commit(&k_empty[s]);
+                return true;
+            };
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) fail(23);
+            if (ok && !issue_s(0)) { fail(24); ok = false; }
+            for (int j = 0; ok && j < nb; ++j) {
+                if (j + 1 < nb && !issue_s(j + 1)) { fail(24); break; }
+                const int s = j % kStages;
+                if (!mbar_wait(p_ready, j & 1)) { fail(25); break; }
+                if (!mbar_wait(&v_full[s], (j / kStages) & 1)) { fail(26); break; }
+                tc_fence_after_sync();
+                const uint64_t pd = umma_desc_sw128(smem_u32(sP));
+                const uint64_t vd = umma_desc_mn_sw128(smem_u32(sV + s * kKVBytes), kPage * 128);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_f16(tmem + kColO, pd + 2 * kk, vd + kk * (2048 >> 4), idesc_o, (j | kk) != 0 ? 1u : 0u);
+                umma_commit(o_done);
+                umma_commit(&v_empty[s]);
+            }
+        }
+    } else {
+        const int q = warp & 3;                                    // TMEM lane quadrant of this warp
+        const int row = q * 32 + lane;                             // query row inside the tile
+        const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+        const int qpos = pos_first + row;
+        float m_ref = -1e30f, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nb; ++j) {
+            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { fail(27); ok = false; break; }
+            tc_fence_after_sync();
+            float sv[kPage];
+#pragma unroll
+            for (int c = 0; c < kPage; c += 16) tmem_ld16(tmem + lane_addr + kColS + (j & 1) * kPage + c, sv + c);
+            const int key0 = j * kPage;
+            float mx = -1e30f;
+#pragma unroll
+            for (int c = 0; c < kPage; ++c) {
+                sv[c] = (key0 + c <= qpos) ? sv[c] * a.scale_log2 : -1e30f;
+                mx = fmaxf(mx, sv[c]);
+            }
+            if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) { fail(28); ok = false; break; }
+            tc_fence_after_sync();
+            // lazy rescale: keep the old reference unless this row's max grew by more than 8 (factor 256)
+            const bool grow = mx > m_ref + 8.f;
+            const float m_new = (j == 0 || grow) ? fmaxf(mx, m_ref) : m_ref;
+            const float factor = exp2f(m_ref - m_new);
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                for (int c = 0; c < kHD; c += 16) {
+                    float o[16];
+                    tmem_ld16(tmem + lane_addr + kColO + c, o);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] *= factor;
+                    tmem_st16(tmem + lane_addr + kColO + c, o);
+                }
+                tmem_st_wait();
+            }
+            l *= factor;
+            m_ref = m_new;
+            uint8_t* prow = sP + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = exp2f(sv[ch * 8 + 2 * i] - m_ref), p1 = exp2f(sv[ch * 8 + 2 * i + 1] - m_ref);
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    l += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+                    w[i] = *reinterpret_cast<const uint32_t*>(&pb);
+                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(p_ready);
+        }
+        if (ok && !mbar_wait(o_done, (nb - 1) & 1)) { fail(29); ok = false; }
+        tc_fence_after_sync();
+        // TMEM loads are warp-collective: every lane of the warp takes the same path, only the store is per row
+        if (__all_sync(0xffffffffu, ok && *abort_flag == 0)) {
+            const float inv = 1.f / l;
+            const long long base = (static_cast<long long>(row0 + row) * a.nq + head) * kHD;
+            for (int c = 0; c < kHD; c += 16) {
+                float o[16];
+                tmem_ld16(tmem + lane_addr + kColO + c, o);
+                if (row < nvalid) {
+                    const uint4 g0 = *reinterpret_cast<const uint4*>(a.gate + base + c), g1 = *reinterpret_cast<const uint4*>(a.gate + base + c + 8);
+                    const __nv_bfloat162* gp0 = reinterpret_cast<const __nv_bfloat162*>(&g0);
+                    const __nv_bfloat162* gp1 = reinterpret_cast<const __nv_bfloat162*>(&g1);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float2 g = __bfloat1622float2(i < 4 ? gp0[i] : gp1[i - 4]);
+                        const __nv_bfloat162 ob = __floats2bfloat162_rn(o[2 * i] * inv * sigmoidf_(g.x), o[2 * i + 1] * inv * sigmoidf_(g.y));
+                        w[i] = *reinterpret_cast<const uint32_t*>(&ob);
+                    }
+                    *reinterpret_cast<uint4*>(a.out + base + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(a.out + base + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool make_tmap(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+const char* attn_prefill_umma(const void* q, const void* gate, const void* k_pages, const void* v_pages, long long n_pages,
+                              const int* block_table, int max_pages, const int* seq_slot, const int* seq_start, const int* seq_pos0,
+                              int n_seq, int rows, int max_seq_rows, int nq, int nkv, int hd, void* out, uint32_t* status,
+                              cudaStream_t s) {
+    if (hd != kHD) return "attention kernels handle head dimension 256";
+    if (nq % nkv != 0) return "bad GQA group";
+    CUtensorMap tq, tk, tv;
+    if (!make_tmap(&tq, q, static_cast<uint64_t>(nq) * kHD, static_cast<uint64_t>(rows), kQRows) ||
+        !make_tmap(&tk, k_pages, static_cast<uint64_t>(nkv) * kHD, static_cast<uint64_t>(n_pages) * kPage, kPage) ||
+        !make_tmap(&tv, v_pages, static_cast<uint64_t>(nkv) * kHD, static_cast<uint64_t>(n_pages) * kPage, kPage))
+        return "cuTensorMapEncodeTiled failed";
+    PrefillArgs a;
+    a.gate = static_cast<const __nv_bfloat16*>(gate);
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.block_table = block_table; a.seq_slot = seq_slot; a.seq_start = seq_start; a.seq_pos0 = seq_pos0;
+    a.status = status; a.max_pages = max_pages; a.nq = nq; a.nkv = nkv;
+    a.scale_log2 = kLog2e / sqrtf(static_cast<float>(hd));
+    constexpr int smem = kQBytes + 2 * kStages * kKVBytes + kPBytes + 16 * 8 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return "cannot raise shared memory limit";
+        configured = true;
+    }
+    const dim3 grid((max_seq_rows + kQRows - 1) / kQRows, nq, n_seq);
+    attn_prefill_umma_kernel<<<grid, kThreads, smem, s>>>(tq, tk, tv, a);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "attn_prefill launch failed";
+}
+
+}  // namespace vade

@@ -163,6 +163,22 @@ void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torc
                          static_cast<float>(eps), gate_silu, stream_of(proj)));
 }
 
+void gdn_prefill(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
+                 torch::Tensor dt_bias, torch::Tensor norm_w, torch::Tensor row_seq, torch::Tensor seq_slot, torch::Tensor seq_start,
+                 int64_t n_seq, torch::Tensor scratch, torch::Tensor out, int64_t kh, int64_t vh, int64_t kd, int64_t vd, double eps,
+                 bool gate_silu) {
+    const int64_t rows = proj.size(0);
+    need(proj.dim() == 2 && proj.scalar_type() == torch::kBFloat16 && proj.stride(1) == 1 && scratch.scalar_type() == torch::kFloat32 &&
+         scratch.numel() >= rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh && out.scalar_type() == torch::kBFloat16 && out.is_contiguous(),
+         "gdn_prefill arguments");
+    c10::cuda::CUDAGuard guard(proj.device());
+    check(vade::gdn_prefill(proj.data_ptr(), static_cast<int>(proj.stride(0)), static_cast<int>(rows), conv_w.data_ptr<float>(),
+                            hist.data_ptr<float>(), state.data_ptr<float>(), a_log.data_ptr<float>(), dt_bias.data_ptr<float>(),
+                            norm_w.data_ptr<float>(), row_seq.data_ptr<int>(), seq_slot.data_ptr<int>(), seq_start.data_ptr<int>(),
+                            static_cast<int>(n_seq), scratch.data_ptr<float>(), out.data_ptr(), static_cast<int>(kh), static_cast<int>(vh),
+                            static_cast<int>(kd), static_cast<int>(vd), static_cast<float>(eps), gate_silu, stream_of(proj)));
+}
+
 void attn_prep(torch::Tensor qkv, int64_t nq, int64_t nkv, int64_t hd, torch::Tensor q_norm, torch::Tensor k_norm,
                torch::Tensor positions, torch::Tensor row_slot, torch::Tensor block_table, torch::Tensor q_out, torch::Tensor gate_out,
                torch::Tensor k_pages, torch::Tensor v_pages, int64_t rot, double theta, double eps) {
@@ -190,6 +206,21 @@ void attn_rows(torch::Tensor q, torch::Tensor gate, torch::Tensor k_pages, torch
                           positions.data_ptr<int>(), row_slot.data_ptr<int>(), block_table.data_ptr<int>(),
                           static_cast<int>(block_table.size(1)), static_cast<int>(q.size(0)), static_cast<int>(nq), static_cast<int>(nkv),
                           static_cast<int>(hd), split, ptr<float>(partial), static_cast<int>(n_split), out.data_ptr(), stream_of(q)));
+}
+
+void attn_prefill(torch::Tensor q, torch::Tensor gate, torch::Tensor k_pages, torch::Tensor v_pages, torch::Tensor block_table,
+                  torch::Tensor seq_slot, torch::Tensor seq_start, torch::Tensor seq_pos0, int64_t n_seq, int64_t max_seq_rows,
+                  int64_t nq, int64_t nkv, int64_t hd, torch::Tensor out, c10::optional<torch::Tensor> status) {
+    need(q.scalar_type() == torch::kBFloat16 && q.is_contiguous() && gate.is_contiguous() && k_pages.is_contiguous() &&
+         v_pages.is_contiguous() && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() &&
+         seq_pos0.scalar_type() == torch::kInt32, "attn_prefill arguments");
+    c10::cuda::CUDAGuard guard(q.device());
+    check(vade::attn_prefill_umma(q.data_ptr(), gate.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.size(0),
+                                  block_table.data_ptr<int>(), static_cast<int>(block_table.size(1)), seq_slot.data_ptr<int>(),
+                                  seq_start.data_ptr<int>(), seq_pos0.data_ptr<int>(), static_cast<int>(n_seq),
+                                  static_cast<int>(q.size(0)), static_cast<int>(max_seq_rows), static_cast<int>(nq), static_cast<int>(nkv),
+                                  static_cast<int>(hd), out.data_ptr(),
+                                  status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr, stream_of(q)));
 }
 
 void swiglu_fold(torch::Tensor parts, torch::Tensor meta, torch::Tensor mid) {
@@ -268,8 +299,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_route_small", &moe_route_small);
     m.def("gdn_scan", &gdn_scan);
+    m.def("gdn_prefill", &gdn_prefill);
     m.def("attn_prep", &attn_prep);
     m.def("attn_rows", &attn_rows);
+    m.def("attn_prefill", &attn_prefill);
     m.def("argmax_rows", &argmax_rows);
     m.def("attn_split_keys", &vade::attn_split_keys);
     m.def("argmax_chunk", &vade::argmax_chunk);

@@ -132,6 +132,206 @@ gdn_scan_kernel(const void* __restrict__ proj, int ld, int n_parts, long long pa
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prompt-class path: the same recurrence cut into three launches so the serial walk over a tile does
+// no block-wide reductions.  prep (parallel over rows): conv + SiLU, l2-normalised q/k, beta, e^g.
+// scan (serial over rows, one CTA per key head): state columns in registers, q/k of the next row
+// prefetched into shared memory; the two 128-term sums run as four interleaved chains joined as
+// (c0 + c1) + (c2 + c3).  post (parallel over rows): gated RMSNorm.
+__global__ void __launch_bounds__(128)
+gdn_prep_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __restrict__ conv_w, const float* __restrict__ hist,
+                const float* __restrict__ a_log, const float* __restrict__ dt_bias, const int* __restrict__ row_seq,
+                const int* __restrict__ seq_slot, const int* __restrict__ seq_start, float* __restrict__ qn, float* __restrict__ kn,
+                float* __restrict__ vv, float* __restrict__ beta, float* __restrict__ decay, int kh, int vh) {
+    __shared__ float red[4];
+    const int row = blockIdx.x, unit = blockIdx.y, j = threadIdx.x;
+    const int C = 2 * kh * kD + vh * kD;
+    const int b = row_seq[row];
+    const int r0 = seq_start[b];
+    const int slot = seq_slot[b];
+    // unit: [0, kh) query heads, [kh, 2kh) key heads, [2kh, 2kh + vh) value heads; channel index follows the same order
+    const int ch = unit * kD + j;
+    float acc = 0.f;
+#pragma unroll
+    for (int tap = 0; tap < 4; ++tap) {
+        const int src = row - 3 + tap;                    // rows before the sequence's first row of this pass come from the history
+        const float x = src >= r0 ? __bfloat162float(proj[static_cast<long long>(src) * ld + ch])
+                                  : hist[(static_cast<long long>(slot) * 3 + (3 + src - r0)) * C + ch];
+        acc += x * conv_w[ch * 4 + tap];
+    }
+    const float c = siluf_(acc);
+    if (unit < 2 * kh) {
+        float ss = c * c;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((j & 31) == 0) red[j >> 5] = ss;
+        __syncthreads();
+        const float tot = (red[0] + red[1]) + (red[2] + red[3]);
+        const float n = c * rsqrtf(tot + 1e-6f);
+        if (unit < kh) qn[(static_cast<long long>(row) * kh + unit) * kD + j] = n * rsqrtf(static_cast<float>(kD));
+        else kn[(static_cast<long long>(row) * kh + (unit - kh)) * kD + j] = n;
+    } else {
+        const int h = unit - 2 * kh;
+        vv[(static_cast<long long>(row) * vh + h) * kD + j] = c;
+        if (j == 0) {
+            const __nv_bfloat16* p = proj + static_cast<long long>(row) * ld;
+            beta[static_cast<long long>(row) * vh + h] = sigmoidf_(__bfloat162float(p[C + vh * kD + h]));
+            const float ax = __bfloat162float(p[C + vh * kD + vh + h]) + dt_bias[h];
+            const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
+            decay[static_cast<long long>(row) * vh + h] = __expf(-__expf(a_log[h]) * sp);
+        }
+    }
+}
+
+// New history = the last three raw rows of [old history, this pass's rows]; one thread per (sequence, channel).
+__global__ void gdn_hist_kernel(const __nv_bfloat16* __restrict__ proj, int ld, float* __restrict__ hist,
+                                const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int C) {
+    const int b = blockIdx.y;
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= C) return;
+    const int r0 = seq_start[b], r1 = seq_start[b + 1];
+    float* h = hist + static_cast<long long>(seq_slot[b]) * 3 * C + ch;
+    float v[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const int src = r1 - 3 + i;
+        v[i] = src >= r0 ? __bfloat162float(proj[static_cast<long long>(src) * ld + ch]) : h[(3 + src - r0) * C];
+    }
+#pragma unroll
+    for (int i = 0; i < 3; ++i) h[i * C] = v[i];
+}
+
+// One CTA owns 32 state columns of one value head; the 128 state rows of a column are split over
+// 8 adjacent lanes (16 rows each), so a row of the tile costs each thread 16 + 16 multiply-adds and two
+// 3-step butterflies.  Columns are independent, so a head's four column groups run on four SMs.
+constexpr int kLeanCols = 32;
+constexpr int kLeanParts = 8;
+constexpr int kLeanRows = kD / kLeanParts;          // 16 state rows per thread
+
+constexpr int kLeanAhead = 8;                       // rows in flight (asynchronous copies)
+constexpr int kLeanRing = kLeanAhead + 1;           // one spare slot: a single barrier per row is enough
+
+__device__ __forceinline__ void cp_async_f(void* dst, const void* src, int bytes) {
+    if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kLeanCols * kLeanParts)
+gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                     const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
+                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, float* __restrict__ o_out, int kh, int vh) {
+    __shared__ __align__(16) float qk[kLeanRing][2 * kD];          // [slot][q(128) | k(128)]
+    __shared__ __align__(16) float vs[kLeanRing][kLeanCols];
+    __shared__ __align__(16) float bd[kLeanRing][4];               // beta, decay
+    const int groups = kD / kLeanCols;
+    const int vhead = blockIdx.x / groups, cg = blockIdx.x % groups, b = blockIdx.y;
+    const int khead = vhead / (vh / kh);
+    const int part = threadIdx.x & (kLeanParts - 1);
+    const int lcol = threadIdx.x >> 3;
+    const int col = cg * kLeanCols + lcol;
+    const int i0 = part * kLeanRows;
+    const int slot = seq_slot[b];
+    const int r0 = seq_start[b], r1 = seq_start[b + 1];
+    if (r0 >= r1) return;
+    float S[kLeanRows];
+    float* sp = state + ((static_cast<long long>(slot) * vh + vhead) * kD + i0) * kD + col;
+#pragma unroll
+    for (int i = 0; i < kLeanRows; ++i) S[i] = sp[i * kD];
+    // row rr of the tile -> ring slot (rr - r0) % kLeanRing, one commit group per row (empty past the end)
+    auto stage = [&](int rr) {
+        if (rr < r1) {
+            const int sl = (rr - r0) % kLeanRing, t = threadIdx.x;
+            if (t < 32) cp_async_f(&qk[sl][t * 4], qn + (static_cast<long long>(rr) * kh + khead) * kD + t * 4, 16);
+            else if (t < 64) cp_async_f(&qk[sl][kD + (t - 32) * 4], kn + (static_cast<long long>(rr) * kh + khead) * kD + (t - 32) * 4, 16);
+            else if (t < 72) cp_async_f(&vs[sl][(t - 64) * 4], vv + (static_cast<long long>(rr) * vh + vhead) * kD + cg * kLeanCols + (t - 64) * 4, 16);
+            else if (t == 72) cp_async_f(&bd[sl][0], beta + static_cast<long long>(rr) * vh + vhead, 4);
+            else if (t == 73) cp_async_f(&bd[sl][1], decay + static_cast<long long>(rr) * vh + vhead, 4);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int i = 0; i < kLeanAhead; ++i) stage(r0 + i);
+    for (int r = r0; r < r1; ++r) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kLeanAhead - 1) : "memory");      // the group of row r has landed
+        __syncthreads();                                                                // ... for every thread; row r - 1 is fully consumed
+        stage(r + kLeanAhead);                                                          // overwrites the slot of row r - 1
+        const int sl = (r - r0) % kLeanRing;
+        const float4* q4 = reinterpret_cast<const float4*>(qk[sl] + i0);
+        const float4* k4 = reinterpret_cast<const float4*>(qk[sl] + kD + i0);
+        const float v = vs[sl][lcol], bt = bd[sl][0], dc = bd[sl][1];
+        float4 kk[kLeanRows / 4];
+#pragma unroll
+        for (int i = 0; i < kLeanRows / 4; ++i) kk[i] = k4[i];
+        float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kLeanRows / 4; ++i) {
+            S[4 * i] *= dc; S[4 * i + 1] *= dc; S[4 * i + 2] *= dc; S[4 * i + 3] *= dc;
+            m0 += S[4 * i] * kk[i].x; m1 += S[4 * i + 1] * kk[i].y; m0 += S[4 * i + 2] * kk[i].z; m1 += S[4 * i + 3] * kk[i].w;
+        }
+        float mem = m0 + m1;
+        mem += __shfl_xor_sync(0xffffffffu, mem, 1);
+        mem += __shfl_xor_sync(0xffffffffu, mem, 2);
+        mem += __shfl_xor_sync(0xffffffffu, mem, 4);
+        const float delta = (v - mem) * bt;
+        float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kLeanRows / 4; ++i) {
+            const float4 qq = q4[i];
+            S[4 * i] += kk[i].x * delta; S[4 * i + 1] += kk[i].y * delta; S[4 * i + 2] += kk[i].z * delta; S[4 * i + 3] += kk[i].w * delta;
+            o0 += S[4 * i] * qq.x; o1 += S[4 * i + 1] * qq.y; o0 += S[4 * i + 2] * qq.z; o1 += S[4 * i + 3] * qq.w;
+        }
+        float o = o0 + o1;
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        o += __shfl_xor_sync(0xffffffffu, o, 4);
+        if (part == 0) o_out[(static_cast<long long>(r) * vh + vhead) * kD + col] = o;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < kLeanRows; ++i) sp[i * kD] = S[i];
+}
+
+__global__ void __launch_bounds__(128)
+gdn_post_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, int ld, const float* __restrict__ norm_w,
+                __nv_bfloat16* __restrict__ out, int kh, int vh, float eps, int gate_silu) {
+    __shared__ float red[4];
+    const int row = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    const float x = o[(static_cast<long long>(row) * vh + h) * kD + j];
+    float ss = x * x;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((j & 31) == 0) red[j >> 5] = ss;
+    __syncthreads();
+    const float tot = (red[0] + red[1]) + (red[2] + red[3]);
+    const int C = 2 * kh * kD + vh * kD;
+    const float z = __bfloat162float(proj[static_cast<long long>(row) * ld + C + h * kD + j]);
+    const float gz = gate_silu ? siluf_(z) : sigmoidf_(z);
+    out[(static_cast<long long>(row) * vh + h) * kD + j] = __float2bfloat16_rn(x * rsqrtf(tot / kD + eps) * norm_w[j] * gz);
+}
+
+// Prompt-class entry: scratch = fp32 [rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh] (q, k, v, o, beta, decay).
+const char* gdn_prefill(const void* proj, int ld, int rows, const float* conv_w, float* hist, float* state, const float* a_log,
+                        const float* dt_bias, const float* norm_w, const int* row_seq, const int* seq_slot, const int* seq_start,
+                        int n_seq, float* scratch, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
+                        cudaStream_t s) {
+    if (kd != kD || vd != kD) return "gdn kernels handle head dimension 128";
+    if (vh % kh != 0) return "value heads must be a multiple of key heads";
+    const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
+    float* qn = scratch;
+    float* kn = qn + static_cast<long long>(rows) * kh * kD;
+    float* vv = kn + static_cast<long long>(rows) * kh * kD;
+    float* oo = vv + static_cast<long long>(rows) * vh * kD;
+    float* bt = oo + static_cast<long long>(rows) * vh * kD;
+    float* dc = bt + static_cast<long long>(rows) * vh;
+    gdn_prep_kernel<<<dim3(rows, 2 * kh + vh), kD, 0, s>>>(pj, ld, conv_w, hist, a_log, dt_bias, row_seq, seq_slot, seq_start,
+                                                          qn, kn, vv, bt, dc, kh, vh);
+    const int C = 2 * kh * kD + vh * kD;
+    gdn_hist_kernel<<<dim3((C + 255) / 256, n_seq), 256, 0, s>>>(pj, ld, hist, seq_slot, seq_start, C);
+    gdn_scan_lean_kernel<<<dim3(vh * (kD / kLeanCols), n_seq), kLeanCols * kLeanParts, 0, s>>>(qn, kn, vv, bt, dc, state, seq_slot,
+                                                                                              seq_start, oo, kh, vh);
+    gdn_post_kernel<<<dim3(rows, vh), kD, 0, s>>>(oo, pj, ld, norm_w, static_cast<__nv_bfloat16*>(out), kh, vh, eps, gate_silu ? 1 : 0);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_prefill launch failed";
+}
+
 const char* gdn_scan(const void* proj, bool parts, int n_parts, long long part_stride, int ld, const float* conv_w, float* hist,
                      float* state, const float* a_log, const float* dt_bias, const float* norm_w, const int* seq_slot,
                      const int* seq_start, int n_seq, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,

@@ -12,4 +12,12 @@ const char* gdn_scan(const void* proj, bool parts, int n_parts, long long part_s
                      const int* seq_start, int n_seq, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
                      cudaStream_t s);
 
+// Prompt-class form of the same recurrence (three launches, no block-wide reductions in the serial walk).
+// proj bf16 [rows][ld]; row_seq[row] = index of the row's sequence; scratch fp32 of
+// rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh floats.
+const char* gdn_prefill(const void* proj, int ld, int rows, const float* conv_w, float* hist, float* state, const float* a_log,
+                        const float* dt_bias, const float* norm_w, const int* row_seq, const int* seq_slot, const int* seq_start,
+                        int n_seq, float* scratch, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
+                        cudaStream_t s);
+
 }  // namespace vade

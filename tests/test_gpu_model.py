@@ -63,3 +63,14 @@ def test_speculative_decoding_is_exact():
     plain = eng.generate(p, 32)
     spec = eng.generate(p, 32, draft_depth=3)
     assert plain.generated == spec.generated and spec.drafted > 0
+
+
+def test_prompt_slicing_does_not_change_tokens():
+    cfg = small_gpu_config()
+    p = _prompt(333, seed=5)
+    outs = []
+    for chunk in (2048, 128, 64):
+        eng = build_engine(cfg, device="cuda", seed=0, max_seq=768, prefill_chunk=chunk)
+        outs.append(eng.generate(p, 12).generated)
+        eng.model.ops.check_status()
+    assert outs[0] == outs[1] == outs[2]

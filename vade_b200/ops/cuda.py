@@ -136,6 +136,17 @@ class CudaOps:
         vh = lw.a_log.shape[0]
         kh = vh * cfg.linear_num_key_heads // cfg.linear_num_value_heads
         out = torch.empty(proj.shape[-2], vh * cfg.linear_value_head_dim, dtype=torch.bfloat16, device=self.device)
+        if batch.phase == "prefill" and proj.dim() == 2:
+            rows = proj.shape[0]
+            if "row_seq" not in d:
+                counts = torch.tensor([e - s for s, e in zip(batch.seq_start, batch.seq_start[1:])], device=self.device)
+                d["row_seq"] = torch.repeat_interleave(torch.arange(len(batch.seq_slots), device=self.device), counts).to(torch.int32)
+            scratch = torch.empty(rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh, dtype=torch.float32, device=self.device)
+            self.launches += 4
+            self.ext.gdn_prefill(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
+                                 d["row_seq"], d["seq_slot"], d["seq_start"], len(batch.seq_slots), scratch, out, kh, vh,
+                                 cfg.linear_key_head_dim, cfg.linear_value_head_dim, cfg.rms_norm_eps, False)
+            return out
         self.launches += 1
         self.ext.gdn_scan(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
                           d["seq_slot"], d["seq_start"], len(batch.seq_slots), out, kh, vh, cfg.linear_key_head_dim,
@@ -155,6 +166,15 @@ class CudaOps:
         self.ext.attn_prep(qkv, nq, nkv, hd, lw.q_norm, lw.k_norm, d["positions"], d["row_slot"], cache.block_table, q, gate,
                            kp, vp, cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_norm_eps)
         out = torch.empty(T, nq * hd, dtype=torch.bfloat16, device=self.device)
+        if batch.phase == "prefill":
+            # prompt class: tensor-core attention over the paged cache, one CTA per 128 query rows and head
+            if "seq_pos0" not in d:
+                d["seq_pos0"] = torch.tensor(batch.seq_pos0, dtype=torch.int32, device=self.device)
+            max_rows = max(e - s for s, e in zip(batch.seq_start, batch.seq_start[1:]))
+            self.launches += 2
+            self.ext.attn_prefill(q, gate, kp, vp, cache.block_table, d["seq_slot"], d["seq_start"], d["seq_pos0"],
+                                  len(batch.seq_slots), max_rows, nq, nkv, hd, out, self.status)
+            return out
         split = batch.phase == "decode"
         partial, n_split = None, 1
         if split:
