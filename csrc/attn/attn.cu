@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <cfloat>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "attn.h"
 #include "attn_static.h"
 #include <mutex>
@@ -45,6 +46,8 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, int ld, int n_par
                                  __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ gate_out,
                                  __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int rot,
                                  double log_theta, float eps) {
+    chain_release();
+    chain_wait();
     __shared__ float xs[kHD];
     __shared__ float red[8];
     const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
@@ -107,6 +110,8 @@ attn_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
                  const int* __restrict__ positions, const int* __restrict__ row_slot,
                  const int* __restrict__ block_table, int max_pages, int nq, int nkv, float scale,
                  float* __restrict__ partial, int n_split, __nv_bfloat16* __restrict__ out) {
+    chain_release();
+    chain_wait();
     extern __shared__ float q_s[];                 // [group][256]
     const int row = blockIdx.x, kvh = blockIdx.y, split = SPLIT ? blockIdx.z : 0;
     const int group = nq / nkv;
@@ -216,6 +221,8 @@ attn_split_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ positions,
                   const int* __restrict__ row_slot, const int* __restrict__ block_table, int max_pages, int nq, int nkv,
                   float scale, float* __restrict__ partial, int n_split) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_attn);                  // [128][264]
     __nv_bfloat16* Vs = Ks + kSplit * kKStride;                                       // [128][256]
@@ -306,6 +313,8 @@ attn_split_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
 __global__ void __launch_bounds__(1024)
 attn_merge_kernel(const float* __restrict__ partial, int n_split, const int* __restrict__ positions,
                   const __nv_bfloat16* __restrict__ gate_buf, int nq, __nv_bfloat16* __restrict__ out) {
+    chain_release();
+    chain_wait();
     extern __shared__ float sm_merge[];            // e[n_split], then 32 reduction words, then 4 x 256 class sums
     const int row = blockIdx.x, head = blockIdx.y;
     const int tid = threadIdx.x, cls = tid >> 8, d = tid & 255, lane = tid & 31, warp = tid >> 5;
@@ -364,10 +373,10 @@ const char* attn_prep(const void* qkv, bool parts, int n_parts, long long part_s
     __nv_bfloat16 *qo = static_cast<__nv_bfloat16*>(q_out), *go = static_cast<__nv_bfloat16*>(gate_out);
     __nv_bfloat16 *kp = static_cast<__nv_bfloat16*>(k_pages), *vp = static_cast<__nv_bfloat16*>(v_pages);
     if (parts)
-        attn_prep_kernel<true><<<grid, kHD, 0, s>>>(qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
+        launch_chained(attn_prep_kernel<true>, dim3(grid), dim3(kHD), 0, s, qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
                                                     block_table, max_pages, qo, go, kp, vp, rot, log(theta), eps);
     else
-        attn_prep_kernel<false><<<grid, kHD, 0, s>>>(qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
+        launch_chained(attn_prep_kernel<false>, dim3(grid), dim3(kHD), 0, s, qkv, ld, n_parts, part_stride, nq, nkv, q_norm, k_norm, positions, row_slot,
                                                      block_table, max_pages, qo, go, kp, vp, rot, log(theta), eps);
     return cudaGetLastError() == cudaSuccess ? nullptr : "attn_prep launch failed";
 }
@@ -394,11 +403,11 @@ const char* attn_rows(const void* q, const void* gate, const void* k_pages, cons
             configured = true;
         }
         if (sm_merge > 64 * 1024) return "context too long for the split merge";
-        attn_split_kernel<<<dim3(rows, nkv, n_split), group * 32, sm_split, s>>>(qp, kp, vp, positions, row_slot, block_table,
+        launch_chained(attn_split_kernel, dim3(dim3(rows, nkv, n_split)), dim3(group * 32), sm_split, s, qp, kp, vp, positions, row_slot, block_table,
                                                                                 max_pages, nq, nkv, scale, partial, n_split);
-        attn_merge_kernel<<<dim3(rows, nq), 1024, sm_merge, s>>>(partial, n_split, positions, gp, nq, o);
+        launch_chained(attn_merge_kernel, dim3(dim3(rows, nq)), dim3(1024), sm_merge, s, partial, n_split, positions, gp, nq, o);
     } else {
-        attn_rows_kernel<false><<<dim3(rows, nkv, 1), group * 32, sm, s>>>(qp, gp, kp, vp, positions, row_slot, block_table,
+        launch_chained(attn_rows_kernel<false>, dim3(dim3(rows, nkv, 1)), dim3(group * 32), sm, s, qp, gp, kp, vp, positions, row_slot, block_table,
                                                                           max_pages, nq, nkv, scale, partial, 1, o);
     }
     return cudaGetLastError() == cudaSuccess ? nullptr : "attention launch failed";

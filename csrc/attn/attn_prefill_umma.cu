@@ -18,6 +18,7 @@
 #include <cstdint>
 #include <mutex>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "attn.h"
 
 namespace vade {
@@ -74,6 +75,8 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const PrefillArgs a) {
+    chain_release();
+    chain_wait();
     const int tile = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
     const int r0 = a.seq_start[b], r1 = a.seq_start[b + 1];
     const int row0 = r0 + tile * kQRows;
@@ -325,7 +328,7 @@ const char* attn_prefill_umma(const void* q, const void* gate, const void* k_pag
         configured = true;
     }
     const dim3 grid((max_seq_rows + kQRows - 1) / kQRows, nq, n_seq);
-    attn_prefill_umma_kernel<<<grid, kThreads, smem, s>>>(tq, tk, tv, a);
+    launch_chained(attn_prefill_umma_kernel, dim3(grid), dim3(kThreads), smem, s, tq, tk, tv, a);
     return cudaGetLastError() == cudaSuccess ? nullptr : "attn_prefill launch failed";
 }
 

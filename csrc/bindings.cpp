@@ -33,7 +33,7 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
           int64_t epilogue, int64_t bn, int64_t ranges, int64_t tokens, int64_t ldo, int64_t out_range_stride,
           c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
           c10::optional<torch::Tensor> status, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
-          int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from) {
+          int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from, bool rows_kernel) {
     need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows on the GPU");
     need(w.is_cuda() && w.is_contiguous() && row_scale.is_cuda() && row_scale.scalar_type() == torch::kFloat32, "bad weights");
     need(out.is_cuda(), "bad output");
@@ -43,6 +43,7 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
     a.w = w.data_ptr(); a.nvfp4 = nvfp4; a.row_scale = row_scale.data_ptr<float>(); a.n_out = static_cast<int>(n_out);
     a.out = out.data_ptr(); a.ldo = static_cast<int>(ldo); a.out_range_stride = out_range_stride; a.epilogue = static_cast<int>(epilogue);
     a.tokens = static_cast<int>(tokens); a.bn = static_cast<int>(bn); a.ranges = static_cast<int>(ranges);
+    a.rows_kernel = rows_kernel;
     if (tasks.has_value()) {
         need(meta.has_value(), "grouped GEMM needs the task count");
         a.tasks = tasks->data_ptr<int>(); a.num_tasks = meta->data_ptr<int>(); a.max_tasks = static_cast<int>(max_tasks);

@@ -1,0 +1,49 @@
+// Chained kernel launches (programmatic dependent launch).
+//
+// Every kernel of the extension is launched through launch_chained(): the launch carries the
+// programmatic-stream-serialization attribute, so the kernel's blocks may become resident while the
+// previous kernel of the stream is still draining.  The device side of the contract, which every
+// kernel launched here follows:
+//   * chain_release() near the top lets the NEXT kernel's blocks start their own prologue early;
+//   * chain_wait() returns only when the previous kernel has completed and its writes are visible;
+//     a kernel touches no memory that another kernel writes (and writes nothing at all) before it.
+// What runs ahead of chain_wait() is therefore limited to prologues over immutable data: barrier and
+// tensor-memory set-up, tensor-map prefetch and, in the dense GEMM, the weight stream itself.
+// A decode step is a few hundred short dependent kernels; this overlap removes most of the
+// launch-to-launch gap between them.  VADE_PDL=0 turns the attribute off (plain stream order).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdlib>
+#include <utility>
+
+namespace vade {
+
+inline bool chained_launch_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("VADE_PDL");
+        return e == nullptr || e[0] != '0';
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = chained_launch_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
+}  // namespace vade

@@ -14,6 +14,7 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "gdn_scan.h"
 
 namespace vade {
@@ -51,6 +52,8 @@ gdn_scan_kernel(const void* __restrict__ proj, int ld, int n_parts, long long pa
                 const float* __restrict__ dt_bias, const float* __restrict__ norm_w,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                 __nv_bfloat16* __restrict__ out, int kh, int vh, float eps, int gate_silu) {
+    chain_release();
+    chain_wait();
     extern __shared__ float sm[];
     constexpr int rep = REP;
     float* q_s = sm;                         // [rep][128]
@@ -143,6 +146,8 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
                 const float* __restrict__ a_log, const float* __restrict__ dt_bias, const int* __restrict__ row_seq,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start, float* __restrict__ qn, float* __restrict__ kn,
                 float* __restrict__ vv, float* __restrict__ beta, float* __restrict__ decay, int kh, int vh) {
+    chain_release();
+    chain_wait();
     __shared__ float red[4];
     const int row = blockIdx.x, unit = blockIdx.y, j = threadIdx.x;
     const int C = 2 * kh * kD + vh * kD;
@@ -186,6 +191,8 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ proj, int ld, const float* __r
 // New history = the last three raw rows of [old history, this pass's rows]; one thread per (sequence, channel).
 __global__ void gdn_hist_kernel(const __nv_bfloat16* __restrict__ proj, int ld, float* __restrict__ hist,
                                 const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int C) {
+    chain_release();
+    chain_wait();
     const int b = blockIdx.y;
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= C) return;
@@ -220,6 +227,8 @@ __global__ void __launch_bounds__(kLeanCols * kLeanParts)
 gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                      const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                      const int* __restrict__ seq_slot, const int* __restrict__ seq_start, float* __restrict__ o_out, int kh, int vh) {
+    chain_release();
+    chain_wait();
     __shared__ __align__(16) float qk[kLeanRing][2 * kD];          // [slot][q(128) | k(128)]
     __shared__ __align__(16) float vs[kLeanRing][kLeanCols];
     __shared__ __align__(16) float bd[kLeanRing][4];               // beta, decay
@@ -229,14 +238,15 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
     const int part = threadIdx.x & (kLeanParts - 1);
     const int lcol = threadIdx.x >> 3;
     const int col = cg * kLeanCols + lcol;
-    const int i0 = part * kLeanRows;
+    // thread `part` owns state rows 4 * (part + 8 * jj) + c (jj, c in 0..3): the eight lanes of a column read
+    // eight consecutive float4 of k / q, which is bank-conflict free
     const int slot = seq_slot[b];
     const int r0 = seq_start[b], r1 = seq_start[b + 1];
     if (r0 >= r1) return;
     float S[kLeanRows];
-    float* sp = state + ((static_cast<long long>(slot) * vh + vhead) * kD + i0) * kD + col;
+    float* sp = state + ((static_cast<long long>(slot) * vh + vhead) * kD) * kD + col;
 #pragma unroll
-    for (int i = 0; i < kLeanRows; ++i) S[i] = sp[i * kD];
+    for (int i = 0; i < kLeanRows; ++i) S[i] = sp[(4 * (part + 8 * (i >> 2)) + (i & 3)) * kD];
     // row rr of the tile -> ring slot (rr - r0) % kLeanRing, one commit group per row (empty past the end)
     auto stage = [&](int rr) {
         if (rr < r1) {
@@ -255,12 +265,12 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         __syncthreads();                                                                // ... for every thread; row r - 1 is fully consumed
         stage(r + kLeanAhead);                                                          // overwrites the slot of row r - 1
         const int sl = (r - r0) % kLeanRing;
-        const float4* q4 = reinterpret_cast<const float4*>(qk[sl] + i0);
-        const float4* k4 = reinterpret_cast<const float4*>(qk[sl] + kD + i0);
+        const float4* q4 = reinterpret_cast<const float4*>(qk[sl]) + part;
+        const float4* k4 = reinterpret_cast<const float4*>(qk[sl] + kD) + part;
         const float v = vs[sl][lcol], bt = bd[sl][0], dc = bd[sl][1];
         float4 kk[kLeanRows / 4];
 #pragma unroll
-        for (int i = 0; i < kLeanRows / 4; ++i) kk[i] = k4[i];
+        for (int i = 0; i < kLeanRows / 4; ++i) kk[i] = k4[8 * i];
         float m0 = 0.f, m1 = 0.f;
 #pragma unroll
         for (int i = 0; i < kLeanRows / 4; ++i) {
@@ -275,7 +285,7 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         float o0 = 0.f, o1 = 0.f;
 #pragma unroll
         for (int i = 0; i < kLeanRows / 4; ++i) {
-            const float4 qq = q4[i];
+            const float4 qq = q4[8 * i];
             S[4 * i] += kk[i].x * delta; S[4 * i + 1] += kk[i].y * delta; S[4 * i + 2] += kk[i].z * delta; S[4 * i + 3] += kk[i].w * delta;
             o0 += S[4 * i] * qq.x; o1 += S[4 * i + 1] * qq.y; o0 += S[4 * i + 2] * qq.z; o1 += S[4 * i + 3] * qq.w;
         }
@@ -287,12 +297,14 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < kLeanRows; ++i) sp[i * kD] = S[i];
+    for (int i = 0; i < kLeanRows; ++i) sp[(4 * (part + 8 * (i >> 2)) + (i & 3)) * kD] = S[i];
 }
 
 __global__ void __launch_bounds__(128)
 gdn_post_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, int ld, const float* __restrict__ norm_w,
                 __nv_bfloat16* __restrict__ out, int kh, int vh, float eps, int gate_silu) {
+    chain_release();
+    chain_wait();
     __shared__ float red[4];
     const int row = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
     const float x = o[(static_cast<long long>(row) * vh + h) * kD + j];
@@ -322,13 +334,13 @@ const char* gdn_prefill(const void* proj, int ld, int rows, const float* conv_w,
     float* oo = vv + static_cast<long long>(rows) * vh * kD;
     float* bt = oo + static_cast<long long>(rows) * vh * kD;
     float* dc = bt + static_cast<long long>(rows) * vh;
-    gdn_prep_kernel<<<dim3(rows, 2 * kh + vh), kD, 0, s>>>(pj, ld, conv_w, hist, a_log, dt_bias, row_seq, seq_slot, seq_start,
+    launch_chained(gdn_prep_kernel, dim3(dim3(rows, 2 * kh + vh)), dim3(kD), 0, s, pj, ld, conv_w, hist, a_log, dt_bias, row_seq, seq_slot, seq_start,
                                                           qn, kn, vv, bt, dc, kh, vh);
     const int C = 2 * kh * kD + vh * kD;
-    gdn_hist_kernel<<<dim3((C + 255) / 256, n_seq), 256, 0, s>>>(pj, ld, hist, seq_slot, seq_start, C);
-    gdn_scan_lean_kernel<<<dim3(vh * (kD / kLeanCols), n_seq), kLeanCols * kLeanParts, 0, s>>>(qn, kn, vv, bt, dc, state, seq_slot,
+    launch_chained(gdn_hist_kernel, dim3(dim3((C + 255) / 256, n_seq)), dim3(256), 0, s, pj, ld, hist, seq_slot, seq_start, C);
+    launch_chained(gdn_scan_lean_kernel, dim3(dim3(vh * (kD / kLeanCols), n_seq)), dim3(kLeanCols * kLeanParts), 0, s, qn, kn, vv, bt, dc, state, seq_slot,
                                                                                               seq_start, oo, kh, vh);
-    gdn_post_kernel<<<dim3(rows, vh), kD, 0, s>>>(oo, pj, ld, norm_w, static_cast<__nv_bfloat16*>(out), kh, vh, eps, gate_silu ? 1 : 0);
+    launch_chained(gdn_post_kernel, dim3(dim3(rows, vh)), dim3(kD), 0, s, oo, pj, ld, norm_w, static_cast<__nv_bfloat16*>(out), kh, vh, eps, gate_silu ? 1 : 0);
     return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_prefill launch failed";
 }
 
@@ -343,7 +355,7 @@ const char* gdn_scan(const void* proj, bool parts, int n_parts, long long part_s
     const dim3 grid(kh, n_seq);
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
     const int gs = gate_silu ? 1 : 0;
-#define VADE_GDN(REP, PARTS) gdn_scan_kernel<REP, PARTS><<<grid, REP * 128, smem, s>>>(proj, ld, n_parts, part_stride, conv_w, hist, \
+#define VADE_GDN(REP, PARTS) launch_chained((gdn_scan_kernel<REP, PARTS>), dim3(grid), dim3(REP * 128), smem, s, proj, ld, n_parts, part_stride, conv_w, hist, \
         state, a_log, dt_bias, norm_w, seq_slot, seq_start, o, kh, vh, eps, gs)
     if (parts) {
         if (rep == 1) VADE_GDN(1, true); else if (rep == 2) VADE_GDN(2, true); else VADE_GDN(3, true);

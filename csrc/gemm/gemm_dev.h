@@ -1,0 +1,39 @@
+// Device-side argument block shared by the projection GEMM kernels (tcgen05 tiles and the
+// register-dataflow decode kernel), plus the tile geometry of the packed NVFP4 weight layout.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "../common/ptx.cuh"
+#include "umma_gemm.h"
+
+namespace vade {
+
+constexpr int kTileM = 128;             // weight rows per tile block
+constexpr int kTileK = 64;              // columns per tile block
+constexpr int kWBlockBytes = 4608;      // 128 x 16 B (columns 0..31), 128 x 16 B (columns 32..63), 128 x 4 scale bytes
+
+struct GemmDev {
+    const uint8_t* w_tiles;
+    const float* row_scale;
+    void* out;
+    const int4* tasks;
+    const int* num_tasks;
+    uint32_t* status;
+    long long w_expert_stride;      // bytes between stacked matrices (NVFP4 tiles)
+    long long out_range_stride;     // elements between range partials
+    int rs_expert_stride;
+    int n_out;
+    int kb_total;                   // K / 64 of one matrix
+    int kb_per_range;
+    int tokens;
+    int ldo;
+    PeerExchange px;                // px.n > 0: the epilogue stores into every rank's buffer and signals
+};
+
+// Fills the device argument block from the host arguments; returns an error text or nullptr.
+const char* fill_gemm_dev(const GemmArgs& h, GemmDev* d);
+
+// Decode-class kernel (rows_mma.cu): same arguments, NVFP4 weights only, epilogue 0 or 1.
+const char* rows_mma_gemm(const GemmArgs& h, const GemmDev& d, cudaStream_t stream);
+
+}  // namespace vade

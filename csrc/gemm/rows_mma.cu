@@ -1,0 +1,236 @@
+// Decode-class projection for a handful of token rows (1..64), NVFP4 weights, sm_100a.
+//
+//   D[m, n] = sum_k W[m, k] * X[n, k]        W = packed weight rows, X = token rows
+//
+// With one to a few token rows the projection is a stream over the packed weights: there is no tile
+// reuse to stage, so the tcgen05 pipeline's shared-memory round trip (expand the A tile, fence, barrier,
+// MMA, commit, TMEM read-back) is pure latency.  This kernel is a register dataflow instead:
+//   global -> registers   every thread issues ALL of its 32-bit weight words for up to 8 K blocks up
+//                         front (before it waits for the previous kernel: weights are immutable);
+//   registers -> bf16     e2m1 pairs expand to bf16x2 and take their e4m3 block scale exactly
+//                         (cvt.rn.f16x2.e2m1x2, a bit shift, mul.rn.bf16x2);
+//   bf16 -> fp32          warp-level mma (m16n8k16, fp32 accumulate); no barrier in the main loop.
+// The 16 K slots of one mma are a fixed permutation of 16 columns (the same permutation is applied to
+// the token operand), chosen so that a thread's four A registers of two consecutive mmas are the four
+// bytes of ONE 32-bit word of the packed row: thread (g, t) owns columns 8t..8t+7 of each 32-column half.
+// Token rows are the N operand (8 per mma): the value of an output never depends on how many rows share
+// the pass or on which slot a row occupies.
+//
+// One CTA = 4 warps x 16 weight rows (half of a 128-row tile block) x one K range.
+// grid = (2 x row tiles, token groups or grouped tasks, K ranges).  Output, row scale, grouped tasks and
+// the peer-store epilogue are those of the tcgen05 kernel (umma_gemm.cu).
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "../common/ptx.cuh"
+#include "../common/launch.h"
+#include "gemm_dev.h"
+
+namespace vade {
+
+constexpr int kRowsThreads = 128;
+constexpr int kChunk = 8;                                  // K blocks kept in flight per thread
+constexpr int kXStride = kChunk * 128 + 64;                // bytes per staged token row (odd multiple of 64: conflict-free 16-byte reads)
+
+// One byte (two e2m1 values, low nibble first) -> bf16x2 of value * scale, where `mult` holds
+// bf16(scale * 2^112) in both halves: f16 bits >> 3 read as bf16 equal value * 2^-112 (exact).
+__device__ __forceinline__ uint32_t expand_pair(uint32_t word, int byte, uint32_t mult) {
+    uint32_t h2, out;
+    const uint16_t b = static_cast<uint16_t>((word >> (8 * byte)) & 0xFFu);
+    asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(b));
+    const uint32_t p = ((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u);
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(p), "r"(mult));
+    return out;
+}
+
+// Scale bytes `b` and `b + 2` of a row's four e4m3 block scales -> two bf16x2 multipliers (scale * 2^112).
+__device__ __forceinline__ void scale_mults(uint32_t scales, int b, uint32_t* m_half0, uint32_t* m_half1) {
+    const uint32_t pair = __byte_perm(scales, 0u, static_cast<uint32_t>(b | ((b + 2) << 4)) | 0x4400u);
+    uint32_t h01;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(static_cast<uint16_t>(pair & 0xFFFFu)));
+    const __half2 hh = *reinterpret_cast<const __half2*>(&h01);
+    const uint32_t b0 = __float_as_uint(__low2float(hh) * 0x1p112f) >> 16;     // exact: <= 4 significant bits
+    const uint32_t b1 = __float_as_uint(__high2float(hh) * 0x1p112f) >> 16;
+    *m_half0 = b0 | (b0 << 16);
+    *m_half1 = b1 | (b1 << 16);
+}
+
+__device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t ldg_stream(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+template <int NT, int EPI>
+__global__ void __launch_bounds__(kRowsThreads)
+rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx) {
+    chain_release();
+    extern __shared__ __align__(16) uint8_t xs[];          // [NT * 8 token rows][kXStride]
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int mtile = blockIdx.x >> 1;
+    const int rit = (blockIdx.x & 1) * 64 + warp * 16 + g;  // this thread's first row inside the tile block (second: + 8)
+    const int range = blockIdx.z;
+    const int kb0 = range * a.kb_per_range;
+    const int nkb = a.kb_per_range;
+
+    int expert = 0, row0, nrows, orow0;
+    bool active = true;
+    bool waited = false;
+    if (a.tasks != nullptr) {
+        chain_wait();                                      // the task list is the routing kernel's output
+        waited = true;
+        active = static_cast<int>(blockIdx.y) < *a.num_tasks;
+        const int4 task = active ? a.tasks[blockIdx.y] : make_int4(0, 0, 0, 0);
+        expert = task.x; row0 = task.y; nrows = task.z; orow0 = task.w;
+    } else {
+        row0 = blockIdx.y * (NT * 8);
+        nrows = min(NT * 8, a.tokens - row0);
+        orow0 = row0;
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+    if (active) {
+        const uint8_t* wb = a.w_tiles + static_cast<long long>(expert) * a.w_expert_stride
+                          + (static_cast<long long>(mtile) * a.kb_total + kb0) * kWBlockBytes;
+        for (int c0 = 0; c0 < nkb; c0 += kChunk) {
+            const int nc = min(kChunk, nkb - c0);
+            uint32_t wq[kChunk][4], ws[kChunk][2];
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+                if (i < nc) {
+                    const uint8_t* blk = wb + static_cast<long long>(c0 + i) * kWBlockBytes;
+                    wq[i][0] = ldg_stream(blk + rit * 16 + 4 * t);                 // row g,     columns  0..31
+                    wq[i][1] = ldg_stream(blk + (rit + 8) * 16 + 4 * t);           // row g + 8, columns  0..31
+                    wq[i][2] = ldg_stream(blk + 2048 + rit * 16 + 4 * t);          // row g,     columns 32..63
+                    wq[i][3] = ldg_stream(blk + 2048 + (rit + 8) * 16 + 4 * t);    // row g + 8, columns 32..63
+                    ws[i][0] = ldg_stream(blk + 4096 + rit * 4);
+                    ws[i][1] = ldg_stream(blk + 4096 + (rit + 8) * 4);
+                }
+            }
+            if (!waited) {
+                chain_wait();                              // from here on the token rows are valid
+                waited = true;
+            }
+            if (c0 > 0) __syncthreads();                   // the previous chunk's token columns are no longer read
+            const int pieces = nc * 8;                     // 16-byte pieces per staged token row
+            for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRowsThreads) {
+                const int j = p / pieces;
+                const int q = p - j * pieces;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (j < nrows)
+                    v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row0 + j) * ldx + (kb0 + c0) * kTileK + q * 8);
+                *reinterpret_cast<uint4*>(xs + j * kXStride + q * 16) = v;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+                if (i < nc) {
+                    uint32_t m0[2], m1[2];                 // multipliers of rows g / g + 8 for the two halves
+                    scale_mults(ws[i][0], t >> 1, &m0[0], &m0[1]);
+                    scale_mults(ws[i][1], t >> 1, &m1[0], &m1[1]);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t w0 = wq[i][2 * h], w1 = wq[i][2 * h + 1];
+                        uint32_t A[8];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            A[2 * b] = expand_pair(w0, b, m0[h]);
+                            A[2 * b + 1] = expand_pair(w1, b, m1[h]);
+                        }
+#pragma unroll
+                        for (int n = 0; n < NT; ++n) {
+                            const uint4 bx = *reinterpret_cast<const uint4*>(xs + (n * 8 + g) * kXStride + i * 128 + h * 64 + t * 16);
+                            mma_bf16(acc[n], A[0], A[1], A[2], A[3], bx.x, bx.y);
+                            mma_bf16(acc[n], A[4], A[5], A[6], A[7], bx.z, bx.w);
+                        }
+                    }
+                }
+            }
+        }
+
+        // ---------------- epilogue: row scale, store (plain, range partial, or every rank's exchange buffer)
+        const long long px_base = a.px.n > 0 ? static_cast<long long>(exchange_parity(a.px)) * a.px.half_stride : 0;
+        const bool px_all = expert < a.px.local_only_from;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int m = mtile * kTileM + rit + 8 * r;
+            if (m >= a.n_out) continue;
+            const float rs = a.row_scale[static_cast<long long>(expert) * a.rs_expert_stride + m];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = n * 8 + 2 * t + e;
+                    if (j >= nrows) continue;
+                    const float y = acc[n][2 * r + e] * rs;
+                    const long long tok = orow0 + j;
+                    if (a.px.n == 0) {
+                        if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
+                        else reinterpret_cast<float*>(a.out)[range * a.out_range_stride + tok * a.ldo + m] = y;
+                    } else {
+                        const long long at = px_base + (EPI == 0 ? 0 : range * a.out_range_stride) + tok * a.ldo + m;
+                        if (px_all) {
+                            for (int d = 0; d < a.px.n; ++d) {
+                                if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[d])[at] = __float2bfloat16_rn(y);
+                                else reinterpret_cast<float*>(a.px.out[d])[at] = y;
+                            }
+                        } else {
+                            if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[a.px.self])[at] = __float2bfloat16_rn(y);
+                            else reinterpret_cast<float*>(a.px.out[a.px.self])[at] = y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (a.px.n > 0) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
+    }
+}
+
+template <int NT, int EPI>
+static const char* launch_rows(const GemmArgs& h, const GemmDev& d, dim3 grid, cudaStream_t stream) {
+    constexpr int smem = NT * 8 * kXStride;
+    static bool configured = false;
+    auto kern = rows_mma_kernel<NT, EPI>;
+    if (!configured) {
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return "cannot raise shared memory limit";
+        configured = true;
+    }
+    launch_chained(kern, grid, dim3(kRowsThreads), smem, stream, d, static_cast<const __nv_bfloat16*>(h.x), h.ldx);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "kernel launch failed";
+}
+
+const char* rows_mma_gemm(const GemmArgs& h, const GemmDev& d, cudaStream_t stream) {
+    const int group = h.tasks != nullptr ? h.bn : (h.tokens < 64 ? h.tokens : 64);   // token rows per CTA
+    if (group < 1 || group > 64) return "the decode-class kernel takes 1..64 token rows per task";
+    const int nt = group <= 8 ? 1 : group <= 16 ? 2 : group <= 32 ? 4 : 8;
+    const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
+    const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + nt * 8 - 1) / (nt * 8);
+    if (y <= 0) return "empty grid";
+    const dim3 grid(2 * m_tiles, y, h.ranges);
+#define VADE_ROWS(NT_) return h.epilogue == 0 ? launch_rows<NT_, 0>(h, d, grid, stream) : launch_rows<NT_, 1>(h, d, grid, stream)
+    switch (nt) {
+        case 1: VADE_ROWS(1);
+        case 2: VADE_ROWS(2);
+        case 4: VADE_ROWS(4);
+        default: VADE_ROWS(8);
+    }
+#undef VADE_ROWS
+}
+
+}  // namespace vade

@@ -7,8 +7,10 @@
 // per CTA), so the per-output accumulation never depends on how many rows share a pass.
 //
 // One CTA computes one 128 x BN output tile over one K range:
-//   warp 0      producer: one bulk copy (NVFP4 block) or tiled TMA load (bf16 weights) plus one
-//               tiled TMA load of the X tile per 64-column K block, STAGES deep
+//   warp 0      weight producer: one 4608-byte bulk copy per 64-column K block into a DEEP ring (RAW
+//               stages; packed blocks are small, so many can be in flight to cover HBM latency)
+//   warp 10     activation producer: one tiled TMA load of the X tile per K block into the shallow
+//               A/B ring (STAGES); with bf16 weights it also loads the weight tile there
 //   warps 2..9  NVFP4 only: expand nibbles to bf16 (e2m1 * e4m3, exact) into the 128-byte
 //               swizzled A tile (one thread per row and 32-column half); afterwards the epilogue:
 //               tcgen05.ld, row scale, store (each warp set takes half of the token columns)
@@ -23,54 +25,27 @@
 #include <cstdio>
 #include <mutex>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "umma_gemm.h"
+#include "gemm_dev.h"
 
 namespace vade {
 
-constexpr int kTileM = 128;
-constexpr int kTileK = 64;
-constexpr int kWBlockBytes = 4608;
 constexpr int kAStageBytes = kTileM * kTileK * 2;
-constexpr int kThreads = 320;             // warp 0 producer, warp 1 MMA, warps 2..9 dequant + epilogue
+constexpr int kThreads = 352;             // warp 0 weight producer, warp 1 MMA, warps 2..9 dequant + epilogue, warp 10 activation producer
 
-struct GemmDev {
-    const uint8_t* w_tiles;
-    const float* row_scale;
-    void* out;
-    const int4* tasks;
-    const int* num_tasks;
-    uint32_t* status;
-    long long w_expert_stride;      // bytes between stacked matrices (NVFP4 tiles)
-    long long out_range_stride;     // elements between range partials
-    int rs_expert_stride;
-    int n_out;
-    int kb_total;                   // K / 64 of one matrix
-    int kb_per_range;
-    int tokens;
-    int ldo;
-    PeerExchange px;                // px.n > 0: the epilogue stores into every rank's buffer and signals
-};
 
-template <int BN, int STAGES, bool NVFP4, int EPI>
-__global__ void __launch_bounds__(kThreads, (BN <= 32 ? 2 : 1))
+// Resident CTAs per SM that the stage memory allows (the launch bound caps registers to match).
+constexpr int gemm_ctas_per_sm(int stage_bytes) { return stage_bytes <= 73 * 1024 ? 3 : stage_bytes <= 110 * 1024 ? 2 : 1; }
+
+template <int BN, int STAGES, int RAW, bool NVFP4, int EPI>
+__global__ void __launch_bounds__(kThreads, gemm_ctas_per_sm(STAGES * (kAStageBytes + BN * kTileK * 2) + (NVFP4 ? RAW * kWBlockBytes : 0)))
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmDev a) {
     constexpr int kBStageBytes = BN * kTileK * 2;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
-    constexpr uint32_t kTxBytes = (NVFP4 ? kWBlockBytes : kAStageBytes) + kBStageBytes;
+    constexpr uint32_t kTxBytes = (NVFP4 ? 0 : kAStageBytes) + kBStageBytes;      // bytes landing on full[s]
 
-    int expert = 0, row0, nrows, orow0;
-    if (a.tasks != nullptr) {
-        if (static_cast<int>(blockIdx.y) >= *a.num_tasks) {
-            if (a.px.n > 0 && threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
-            return;
-        }
-        const int4 t = a.tasks[blockIdx.y];
-        expert = t.x; row0 = t.y; nrows = t.z; orow0 = t.w;
-    } else {
-        row0 = blockIdx.y * BN;
-        nrows = min(BN, a.tokens - row0);
-        orow0 = row0;
-    }
+    chain_release();
     const int mtile = blockIdx.x;
     const int range = blockIdx.z;
     const int kb0 = range * a.kb_per_range;
@@ -81,12 +56,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     uint8_t* sA = smem;
     uint8_t* sB = sA + STAGES * kAStageBytes;
     uint8_t* sW = sB + STAGES * kBStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sW + (NVFP4 ? STAGES * kWBlockBytes : 0));
-    uint64_t* full = bars;
-    uint64_t* aready = bars + STAGES;
-    uint64_t* empty = bars + 2 * STAGES;
-    uint64_t* tmem_full = bars + 3 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sW + (NVFP4 ? RAW * kWBlockBytes : 0));
+    uint64_t* full = bars;                          // [STAGES] X tile (and bf16 weight tile) landed
+    uint64_t* aready = bars + STAGES;               // [STAGES] A tile expanded by the dequant warps
+    uint64_t* empty = bars + 2 * STAGES;            // [STAGES] MMAs that read the stage finished
+    uint64_t* raw_full = bars + 3 * STAGES;         // [RAW] packed weight block landed
+    uint64_t* raw_empty = raw_full + RAW;           // [RAW] all dequant threads have read the block
+    uint64_t* tmem_full = raw_empty + RAW;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -97,6 +74,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             mbar_init(&full[s], 1);
             mbar_init(&aready[s], 256);
             mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < RAW; ++s) {
+            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_empty[s], 256);
         }
         mbar_init(tmem_full, 1);
         *abort_flag = 0;
@@ -113,22 +94,48 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_d = *tmem_slot;
 
+    // Dense launches stream weights (immutable) ahead of the previous kernel's completion; only the
+    // weight producer may do so.  Grouped launches read their task, written by the routing kernel, first.
+    int expert = 0, row0, nrows, orow0;
+    bool active = true;
+    if (a.tasks != nullptr) {
+        chain_wait();
+        active = static_cast<int>(blockIdx.y) < *a.num_tasks;
+        const int4 t = active ? a.tasks[blockIdx.y] : make_int4(0, 0, 0, 0);
+        expert = t.x; row0 = t.y; nrows = t.z; orow0 = t.w;
+    } else {
+        row0 = blockIdx.y * BN;
+        nrows = min(BN, a.tokens - row0);
+        orow0 = row0;
+        if (!(NVFP4 && warp == 0)) chain_wait();
+    }
+
     auto fail = [&](uint32_t code) {
         *abort_flag = 1;
         if (a.status != nullptr) atomicMax(a.status, code);
     };
 
-    if (warp == 0) {
-        if (lane == 0) {
+    if (!active) {
+        // an idle task slot: nothing to compute, fall through to the common exit
+    } else if (warp == 0) {
+        if (NVFP4 && lane == 0) {
             const uint8_t* wbase = a.w_tiles + static_cast<long long>(expert) * a.w_expert_stride
                                  + (static_cast<long long>(mtile) * a.kb_total + kb0) * kWBlockBytes;
             for (int i = 0; i < nkb; ++i) {
+                const int rs = i % RAW;
+                if (!mbar_wait(&raw_empty[rs], ((i / RAW) & 1) ^ 1)) { fail(1); break; }
+                mbar_expect_tx(&raw_full[rs], kWBlockBytes);
+                bulk_load(sW + rs * kWBlockBytes, wbase + static_cast<long long>(i) * kWBlockBytes, kWBlockBytes, &raw_full[rs]);
+            }
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait(&empty[s], ph ^ 1)) { fail(1); break; }
+                if (!mbar_wait(&empty[s], ph ^ 1)) { fail(6); break; }
                 mbar_expect_tx(&full[s], kTxBytes);
-                if (NVFP4) bulk_load(sW + s * kWBlockBytes, wbase + static_cast<long long>(i) * kWBlockBytes, kWBlockBytes, &full[s]);
-                else tma_load_2d(sA + s * kAStageBytes, &tmap_w, (kb0 + i) * kTileK, mtile * kTileM, &full[s]);
+                if (!NVFP4) tma_load_2d(sA + s * kAStageBytes, &tmap_w, (kb0 + i) * kTileK, mtile * kTileM, &full[s]);
                 tma_load_2d(sB + s * kBStageBytes, &tmap_x, (kb0 + i) * kTileK, row0, &full[s]);
             }
         }
@@ -157,10 +164,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait(&full[s], ph)) { fail(4); break; }
-                const uint8_t* raw = sW + s * kWBlockBytes;
+                const int rs = i % RAW;
+                if (!mbar_wait(&raw_full[rs], (i / RAW) & 1)) { fail(4); break; }
+                const uint8_t* raw = sW + rs * kWBlockBytes;
                 const uint4 q = *reinterpret_cast<const uint4*>(raw + half * 2048 + t * 16);
                 const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 4096 + t * 4);
+                mbar_arrive(&raw_empty[rs]);                          // the block is in registers; its slot may be refilled
+                if (!mbar_wait(&empty[s], ph ^ 1)) { fail(7); break; }   // the MMAs of the stage's previous use are done
                 // two e4m3 block scales -> bf16x2 multipliers (scale * 2^112)
                 uint32_t mult[2];
                 {
@@ -248,6 +258,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (a.px.n > 0) __threadfence_system();
     tc_fence_before_sync();
     __syncthreads();
+    chain_wait();                                 // the weight producer never waited; a no-op for the rest
     if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
     if (a.px.n > 0 && threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
 }
@@ -282,49 +293,34 @@ static bool make_tmap(CUtensorMap* m, const void* base, uint64_t inner, uint64_t
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool NVFP4, int EPI>
+template <int BN, int STAGES, int RAW, bool NVFP4, int EPI>
 static const char* launch_one(const GemmArgs& h, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, dim3 grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (kAStageBytes + BN * kTileK * 2 + (NVFP4 ? kWBlockBytes : 0)) + (3 * STAGES + 2) * 8 + 1024;
+    constexpr int smem = STAGES * (kAStageBytes + BN * kTileK * 2) + (NVFP4 ? RAW * kWBlockBytes : 0) + (3 * STAGES + 2 * RAW + 2) * 8 + 1024;
     static bool configured = false;
-    auto kern = umma_gemm_kernel<BN, STAGES, NVFP4, EPI>;
+    auto kern = umma_gemm_kernel<BN, STAGES, RAW, NVFP4, EPI>;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return "cannot raise shared memory limit";
         configured = true;
     }
-    kern<<<grid, kThreads, smem, stream>>>(tx, tw, d);
+    launch_chained(kern, dim3(grid), dim3(kThreads), smem, stream, tx, tw, d);
     return cudaGetLastError() == cudaSuccess ? nullptr : "kernel launch failed";
 }
 
 template <bool NVFP4, int EPI>
 static const char* launch_bn(const GemmArgs& h, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, dim3 grid, cudaStream_t s) {
     switch (h.bn) {
-        case 16:  return launch_one<16, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
-        case 32:  return launch_one<32, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
-        case 64:  return launch_one<64, 6, NVFP4, EPI>(h, tx, tw, d, grid, s);
-        case 128: return launch_one<128, 5, NVFP4, EPI>(h, tx, tw, d, grid, s);
-        case 256: return launch_one<256, 4, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 16:  return launch_one<16, NVFP4 ? 2 : 4, NVFP4 ? 8 : 1, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 32:  return launch_one<32, NVFP4 ? 2 : 4, NVFP4 ? 7 : 1, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 64:  return launch_one<64, NVFP4 ? 3 : 6, NVFP4 ? 8 : 1, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 128: return launch_one<128, NVFP4 ? 4 : 5, NVFP4 ? 8 : 1, NVFP4, EPI>(h, tx, tw, d, grid, s);
+        case 256: return launch_one<256, NVFP4 ? 3 : 4, NVFP4 ? 8 : 1, NVFP4, EPI>(h, tx, tw, d, grid, s);
         default:  return "token tile must be 16, 32, 64, 128 or 256";
     }
 }
 
-const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
-    if (h.k % kTileK != 0 || h.k <= 0) return "K must be a positive multiple of 64";
-    if (h.ranges < 1 || (h.k / kTileK) % h.ranges != 0) return "K blocks must divide evenly into ranges";
-    if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
-    if ((reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
-    if (h.x_rows <= 0 || h.n_out <= 0) return "empty problem";
-    CUtensorMap tx, tw;
-    if (!make_tmap(&tx, h.x, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.x_rows), static_cast<uint64_t>(h.ldx) * 2, h.bn))
-        return "cuTensorMapEncodeTiled failed for the activation tensor";
+const char* fill_gemm_dev(const GemmArgs& h, GemmDev* dp) {
+    GemmDev& d = *dp;
     const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
-    if (h.nvfp4) {
-        if ((reinterpret_cast<uintptr_t>(h.w) & 15) != 0) return "weight tiles must be 16-byte aligned";
-        tw = tx;
-    } else {
-        if (!make_tmap(&tw, h.w, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.n_out), static_cast<uint64_t>(h.k) * 2, kTileM))
-            return "cuTensorMapEncodeTiled failed for the weight tensor";
-    }
-    GemmDev d;
     d.w_tiles = static_cast<const uint8_t*>(h.w);
     d.row_scale = h.row_scale;
     d.out = h.out;
@@ -352,6 +348,32 @@ const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
         d.px.n = h.peers;
         d.px.self = h.peer_self;
         if (h.peer_local_only_from >= 0) d.px.local_only_from = h.peer_local_only_from;
+    }
+    return nullptr;
+}
+
+const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
+    if (h.k % kTileK != 0 || h.k <= 0) return "K must be a positive multiple of 64";
+    if (h.ranges < 1 || (h.k / kTileK) % h.ranges != 0) return "K blocks must divide evenly into ranges";
+    if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
+    if ((reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
+    if (h.x_rows <= 0 || h.n_out <= 0) return "empty problem";
+    if (h.nvfp4 && (reinterpret_cast<uintptr_t>(h.w) & 15) != 0) return "weight tiles must be 16-byte aligned";
+    GemmDev d;
+    if (const char* err = fill_gemm_dev(h, &d)) return err;
+    if (h.rows_kernel) {
+        if (!h.nvfp4 || h.epilogue == 2) return "the decode-class kernel takes NVFP4 weights and epilogue 0 or 1";
+        return rows_mma_gemm(h, d, stream);
+    }
+    CUtensorMap tx, tw;
+    if (!make_tmap(&tx, h.x, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.x_rows), static_cast<uint64_t>(h.ldx) * 2, h.bn))
+        return "cuTensorMapEncodeTiled failed for the activation tensor";
+    const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
+    if (h.nvfp4) {
+        tw = tx;
+    } else {
+        if (!make_tmap(&tw, h.w, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.n_out), static_cast<uint64_t>(h.k) * 2, kTileM))
+            return "cuTensorMapEncodeTiled failed for the weight tensor";
     }
     const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + h.bn - 1) / h.bn;
     if (y <= 0) return "empty grid";

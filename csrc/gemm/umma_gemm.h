@@ -25,6 +25,7 @@ struct GemmArgs {
     int tokens = 0;                         // dense: number of token rows
     int bn = 16;                            // token tile (16, 32, 64, 128, 256)
     int ranges = 1;                         // K ranges (grid.z); > 1 requires epilogue 1
+    bool rows_kernel = false;               // decode class: register-dataflow kernel (rows_mma.cu), bn = rows per task (<= 64)
     // grouped (MoE): tasks[i] = {expert, first x row, rows (<= bn), first output row}; CTAs with blockIdx.y >= *num_tasks exit
     const int* tasks = nullptr;
     const int* num_tasks = nullptr;

@@ -4,12 +4,15 @@
 #include <cstdint>
 #include <cfloat>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "head.h"
 
 namespace vade {
 
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, long long ld, int n, int id0,
                                    float* __restrict__ best_val, long long* __restrict__ best_id) {
+    chain_release();
+    chain_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const long long row = blockIdx.x;
@@ -47,6 +50,8 @@ constexpr int kChunk = 4096;
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, int id0, uint2* __restrict__ cand, int n_chunks,
                      int rows, const PeerExchange px) {
+    chain_release();
+    chain_wait();
     __shared__ float sv[8];
     __shared__ int si[8];
     const long long row = blockIdx.y;
@@ -87,6 +92,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, int 
 __global__ void __launch_bounds__(32)
 argmax_join_kernel(const uint2* __restrict__ cand_in, int n_cand_per_rank, int ranks, const uint32_t* flags, int self,
                    long long half_stride, uint32_t* status, float* __restrict__ best_val, long long* __restrict__ best_id) {
+    chain_release();
+    chain_wait();
     const long long row = blockIdx.x;
     const int rows = gridDim.x;
     const uint2* cand = cand_in;
@@ -112,7 +119,7 @@ argmax_join_kernel(const uint2* __restrict__ cand_in, int n_cand_per_rank, int r
 void argmax_rows(const float* logits, long long ld, int rows, int n, int id0, float* best_val, long long* best_id,
                  void* cand, const HeadExchange* hx, uint32_t* status, cudaStream_t s) {
     if (cand == nullptr && hx == nullptr) {
-        argmax_rows_kernel<<<rows, 1024, 0, s>>>(logits, ld, n, id0, best_val, best_id);
+        launch_chained(argmax_rows_kernel, dim3(rows), dim3(1024), 0, s, logits, ld, n, id0, best_val, best_id);
         return;
     }
     const int n_chunks = (n + kChunk - 1) / kChunk;
@@ -121,12 +128,12 @@ void argmax_rows(const float* logits, long long ld, int rows, int n, int id0, fl
         for (int i = 0; i < hx->ranks; ++i) { px.out[i] = hx->out[i]; px.flags[i] = hx->flags[i]; }
         px.local = hx->local; px.half_stride = hx->half_stride; px.n = hx->ranks; px.self = hx->self; px.local_only_from = 0x7fffffff;
     }
-    argmax_chunks_kernel<<<dim3(n_chunks, rows), 256, 0, s>>>(logits, ld, n, id0, static_cast<uint2*>(cand), n_chunks, rows, px);
+    launch_chained(argmax_chunks_kernel, dim3(dim3(n_chunks, rows)), dim3(256), 0, s, logits, ld, n, id0, static_cast<uint2*>(cand), n_chunks, rows, px);
     if (hx != nullptr)
-        argmax_join_kernel<<<rows, 32, 0, s>>>(static_cast<const uint2*>(hx->out[hx->self]), n_chunks, hx->ranks, hx->flags[hx->self],
+        launch_chained(argmax_join_kernel, dim3(rows), dim3(32), 0, s, static_cast<const uint2*>(hx->out[hx->self]), n_chunks, hx->ranks, hx->flags[hx->self],
                                               hx->self, hx->half_stride, status, best_val, best_id);
     else
-        argmax_join_kernel<<<rows, 32, 0, s>>>(static_cast<const uint2*>(cand), n_chunks, 1, nullptr, 0, 0, status, best_val, best_id);
+        launch_chained(argmax_join_kernel, dim3(rows), dim3(32), 0, s, static_cast<const uint2*>(cand), n_chunks, 1, nullptr, 0, 0, status, best_val, best_id);
 }
 
 int argmax_chunk() { return kChunk; }

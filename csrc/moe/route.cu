@@ -22,6 +22,7 @@
 #include <cstdint>
 #include <cfloat>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "route.h"
 
 namespace vade {
@@ -85,6 +86,8 @@ __device__ __forceinline__ void warp_topk(const float* __restrict__ logits, long
 template <int PER>
 __global__ void route_topk_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E,
                                   int k, int renorm, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sg) {
+    chain_release();
+    chain_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -102,6 +105,8 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, long long pa
 // pos[p] = number of pairs p' < p with ids[p'] == ids[p]; counts[e] = pairs of expert e.
 __global__ void __launch_bounds__(256)
 route_positions_kernel(const int* __restrict__ ids, int P, int* __restrict__ pos, int* __restrict__ counts) {
+    chain_release();
+    chain_wait();
     __shared__ int wsum[8];
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -151,6 +156,8 @@ __device__ __forceinline__ void block_scan2(int& a, int& b, int* sa, int* sb) {
 __global__ void __launch_bounds__(1024, 1)
 scan_tasks_kernel(const int* __restrict__ counts, int E, int e0, int n_local, int ns, int T, int bn,
                   int* __restrict__ offsets, int4* __restrict__ tasks, int* __restrict__ meta, int max_tasks) {
+    chain_release();
+    chain_wait();
     __shared__ int sa[32], sb[32];
     const int ne = E + ns;
     int carry_rows = 0, carry_tasks = 0;
@@ -187,6 +194,8 @@ scan_tasks_kernel(const int* __restrict__ counts, int E, int e0, int n_local, in
 
 __global__ void scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const int* __restrict__ offsets,
                                     int T, int k, int ns, int E, int* __restrict__ row_token, int* __restrict__ slot_row) {
+    chain_release();
+    chain_wait();
     const int slots = k + ns;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * slots) return;
@@ -202,6 +211,8 @@ __global__ void __launch_bounds__(1024, 1)
 route_small_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k, int renorm,
                    int e0, int n_local, int ns, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sg,
                    int4* __restrict__ tasks_up, int4* __restrict__ tasks_down, int* __restrict__ meta, int* __restrict__ slot_row) {
+    chain_release();
+    chain_wait();
     extern __shared__ float lg[];              // [T][E + 1] logits with their K-range partials added
     __shared__ int present[1024];
     __shared__ int index_of[1024];
@@ -276,7 +287,7 @@ template <int PER>
 static void route_large(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm,
                         int* ids, float* wts, float* sg, cudaStream_t s) {
     const int wpb = 4;
-    route_topk_kernel<PER><<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>(logits, part_stride, n_parts, ld, T, E, k, renorm ? 1 : 0, ids, wts, sg);
+    launch_chained(route_topk_kernel<PER>, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), 0, s, logits, part_stride, n_parts, ld, T, E, k, renorm ? 1 : 0, ids, wts, sg);
 }
 
 const char* moe_route(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
@@ -286,10 +297,10 @@ const char* moe_route(const float* logits, long long part_stride, int n_parts, i
     if (E <= 128) route_large<4>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
     else if (E <= 512) route_large<16>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
     else route_large<32>(logits, part_stride, n_parts, ld, T, E, k, renorm, ids, wts, sg, s);
-    route_positions_kernel<<<E, 256, 0, s>>>(ids, T * k, pos, counts);
-    scan_tasks_kernel<<<1, 1024, 0, s>>>(counts, E, e0, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
+    launch_chained(route_positions_kernel, dim3(E), dim3(256), 0, s, ids, T * k, pos, counts);
+    launch_chained(scan_tasks_kernel, dim3(1), dim3(1024), 0, s, counts, E, e0, n_local, ns, T, bn, offsets, reinterpret_cast<int4*>(tasks), meta, max_tasks);
     const int total = T * (k + ns);
-    scatter_rows_kernel<<<(total + 255) / 256, 256, 0, s>>>(ids, pos, offsets, T, k, ns, E, row_token, slot_row);
+    launch_chained(scatter_rows_kernel, dim3((total + 255) / 256), dim3(256), 0, s, ids, pos, offsets, T, k, ns, E, row_token, slot_row);
     return cudaGetLastError() == cudaSuccess ? nullptr : "route launch failed";
 }
 
@@ -308,9 +319,9 @@ const char* moe_route_small(const float* logits, long long part_stride, int n_pa
         cudaFuncSetAttribute(route_small_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1025 * 4);
         configured = true;
     }
-    if (E <= 128) route_small_kernel<4><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
-    else if (E <= 512) route_small_kernel<16><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
-    else route_small_kernel<32><<<1, 1024, sm, s>>>(logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    if (E <= 128) launch_chained(route_small_kernel<4>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    else if (E <= 512) launch_chained(route_small_kernel<16>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    else launch_chained(route_small_kernel<32>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
     return cudaGetLastError() == cudaSuccess ? nullptr : "route_small launch failed";
 }
 

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 #include "../common/ptx.cuh"
+#include "../common/launch.h"
 #include "rows.h"
 
 namespace vade {
@@ -49,6 +50,8 @@ __device__ __forceinline__ long long exchange_base(const ExchangeIn& ex, long lo
 
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ tokens,
                              float* __restrict__ x, int H) {
+    chain_release();
+    chain_wait();
     const long long row = blockIdx.x;
     const __nv_bfloat16* src = table + tokens[row] * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) x[row * H + i] = __bfloat162float(src[i]);
@@ -61,6 +64,8 @@ __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162flo
 template <typename TIn>
 __global__ void rmsnorm_kernel(const TIn* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ h,
                                int H, float eps, int ldh, int h_off) {
+    chain_release();
+    chain_wait();
     __shared__ float red[32];
     const long long row = blockIdx.x;
     float ss = 0.f;
@@ -77,6 +82,8 @@ template <int NP>
 __global__ void __launch_bounds__(kRowThreads)
 fold_add_norm_kernel(const float* __restrict__ parts_in, long long part_stride, float* __restrict__ x,
                      const float* __restrict__ w, __nv_bfloat16* __restrict__ h, int H, float eps, const ExchangeIn ex) {
+    chain_release();
+    chain_wait();
     __shared__ float red[32];
     __shared__ long long ex_slot;
     const float* parts = parts_in + exchange_base(ex, &ex_slot);
@@ -128,6 +135,8 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y_in, const int* __res
                         const int* __restrict__ ids, const float* __restrict__ wts, const float* __restrict__ sg,
                         int k, int ns, float* __restrict__ x, const float* __restrict__ w,
                         __nv_bfloat16* __restrict__ h, int H, float eps, const ExchangeIn ex) {
+    chain_release();
+    chain_wait();
     __shared__ float red[32];
     __shared__ long long ex_slot;
     __shared__ float ow[kMaxSlots];
@@ -206,6 +215,8 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y_in, const int* __res
 // rows of xs = rows of x picked by row_token (the MoE dispatch gather into expert-sorted order)
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
                                    const int* __restrict__ meta, __nv_bfloat16* __restrict__ xs, int H) {
+    chain_release();
+    chain_wait();
     // meta: [1] rows of the layout, [4]..[5] rows of this rank's routed experts, [6] first shared row
     const int r = blockIdx.x;
     if (r >= meta[1] || !((r >= meta[4] && r < meta[5]) || r >= meta[6])) return;
@@ -218,6 +229,8 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
 // K-range partials of interleaved gate/up rows (column 2f = gate, 2f + 1 = up).
 __global__ void swiglu_fold_kernel(const float* __restrict__ parts, long long part_stride, int n_parts,
                                    const int* __restrict__ n_rows, __nv_bfloat16* __restrict__ mid, int I) {
+    chain_release();
+    chain_wait();
     const int r = blockIdx.x;
     if (r >= *n_rows) return;
     for (int f = threadIdx.x; f < I; f += blockDim.x) {
@@ -235,17 +248,17 @@ __global__ void swiglu_fold_kernel(const float* __restrict__ parts, long long pa
 }
 
 void swiglu_fold(const float* parts, long long part_stride, int n_parts, const int* n_rows, void* mid, int max_rows, int I, cudaStream_t s) {
-    swiglu_fold_kernel<<<max_rows, 256, 0, s>>>(parts, part_stride, n_parts, n_rows, static_cast<__nv_bfloat16*>(mid), I);
+    launch_chained(swiglu_fold_kernel, dim3(max_rows), dim3(256), 0, s, parts, part_stride, n_parts, n_rows, static_cast<__nv_bfloat16*>(mid), I);
 }
 
 void embed(const void* table, const long long* tokens, float* x, int rows, int H, cudaStream_t s) {
-    embed_kernel<<<rows, kRowThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(table), tokens, x, H);
+    launch_chained(embed_kernel, dim3(rows), dim3(kRowThreads), 0, s, static_cast<const __nv_bfloat16*>(table), tokens, x, H);
 }
 void rmsnorm(const void* x, bool x_is_bf16, const float* w, void* h, int rows, int H, float eps, int ldh, int h_off, cudaStream_t s) {
     if (x_is_bf16)
-        rmsnorm_kernel<__nv_bfloat16><<<rows, kRowThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
+        launch_chained(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(kRowThreads), 0, s, static_cast<const __nv_bfloat16*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
     else
-        rmsnorm_kernel<float><<<rows, kRowThreads, 0, s>>>(static_cast<const float*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
+        launch_chained(rmsnorm_kernel<float>, dim3(rows), dim3(kRowThreads), 0, s, static_cast<const float*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
 }
 static ExchangeIn make_ex(const ExchangeWait* e) {
     ExchangeIn ex{nullptr, nullptr, 0, 0, 0};
@@ -258,20 +271,20 @@ void fold_add_norm(const float* parts, long long part_stride, int n_parts, float
     __nv_bfloat16* hb = static_cast<__nv_bfloat16*>(h);
     const ExchangeIn ex = make_ex(wait);
     switch (n_parts) {
-        case 1: fold_add_norm_kernel<1><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
-        case 2: fold_add_norm_kernel<2><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
-        case 4: fold_add_norm_kernel<4><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
-        default: fold_add_norm_kernel<8><<<rows, kRowThreads, 0, s>>>(parts, part_stride, x, w, hb, H, eps, ex); break;
+        case 1: launch_chained(fold_add_norm_kernel<1>, dim3(rows), dim3(kRowThreads), 0, s, parts, part_stride, x, w, hb, H, eps, ex); break;
+        case 2: launch_chained(fold_add_norm_kernel<2>, dim3(rows), dim3(kRowThreads), 0, s, parts, part_stride, x, w, hb, H, eps, ex); break;
+        case 4: launch_chained(fold_add_norm_kernel<4>, dim3(rows), dim3(kRowThreads), 0, s, parts, part_stride, x, w, hb, H, eps, ex); break;
+        default: launch_chained(fold_add_norm_kernel<8>, dim3(rows), dim3(kRowThreads), 0, s, parts, part_stride, x, w, hb, H, eps, ex); break;
     }
 }
 void combine_add_norm(const void* y, const int* slot_row, const int* ids, const float* wts, const float* sg, int k, int ns,
                       float* x, const float* w, void* h, int rows, int H, float eps, const ExchangeWait* wait, cudaStream_t s) {
     const int threads = ((H / 8 + 31) / 32) * 32;          // one 8-column piece per thread, H <= 8192
-    combine_add_norm_kernel<<<rows, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(y), slot_row, ids, wts, sg, k, ns, x, w,
+    launch_chained(combine_add_norm_kernel, dim3(rows), dim3(threads), 0, s, static_cast<const __nv_bfloat16*>(y), slot_row, ids, wts, sg, k, ns, x, w,
                                                         static_cast<__nv_bfloat16*>(h), H, eps, make_ex(wait));
 }
 void gather_rows(const void* x, const int* row_token, const int* meta, void* xs, int max_rows, int H, cudaStream_t s) {
-    gather_rows_kernel<<<max_rows, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), row_token, meta, static_cast<__nv_bfloat16*>(xs), H);
+    launch_chained(gather_rows_kernel, dim3(max_rows), dim3(128), 0, s, static_cast<const __nv_bfloat16*>(x), row_token, meta, static_cast<__nv_bfloat16*>(xs), H);
 }
 
 }  // namespace vade

@@ -101,6 +101,39 @@ def test_gemm_rows_do_not_depend_on_batch():
         assert torch.equal(part, full[:t]), f"rows change with batch width {t}"
 
 
+@pytest.mark.parametrize("T", [1, 3, 8, 9, 16, 30, 64, 70, 150])
+def test_decode_class_gemm_matches_reference(T):
+    """The register-dataflow kernel of the decode class: partial sums per K range, fp32 and bf16 outputs."""
+    ops = _ops()
+    q = _nvfp4(400, 1024, seed=7)                      # 400 rows: the last tile block is ragged
+    x = _x(T, 1024, seed=2)
+    ref = R.dot_rows(x.float(), q.dense()) * q.row_scale
+    parts = ops.linear(x, q, phase="decode")           # [4, T, n] fp32 partials
+    ops.check_status()
+    assert parts.shape == (ops.DECODE_PARTS, T, 400)
+    _close(parts.sum(0), ref, rtol=1e-3, atol=1e-4)
+    pr = R.linear_ranges(x.float(), q.dense(), 8) * q.row_scale
+    _close(ops.linear_ranges(x, q, 8, phase="decode"), pr, rtol=1e-3, atol=1e-4)
+    _close(ops.linear(x, q, out_fp32=True, phase="decode"), ref, rtol=1e-3, atol=1e-4)
+    q2 = _nvfp4(256, 192, seed=9)                      # K not divisible into decode parts: single bf16 pass
+    x2 = _x(T, 192, seed=4)
+    _close(ops.linear(x2, q2, phase="decode"), R.dot_rows(x2.float(), q2.dense()) * q2.row_scale)
+    ops.check_status()
+
+
+def test_decode_class_rows_do_not_depend_on_batch():
+    ops = _ops()
+    q = _nvfp4(256, 1024, seed=5)
+    x = _x(150, 1024)
+    full = ops.linear(x, q, phase="decode")
+    for t in (1, 5, 8, 9, 16, 17, 40, 64, 65, 130):
+        part = ops.linear(x[:t].contiguous(), q, phase="decode")
+        assert torch.equal(part, full[:, :t]), f"decode-class rows change with batch width {t}"
+    for first in (1, 7, 63):                           # a row's bits do not depend on its slot either
+        part = ops.linear(x[first:first + 3].contiguous(), q, phase="decode")
+        assert torch.equal(part, full[:, first:first + 3]), f"decode-class rows change with their slot ({first})"
+
+
 def test_rmsnorm_embed_argmax():
     ops = _ops()
     x = torch.randn(9, 1024, device=DEV)

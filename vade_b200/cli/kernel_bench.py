@@ -88,7 +88,116 @@ def case_gemm(ops, name, n, k, T, ranges=1, plain=False):
     return name, fn, ok, nbytes, 2.0 * n * k * T
 
 
+def _layer_weights(ops, attention: bool):
+    """One layer's weights of the 80B shape (random, generated on the device) and a cache for it."""
+    from ..parallel.plan import make_plan
+    from ..runtime.cache import Cache
+    cfg = ops.cfg
+    small = type(cfg)(**{**{k: getattr(cfg, k) for k in cfg.__dataclass_fields__ if k != "quant"},
+                         "num_hidden_layers": 4, "mtp_num_hidden_layers": 0})
+    small.quant = cfg.quant
+    plan = make_plan(small)
+    mw = W.synth_device_weights(small, plan, ops.device, seed=3, with_mtp=False)
+    return small, plan, mw, (mw.layers[3] if attention else mw.layers[0])
+
+
+def case_gdn_prefill(ops, rows=2048):
+    from ..ops.api import Batch, RefOps
+    from ..runtime.cache import Cache
+    small, plan, mw, lw = _layer_weights(ops, False)
+    dev = ops.device
+    proj = (torch.randn(rows, lw.in_proj.n, device=dev) * 0.5).to(torch.bfloat16)
+    c1 = Cache(small, plan, 2, 64, 4096, torch.bfloat16, dev, mtp=False)
+    c2 = Cache(small, plan, 2, 64, 4096, torch.bfloat16, dev, mtp=False)
+    mk = lambda n: Batch.make([(0, 0, [0] * n)], dev, "prefill")
+    got = ops.gdn_mix(lw, proj[:96].contiguous(), mk(96), c1, 0)
+    ref = RefOps(small, torch.bfloat16).gdn_mix(lw, proj[:96].contiguous(), mk(96), c2, 0)
+    ok = torch.allclose(got.float(), ref.float(), rtol=3e-2, atol=1e-2)
+    batch = mk(rows)
+    fn = lambda: ops.gdn_mix(lw, proj, batch, c1, 0)
+    vh, kh = small.linear_num_value_heads, small.linear_num_key_heads
+    nbytes = rows * lw.in_proj.n * 2 + rows * vh * 128 * 2 + 2 * vh * 128 * 128 * 4
+    flops = 4.0 * rows * vh * 128 * 128
+    return f"GDN prompt tile, {rows} rows, {vh} value heads (fp32 SIMT recurrence)", fn, ok, nbytes, flops
+
+
+def case_attn_prefill(ops, rows=2048, pos0=6144):
+    from ..ops.api import Batch, RefOps
+    from ..runtime.cache import Cache
+    small, plan, mw, lw = _layer_weights(ops, True)
+    dev = ops.device
+    pages = (pos0 + rows) // 64 + 2
+    c1 = Cache(small, plan, 1, pages, pos0 + rows + 64, torch.bfloat16, dev, mtp=False)
+    c2 = Cache(small, plan, 1, pages, pos0 + rows + 64, torch.bfloat16, dev, mtp=False)
+    for c in (c1, c2):
+        c.ensure(0, pos0 + rows)
+    # gate on a short case against the PyTorch statement
+    qs = torch.randn(200, lw.qkv.n, device=dev).to(torch.bfloat16)
+    got = ops.attn_mix(lw, qs, Batch.make([(0, 0, [0] * 200)], dev, "prefill"), c1, 3)
+    ref = RefOps(small, torch.bfloat16).attn_mix(lw, qs, Batch.make([(0, 0, [0] * 200)], dev, "prefill"), c2, 3)
+    ok = torch.allclose(got.float(), ref.float(), rtol=3e-2, atol=1e-2)
+    c1.k_pages[3].normal_()
+    c1.v_pages[3].normal_()
+    qkv = torch.randn(rows, lw.qkv.n, device=dev).to(torch.bfloat16)
+    batch = Batch.make([(0, pos0, [0] * rows)], dev, "prefill")
+    fn = lambda: ops.attn_mix(lw, qkv, batch, c1, 3)
+    nq, nkv, hd = small.num_attention_heads, small.num_key_value_heads, small.head_dim
+    keys = sum(min(pos0 + r + 1, pos0 + rows) for r in range(0, rows, 128)) * 128 // 1      # visible (row, key) pairs, tile granular
+    flops = 4.0 * nq * hd * sum(pos0 + r + 1 for r in range(rows))
+    nbytes = rows * lw.qkv.n * 2 + rows * nq * hd * 2 + 2 * (pos0 + rows) * nkv * hd * 2
+    return f"gated attention prompt tile, {rows} rows at position {pos0}, {nq} heads x {hd} (tcgen05)", fn, ok, nbytes, flops
+
+
+def case_attn_decode(ops, ctx=8192):
+    from ..ops.api import Batch, RefOps
+    from ..runtime.cache import Cache
+    small, plan, mw, lw = _layer_weights(ops, True)
+    dev = ops.device
+    c1 = Cache(small, plan, 1, ctx // 64 + 2, ctx + 64, torch.bfloat16, dev, mtp=False)
+    c2 = Cache(small, plan, 1, ctx // 64 + 2, ctx + 64, torch.bfloat16, dev, mtp=False)
+    for c in (c1, c2):
+        c.ensure(0, ctx + 1)
+    c1.k_pages[3].normal_()
+    c1.v_pages[3].normal_()
+    c2.k_pages[3].copy_(c1.k_pages[3])
+    c2.v_pages[3].copy_(c1.v_pages[3])
+    qkv = torch.randn(4, 1, lw.qkv.n, device=dev) * 0.5
+    mk = lambda: Batch.make([(0, ctx, [0])], dev, "decode")
+    got = ops.attn_mix(lw, qkv, mk(), c1, 3)
+    ref = RefOps(small, torch.bfloat16).attn_mix(lw, qkv.sum(0).to(torch.bfloat16), mk(), c2, 3)
+    ok = torch.allclose(got.float(), ref.float(), rtol=3e-2, atol=1e-2)
+    batch = mk()
+    fn = lambda: ops.attn_mix(lw, qkv, batch, c1, 3)
+    nq, nkv, hd = small.num_attention_heads, small.num_key_value_heads, small.head_dim
+    return (f"gated attention decode row at context {ctx} (128-key splits + merge)", fn, ok,
+            2 * ctx * nkv * hd * 2, 4.0 * nq * hd * ctx)
+
+
+def case_moe(ops, rows, phase):
+    small, plan, mw, lw = _layer_weights(ops, False)
+    from ..ops.api import RefOps
+    dev = ops.device
+    h = torch.randn(rows, small.hidden_size, device=dev).to(torch.bfloat16)
+    x0 = torch.zeros(rows, small.hidden_size, device=dev)
+
+    def fn():
+        r = ops.route(h, lw.moe, phase)
+        y, _ = ops.moe_experts(lw.moe, h, r, phase)
+        return ops.combine_add_norm(y, r, x0.clone(), None)[0]
+    got = fn()
+    ok = bool(torch.isfinite(got).all())
+    k, I, H = small.num_experts_per_tok + 1, small.moe_intermediate_size, small.hidden_size
+    touched = min(small.num_experts, rows * small.num_experts_per_tok) + 1
+    nbytes = touched * 3 * I * H * 0.5625 + rows * k * H * 2 * 3
+    return f"MoE block ({phase} class), {rows} rows: router, routing, grouped gate/up + down, combine", fn, ok, nbytes, 6.0 * rows * k * I * H
+
+
 CASES = {
+    "gdn_prefill_2048": lambda ops: case_gdn_prefill(ops),
+    "attn_prefill_2048_at_6144": lambda ops: case_attn_prefill(ops),
+    "attn_decode_8192": lambda ops: case_attn_decode(ops),
+    "moe_prefill_2048": lambda ops: case_moe(ops, 2048, "prefill"),
+    "moe_decode_1": lambda ops: case_moe(ops, 1, "decode"),
     "gemm_gdn_in_proj_decode": lambda ops: case_gemm(ops, "NVFP4 12352x2048, 1 row", 12352, 2048, 1),
     "gemm_qkv_decode": lambda ops: case_gemm(ops, "NVFP4 9216x2048, 1 row", 9216, 2048, 1),
     "gemm_out_proj_decode": lambda ops: case_gemm(ops, "NVFP4 2048x4096, 8 ranges, 1 row", 2048, 4096, 1, ranges=8),

@@ -55,17 +55,19 @@ class CudaOps:
         return batch.dev
 
     def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0,
-              ex=None, ex_offset: int = 0, local_only_from: int = -1):
-        """ex: parallel.symm.Exchange -> the epilogue stores into every rank's buffer (+ ex_offset bytes)."""
+              ex=None, ex_offset: int = 0, local_only_from: int = -1, rows: bool = False):
+        """ex: parallel.symm.Exchange -> the epilogue stores into every rank's buffer (+ ex_offset bytes).
+        rows: decode class -> the register-dataflow kernel (NVFP4 weights, epilogue 0/1, <= 64 rows per task)."""
         nv = q.kind == "nvfp4"
+        rows = bool(rows and nv and epilogue != 2 and (tasks is None or bn <= 64))
         self.launches += 1
         if ex is None:
             self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1)
+                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1, rows)
         else:
             self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
                           range_stride, tasks, meta, max_tasks, self.status, [p + ex_offset for p in ex.out], ex.flags,
-                          ex.local, ex.half_stride, ex.self_rank, local_only_from)
+                          ex.local, ex.half_stride, ex.self_rank, local_only_from, rows)
 
     # ---- basic
     def embed(self, w, tokens):
@@ -90,17 +92,17 @@ class CudaOps:
     def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
         T = h.shape[0]
         if phase == "decode" and not out_fp32 and q.k % (self.DECODE_PARTS * 64) == 0:
-            return self.linear_parts(h, q, self.DECODE_PARTS)
+            return self.linear_parts(h, q, self.DECODE_PARTS, rows=True)
         out = torch.empty(T, q.n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=self.device)
-        self._gemm(h, q, out, 1 if out_fp32 else 0, _bn_for(T), 1, T, q.n, 0)
+        self._gemm(h, q, out, 1 if out_fp32 else 0, _bn_for(T), 1, T, q.n, 0, rows=phase == "decode")
         return out
 
-    def linear_parts(self, h, q, ranges: int):
+    def linear_parts(self, h, q, ranges: int, rows: bool = False):
         """fp32 K-range partials [ranges, T, n] of a matrix whose consumer adds them itself (decode
         class: more CTAs in flight for a one-row pass)."""
         T = h.shape[0]
         out = torch.empty(ranges, T, q.n, dtype=torch.float32, device=self.device)
-        self._gemm(h, q, out, 1, _bn_for(T), ranges, T, q.n, T * q.n)
+        self._gemm(h, q, out, 1, _bn_for(T), ranges, T, q.n, T * q.n, rows=rows)
         return out
 
     def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
@@ -112,10 +114,11 @@ class CudaOps:
             if 8 * T * q.n > ex.half_stride:
                 raise ValueError("pass has more rows than the symmetric partial buffer was sized for")
             first = ex.self_rank * n_ranges                       # first global range this rank owns
-            self._gemm(h, q, ex.buffer, 1, _bn_for(T), n_ranges, T, q.n, T * q.n, ex=ex, ex_offset=first * T * q.n * 4)
+            self._gemm(h, q, ex.buffer, 1, _bn_for(T), n_ranges, T, q.n, T * q.n, ex=ex, ex_offset=first * T * q.n * 4,
+                       rows=phase == "decode")
             return SimpleNamespace(ex=ex, T=T, n=q.n)
         out = torch.empty(n_ranges, T, q.n, dtype=torch.float32, device=self.device)
-        self._gemm(h, q, out, 1, _bn_for(T), n_ranges, T, q.n, T * q.n)
+        self._gemm(h, q, out, 1, _bn_for(T), n_ranges, T, q.n, T * q.n, rows=phase == "decode")
         return out
 
     def fold_add_norm(self, parts, x, w):
@@ -244,7 +247,7 @@ class CudaOps:
         P = self.DECODE_PARTS
         if phase == "decode" and mw.gate_up.k % (P * 64) == 0:
             gu = torch.empty(P, r.max_rows, I2, dtype=torch.float32, device=self.device)
-            self._gemm(xs, mw.gate_up, gu, 1, r.bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks)
+            self._gemm(xs, mw.gate_up, gu, 1, r.bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks, rows=True)
             self.launches += 1
             self.ext.swiglu_fold(gu, r.meta, mid)
         else:
@@ -254,11 +257,11 @@ class CudaOps:
             if r.max_rows * H > ex.half_stride:
                 raise ValueError("pass has more (token, expert) rows than the symmetric pair buffer was sized for")
             self._gemm(mid, mw.down, ex.buffer, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks,
-                       ex=ex, local_only_from=mw.n_local)
+                       ex=ex, local_only_from=mw.n_local, rows=phase == "decode")
             r.ex = ex
             return ex.buffer, None
         y = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
-        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks)
+        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks, rows=phase == "decode")
         r.ex = None
         return y, (None if self.tp == 1 else r)
 
