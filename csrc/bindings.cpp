@@ -33,7 +33,8 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
           int64_t epilogue, int64_t bn, int64_t ranges, int64_t tokens, int64_t ldo, int64_t out_range_stride,
           c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
           c10::optional<torch::Tensor> status, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
-          int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from, bool rows_kernel) {
+          int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from, bool rows_kernel,
+          c10::optional<torch::Tensor> x_parts) {
     need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows on the GPU");
     need(w.is_cuda() && w.is_contiguous() && row_scale.is_cuda() && row_scale.scalar_type() == torch::kFloat32, "bad weights");
     need(out.is_cuda(), "bad output");
@@ -44,6 +45,11 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
     a.out = out.data_ptr(); a.ldo = static_cast<int>(ldo); a.out_range_stride = out_range_stride; a.epilogue = static_cast<int>(epilogue);
     a.tokens = static_cast<int>(tokens); a.bn = static_cast<int>(bn); a.ranges = static_cast<int>(ranges);
     a.rows_kernel = rows_kernel;
+    if (x_parts.has_value()) {
+        need(x_parts->is_cuda() && x_parts->scalar_type() == torch::kFloat32 && x_parts->is_contiguous() && x_parts->dim() == 3 &&
+             x_parts->size(2) == 2 * k, "x_parts must be fp32 [parts, rows, 2k]");
+        a.x_parts = x_parts->data_ptr<float>(); a.x_part_stride = x_parts->stride(0); a.x_n_parts = static_cast<int>(x_parts->size(0));
+    }
     if (tasks.has_value()) {
         need(meta.has_value(), "grouped GEMM needs the task count");
         a.tasks = tasks->data_ptr<int>(); a.num_tasks = meta->data_ptr<int>(); a.max_tasks = static_cast<int>(max_tasks);
@@ -145,6 +151,28 @@ void moe_route_small(torch::Tensor logits, int64_t n_parts, int64_t E, int64_t k
                                 static_cast<int>(ns), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
                                 tasks_up.data_ptr<int>(), tasks_down.data_ptr<int>(), meta.data_ptr<int>(), slot_row.data_ptr<int>(),
                                 stream_of(logits)));
+}
+
+// Decode-class router (logits as 8 K-range partials) with, optionally, the small-pass routing fused in.
+void router_rows(torch::Tensor w, torch::Tensor x, torch::Tensor logits, c10::optional<torch::Tensor> ticket, int64_t E, int64_t k,
+                 bool renorm, int64_t e0, int64_t n_local, int64_t ns, c10::optional<torch::Tensor> ids, c10::optional<torch::Tensor> wts,
+                 c10::optional<torch::Tensor> sg, c10::optional<torch::Tensor> tasks_up, c10::optional<torch::Tensor> tasks_down,
+                 c10::optional<torch::Tensor> meta, c10::optional<torch::Tensor> slot_row) {
+    need(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 2, "router rows must be bf16");
+    need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) == w.size(1), "router input");
+    need(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous() && logits.dim() == 3 && logits.size(0) == 8 &&
+         logits.size(1) == x.size(0) && logits.size(2) >= w.size(0), "router logits must be fp32 [8, T, ld]");
+    if (ticket.has_value())
+        need(ids.has_value() && wts.has_value() && sg.has_value() && tasks_up.has_value() && tasks_down.has_value() && meta.has_value() &&
+             slot_row.has_value() && ticket->scalar_type() == torch::kInt32, "fused routing outputs");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t T = x.size(0), ld = logits.size(2);
+    check(vade::router_rows(w.data_ptr(), static_cast<int>(w.size(0)), static_cast<int>(w.size(1)), x.data_ptr(),
+                            static_cast<int>(x.stride(0)), static_cast<int>(T), logits.data_ptr<float>(), T * ld, static_cast<int>(ld),
+                            ticket.has_value() ? reinterpret_cast<unsigned int*>(ticket->data_ptr<int>()) : nullptr, static_cast<int>(E),
+                            static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local), static_cast<int>(ns),
+                            ptr<int>(ids), ptr<float>(wts), ptr<float>(sg), ptr<int>(tasks_up), ptr<int>(tasks_down), ptr<int>(meta),
+                            ptr<int>(slot_row), stream_of(x)));
 }
 
 void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
@@ -299,6 +327,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("swiglu_fold", &swiglu_fold);
     m.def("moe_route", &moe_route);
     m.def("moe_route_small", &moe_route_small);
+    m.def("router_rows", &router_rows);
     m.def("gdn_scan", &gdn_scan);
     m.def("gdn_prefill", &gdn_prefill);
     m.def("attn_prep", &attn_prep);

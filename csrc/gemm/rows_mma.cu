@@ -66,9 +66,10 @@ __device__ __forceinline__ uint32_t ldg_stream(const uint8_t* p) {
     return v;
 }
 
-template <int NT, int EPI>
-__global__ void __launch_bounds__(kRowsThreads)
-rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx) {
+template <int NT, int EPI, bool XP>
+__global__ void __launch_bounds__(kRowsThreads, NT > 2 ? 3 : XP ? 4 : 6)
+rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ xparts,
+                long long xpart_stride, int x_nparts) {
     chain_release();
     extern __shared__ __align__(16) uint8_t xs[];          // [NT * 8 token rows][kXStride]
     const int warp = threadIdx.x >> 5;
@@ -128,8 +129,30 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx) {
                 const int j = p / pieces;
                 const int q = p - j * pieces;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (j < nrows)
-                    v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row0 + j) * ldx + (kb0 + c0) * kTileK + q * 8);
+                if (j < nrows) {
+                    const int col = (kb0 + c0) * kTileK + q * 8;
+                    if (!XP) {
+                        v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row0 + j) * ldx + col);
+                    } else {
+                        // token operand = SwiGLU of the previous product's fp32 K-range partials (interleaved gate/up
+                        // columns): ascending sums, bf16 roundings of gate and up, bf16(silu(gate) * up)
+                        const float4* src = reinterpret_cast<const float4*>(xparts + (static_cast<long long>(row0 + j) * a.kb_total * kTileK + col) * 2);
+                        uint32_t o[4];
+#pragma unroll 1
+                        for (int u = 0; u < 4; ++u) {                  // one float4 = gate, up, gate, up of two columns
+                            float4 sum = __ldcg(src + u);
+                            for (int pp = 1; pp < x_nparts; ++pp) {
+                                const float4 nx = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + pp * xpart_stride) + u);
+                                sum.x += nx.x; sum.y += nx.y; sum.z += nx.z; sum.w += nx.w;
+                            }
+                            const float m0 = siluf_(bf16_round(sum.x)) * bf16_round(sum.y);
+                            const float m1 = siluf_(bf16_round(sum.z)) * bf16_round(sum.w);
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(m0, m1);
+                            o[u] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        v = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
                 *reinterpret_cast<uint4*>(xs + j * kXStride + q * 16) = v;
             }
             __syncthreads();
@@ -201,17 +224,18 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx) {
     }
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, bool XP>
 static const char* launch_rows(const GemmArgs& h, const GemmDev& d, dim3 grid, cudaStream_t stream) {
     constexpr int smem = NT * 8 * kXStride;
     static bool configured = false;
-    auto kern = rows_mma_kernel<NT, EPI>;
+    auto kern = rows_mma_kernel<NT, EPI, XP>;
     if (!configured) {
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return "cannot raise shared memory limit";
         configured = true;
     }
-    launch_chained(kern, grid, dim3(kRowsThreads), smem, stream, d, static_cast<const __nv_bfloat16*>(h.x), h.ldx);
+    launch_chained(kern, grid, dim3(kRowsThreads), smem, stream, d, static_cast<const __nv_bfloat16*>(h.x), h.ldx, h.x_parts,
+                   h.x_part_stride, h.x_n_parts);
     return cudaGetLastError() == cudaSuccess ? nullptr : "kernel launch failed";
 }
 
@@ -223,7 +247,11 @@ const char* rows_mma_gemm(const GemmArgs& h, const GemmDev& d, cudaStream_t stre
     const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + nt * 8 - 1) / (nt * 8);
     if (y <= 0) return "empty grid";
     const dim3 grid(2 * m_tiles, y, h.ranges);
-#define VADE_ROWS(NT_) return h.epilogue == 0 ? launch_rows<NT_, 0>(h, d, grid, stream) : launch_rows<NT_, 1>(h, d, grid, stream)
+#define VADE_ROWS(NT_)                                                                                               \
+    return h.x_parts != nullptr ? (h.epilogue == 0 ? launch_rows<NT_, 0, true>(h, d, grid, stream)                   \
+                                                   : launch_rows<NT_, 1, true>(h, d, grid, stream))                  \
+                                : (h.epilogue == 0 ? launch_rows<NT_, 0, false>(h, d, grid, stream)                  \
+                                                   : launch_rows<NT_, 1, false>(h, d, grid, stream))
     switch (nt) {
         case 1: VADE_ROWS(1);
         case 2: VADE_ROWS(2);

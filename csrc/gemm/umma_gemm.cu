@@ -356,7 +356,10 @@ const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
     if (h.k % kTileK != 0 || h.k <= 0) return "K must be a positive multiple of 64";
     if (h.ranges < 1 || (h.k / kTileK) % h.ranges != 0) return "K blocks must divide evenly into ranges";
     if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
-    if ((reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
+    if (h.x_parts != nullptr && !h.rows_kernel) return "a token operand from partials needs the decode-class kernel";
+    if (h.x_parts == nullptr && (reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
+    if (h.x_parts != nullptr && ((reinterpret_cast<uintptr_t>(h.x_parts) & 15) != 0 || h.x_part_stride % 4 != 0 || h.x_n_parts < 1))
+        return "partials of the token operand must be 16-byte aligned";
     if (h.x_rows <= 0 || h.n_out <= 0) return "empty problem";
     if (h.nvfp4 && (reinterpret_cast<uintptr_t>(h.w) & 15) != 0) return "weight tiles must be 16-byte aligned";
     GemmDev d;

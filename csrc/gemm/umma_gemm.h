@@ -25,6 +25,11 @@ struct GemmArgs {
     int tokens = 0;                         // dense: number of token rows
     int bn = 16;                            // token tile (16, 32, 64, 128, 256)
     int ranges = 1;                         // K ranges (grid.z); > 1 requires epilogue 1
+    // rows_kernel only: the token operand is SwiGLU of fp32 K-range partials [x_n_parts][rows][2 * k] (interleaved
+    // gate/up columns) instead of bf16 rows x
+    const float* x_parts = nullptr;
+    long long x_part_stride = 0;
+    int x_n_parts = 0;
     bool rows_kernel = false;               // decode class: register-dataflow kernel (rows_mma.cu), bn = rows per task (<= 64)
     // grouped (MoE): tasks[i] = {expert, first x row, rows (<= bn), first output row}; CTAs with blockIdx.y >= *num_tasks exit
     const int* tasks = nullptr;

@@ -205,7 +205,99 @@ __global__ void scatter_rows_kernel(const int* __restrict__ ids, const int* __re
     row_token[row] = t;
 }
 
-// T <= 16 rows, n_local <= 1024 experts, one CTA of 1024 threads.
+// Routing of a small pass (T <= 16 rows, E <= 1024 experts) by ONE CTA of any width (a multiple of 32
+// threads with E <= 4 * blockDim.x).  lg: shared memory for [T][E + 1] floats.
+template <int PER>
+__device__ void route_small_body(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k,
+                                 int renorm, int e0, int n_local, int ns, int* __restrict__ ids, float* __restrict__ wts,
+                                 float* __restrict__ sg, int4* __restrict__ tasks_up, int4* __restrict__ tasks_down,
+                                 int* __restrict__ meta, int* __restrict__ slot_row, float* lg) {
+    __shared__ unsigned char present[1024];
+    __shared__ short index_of[1024];
+    __shared__ int sa[32], sb[32];
+    __shared__ int sel[16 * 32];
+    const int nthr = blockDim.x, nwarps = nthr >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 1024; i += nthr) present[i] = 0;
+    // all partial loads of an element are issued together, then added in ascending part order
+    for (int i = threadIdx.x; i < T * (E + 1); i += nthr) {
+        const int t = i / (E + 1), e = i % (E + 1);
+        const float* src = logits + static_cast<long long>(t) * ld + e;
+        float a;
+        if (n_parts == 8) {
+            float p[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) p[u] = __ldcg(src + u * part_stride);
+            a = p[0];
+#pragma unroll
+            for (int u = 1; u < 8; ++u) a += p[u];
+        } else {
+            a = __ldcg(src);
+            for (int u = 1; u < n_parts; ++u) a += __ldcg(src + u * part_stride);
+        }
+        lg[i] = a;
+    }
+    __syncthreads();
+    for (int row = warp; row < T; row += nwarps) {
+        float w, gl;
+        int e;
+        warp_topk<PER>(lg + row * (E + 1), 0, 1, E, k, renorm, lane, w, e, gl);
+        if (lane < k) {
+            ids[row * k + lane] = e;
+            wts[row * k + lane] = w;
+            sel[row * 32 + lane] = e;
+            present[e] = 1;
+        }
+        if (lane == 0) sg[row] = sigmoidf_(gl);
+    }
+    __syncthreads();
+    // global block index of every active expert (ascending id); this rank's tasks are the active experts it holds.
+    // Thread i owns the experts [i * ept, (i + 1) * ept).
+    const int ept = (E + nthr - 1) / nthr;
+    const int first = threadIdx.x * ept;
+    int cnt = 0, cnt_local = 0;
+    for (int j = 0; j < ept; ++j) {
+        const int e = first + j;
+        if (e < E && present[e]) {
+            ++cnt;
+            if (e >= e0 && e < e0 + n_local) ++cnt_local;
+        }
+    }
+    int inc = cnt, inc_local = cnt_local;
+    block_scan2(inc, inc_local, sa, sb);
+    const int n_active = sa[nwarps - 1], n_active_local = sb[nwarps - 1];
+    int idx = inc - cnt, li = inc_local - cnt_local;
+    for (int j = 0; j < ept; ++j) {
+        const int e = first + j;
+        if (e < E && present[e]) {
+            index_of[e] = static_cast<short>(idx);
+            if (e >= e0 && e < e0 + n_local) {
+                tasks_up[li] = make_int4(e - e0, 0, T, idx * 16);
+                tasks_down[li] = make_int4(e - e0, idx * 16, T, idx * 16);
+                ++li;
+            }
+            ++idx;
+        }
+    }
+    for (int i = threadIdx.x; i < ns; i += nthr) {
+        const int lt = n_active_local + i, blk = n_active + i;
+        tasks_up[lt] = make_int4(n_local + i, 0, T, blk * 16);
+        tasks_down[lt] = make_int4(n_local + i, blk * 16, T, blk * 16);
+    }
+    if (threadIdx.x < 8) {
+        int v = 0;
+        if (threadIdx.x == 0 || threadIdx.x == 2) v = n_active_local + ns;
+        if (threadIdx.x == 1) v = (n_active + ns) * 16;
+        meta[threadIdx.x] = v;
+    }
+    __syncthreads();
+    const int slots = k + ns;
+    for (int i = threadIdx.x; i < T * slots; i += nthr) {
+        const int t = i / slots, j = i % slots;
+        slot_row[i] = (j < k ? index_of[sel[t * 32 + j]] : n_active + (j - k)) * 16 + t;
+    }
+}
+
 template <int PER>
 __global__ void __launch_bounds__(1024, 1)
 route_small_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k, int renorm,
@@ -214,73 +306,112 @@ route_small_kernel(const float* __restrict__ logits, long long part_stride, int 
     chain_release();
     chain_wait();
     extern __shared__ float lg[];              // [T][E + 1] logits with their K-range partials added
-    __shared__ int present[1024];
-    __shared__ int index_of[1024];
-    __shared__ int sa[32], sb[32];
-    __shared__ int sel[16 * 32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    present[threadIdx.x] = 0;
-    // all partial loads of an element are issued together, then added in ascending part order
-    for (int i = threadIdx.x; i < T * (E + 1); i += blockDim.x) {
-        const int t = i / (E + 1), e = i % (E + 1);
-        const float* src = logits + static_cast<long long>(t) * ld + e;
-        float a;
-        if (n_parts == 8) {
-            float p[8];
+    route_small_body<PER>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ns, ids, wts, sg, tasks_up, tasks_down,
+                          meta, slot_row, lg);
+}
+
+// ------------------------------------------------------------------ decode-class router
+// Router logits of a few token rows as K-range partials by warp-level mma over the plain bf16 router
+// rows (a stream over 2 MB: no tile reuse, so no shared-memory staging of the weights), and, for small
+// passes, the routing itself by the last CTA to finish (a ticket in global memory).
+//   warp = 16 router rows x one of 8 K ranges; thread (g, t) loads 16 bytes (8 columns) of rows g and
+//   g + 8 per 32-column chunk, all chunks up front; the 16 K slots of an mma are a fixed permutation of
+//   16 columns, applied to the token operand as well (see gemm/rows_mma.cu).
+// grid = (row tiles / 8, 8 ranges, groups of NT * 8 token rows), 256 threads.
+constexpr int kRouterThreads = 256;
+constexpr int kRouterChunks = 8;               // 32-column chunks kept in flight per thread
+
+struct RouterFuse {                            // routing by the last CTA (T <= 16); ticket == nullptr: logits only
+    unsigned int* ticket;
+    int E, k, renorm, e0, n_local, ns;
+    int* ids; float* wts; float* sg; int4* tasks_up; int4* tasks_down; int* meta; int* slot_row;
+};
+
+template <int NT, int PER>
+__global__ void __launch_bounds__(kRouterThreads)
+router_rows_kernel(const __nv_bfloat16* __restrict__ w, int n_rows, int K, const __nv_bfloat16* __restrict__ x, int ldx, int T,
+                   float* __restrict__ logits, long long part_stride, int ld, const RouterFuse f) {
+    chain_release();
+    extern __shared__ __align__(16) uint8_t dyn[];          // token columns of this range, later the routing's logits
+    __shared__ int is_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x * (kRouterThreads / 32) + warp;
+    const int range = blockIdx.y;
+    const int rc = K / 8;                                    // columns per range
+    const int col0 = range * rc;
+    const int tok0 = blockIdx.z * (NT * 8);
+    const int ntok = min(NT * 8, T - tok0);
+    const int xstride = rc * 2 + 64;                         // bytes; odd multiple of 64 -> conflict-free 16-byte reads
+    const int r0 = tile * 16 + g, r1 = r0 + 8;
+    const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
+    const uint4* p0 = reinterpret_cast<const uint4*>(w + static_cast<long long>(ok0 ? r0 : 0) * K + col0) + t;
+    const uint4* p1 = reinterpret_cast<const uint4*>(w + static_cast<long long>(ok1 ? r1 : 0) * K + col0) + t;
+    const int chunks = rc / 32;
+
+    float acc[NT][4];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) p[u] = src[u * part_stride];
-            a = p[0];
+    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    bool staged = false;
+    for (int c0 = 0; c0 < chunks; c0 += kRouterChunks) {
+        uint4 u0[kRouterChunks], u1[kRouterChunks];
 #pragma unroll
-            for (int u = 1; u < 8; ++u) a += p[u];
-        } else {
-            a = src[0];
-            for (int u = 1; u < n_parts; ++u) a += src[u * part_stride];
+        for (int i = 0; i < kRouterChunks; ++i) {
+            u0[i] = u1[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (c0 + i < chunks) {
+                if (ok0) u0[i] = __ldg(p0 + (c0 + i) * 4);
+                if (ok1) u1[i] = __ldg(p1 + (c0 + i) * 4);
+            }
         }
-        lg[i] = a;
-    }
-    __syncthreads();
-    if (warp < T) {
-        float w, gl;
-        int e;
-        warp_topk<PER>(lg + warp * (E + 1), 0, 1, E, k, renorm, lane, w, e, gl);
-        if (lane < k) {
-            ids[warp * k + lane] = e;
-            wts[warp * k + lane] = w;
-            sel[warp * 32 + lane] = e;
-            present[e] = 1;
+        if (!staged) {                                       // the router rows are immutable: only the token rows wait
+            chain_wait();
+            const int pieces = rc / 8;
+            for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRouterThreads) {
+                const int j = p / pieces, q = p - j * pieces;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (j < ntok) v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(tok0 + j) * ldx + col0 + q * 8);
+                *reinterpret_cast<uint4*>(dyn + j * xstride + q * 16) = v;
+            }
+            __syncthreads();
+            staged = true;
         }
-        if (lane == 0) sg[warp] = sigmoidf_(gl);
+#pragma unroll
+        for (int i = 0; i < kRouterChunks; ++i) {
+            if (c0 + i < chunks) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint4 bx = *reinterpret_cast<const uint4*>(dyn + (n * 8 + g) * xstride + (c0 + i) * 64 + t * 16);
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[n][0]), "+f"(acc[n][1]), "+f"(acc[n][2]), "+f"(acc[n][3])
+                                 : "r"(u0[i].x), "r"(u1[i].x), "r"(u0[i].y), "r"(u1[i].y), "r"(bx.x), "r"(bx.y));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[n][0]), "+f"(acc[n][1]), "+f"(acc[n][2]), "+f"(acc[n][3])
+                                 : "r"(u0[i].z), "r"(u1[i].z), "r"(u0[i].w), "r"(u1[i].w), "r"(bx.z), "r"(bx.w));
+                }
+            }
+        }
     }
+    float* out = logits + range * part_stride;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int j = n * 8 + 2 * t + e;
+            if (j < ntok) {
+                if (ok0) out[static_cast<long long>(tok0 + j) * ld + r0] = acc[n][e];
+                if (ok1) out[static_cast<long long>(tok0 + j) * ld + r1] = acc[n][2 + e];
+            }
+        }
+    }
+    if (f.ticket == nullptr) return;
+    __threadfence();
     __syncthreads();
-    // global block index of every active expert (ascending id); this rank's tasks are the active experts it holds
-    const int mine = threadIdx.x < E ? present[threadIdx.x] : 0;
-    const int local = (mine && static_cast<int>(threadIdx.x) >= e0 && static_cast<int>(threadIdx.x) < e0 + n_local) ? 1 : 0;
-    int inc = mine, inc_local = local;
-    block_scan2(inc, inc_local, sa, sb);
-    const int n_active = sa[31], n_active_local = sb[31];
-    const int idx = inc - mine;
-    index_of[threadIdx.x] = idx;
-    if (local) {
-        const int li = inc_local - 1;
-        tasks_up[li] = make_int4(threadIdx.x - e0, 0, T, idx * 16);
-        tasks_down[li] = make_int4(threadIdx.x - e0, idx * 16, T, idx * 16);
-    }
-    if (threadIdx.x < ns) {
-        const int li = n_active_local + threadIdx.x, blk = n_active + threadIdx.x;
-        tasks_up[li] = make_int4(n_local + threadIdx.x, 0, T, blk * 16);
-        tasks_down[li] = make_int4(n_local + threadIdx.x, blk * 16, T, blk * 16);
-    }
-    if (threadIdx.x == 0) {
-        meta[0] = n_active_local + ns;
-        meta[1] = (n_active + ns) * 16;
-        meta[2] = n_active_local + ns;
-    }
+    if (threadIdx.x == 0) is_last = atomicAdd(f.ticket, 1u) == gridDim.x * gridDim.y - 1 ? 1 : 0;
     __syncthreads();
-    const int slots = k + ns;
-    for (int i = threadIdx.x; i < T * slots; i += blockDim.x) {
-        const int t = i / slots, j = i % slots;
-        slot_row[i] = (j < k ? index_of[sel[t * 32 + j]] : n_active + (j - k)) * 16 + t;
-    }
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) *f.ticket = 0u;
+    route_small_body<PER>(logits, part_stride, 8, ld, T, f.E, f.k, f.renorm, f.e0, f.n_local, f.ns, f.ids, f.wts, f.sg, f.tasks_up,
+                          f.tasks_down, f.meta, f.slot_row, reinterpret_cast<float*>(dyn));
 }
 
 template <int PER>
@@ -323,6 +454,50 @@ const char* moe_route_small(const float* logits, long long part_stride, int n_pa
     else if (E <= 512) launch_chained(route_small_kernel<16>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
     else launch_chained(route_small_kernel<32>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
     return cudaGetLastError() == cudaSuccess ? nullptr : "route_small launch failed";
+}
+
+template <int NT>
+static const char* launch_router(const void* w, int n_rows, int K, const void* x, int ldx, int T, float* logits, long long part_stride,
+                                 int ld, const RouterFuse& f, int E, cudaStream_t s) {
+    const int tiles = (n_rows + 15) / 16;
+    const dim3 grid((tiles + kRouterThreads / 32 - 1) / (kRouterThreads / 32), 8, (T + NT * 8 - 1) / (NT * 8));
+    const int stage = NT * 8 * (K / 8 * 2 + 64);
+    const int route = f.ticket != nullptr ? T * (E + 1) * static_cast<int>(sizeof(float)) : 0;
+    const int sm = stage > route ? stage : route;
+    auto k4 = router_rows_kernel<NT, 4>;
+    auto k16 = router_rows_kernel<NT, 16>;
+    auto k32 = router_rows_kernel<NT, 32>;
+    auto kern = E <= 128 ? k4 : E <= 512 ? k16 : k32;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k16, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k32, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        configured = true;
+    }
+    if (sm > 96 * 1024) return "router pass does not fit in shared memory";
+    launch_chained(kern, grid, dim3(kRouterThreads), sm, s, static_cast<const __nv_bfloat16*>(w), n_rows, K,
+                   static_cast<const __nv_bfloat16*>(x), ldx, T, logits, part_stride, ld, f);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "router launch failed";
+}
+
+const char* router_rows(const void* w, int n_rows, int K, const void* x, int ldx, int T, float* logits, long long part_stride, int ld,
+                        unsigned int* ticket, int E, int k, bool renorm, int e0, int n_local, int ns, int* ids, float* wts, float* sg,
+                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, cudaStream_t s) {
+    if (K % 512 != 0) return "router columns must be a multiple of 512";
+    if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || ldx % 8 != 0)
+        return "router operands must be 16-byte aligned";
+    RouterFuse f{};
+    if (ticket != nullptr) {
+        if (T > 16 || E > 1024 || k > 32 || ns > 32 || n_rows != E + 1) return "fused routing handles up to 16 rows and 1024 experts";
+        f.ticket = ticket; f.E = E; f.k = k; f.renorm = renorm ? 1 : 0; f.e0 = e0; f.n_local = n_local; f.ns = ns;
+        f.ids = ids; f.wts = wts; f.sg = sg; f.tasks_up = reinterpret_cast<int4*>(tasks_up); f.tasks_down = reinterpret_cast<int4*>(tasks_down);
+        f.meta = meta; f.slot_row = slot_row;
+    }
+    if (T <= 8) return launch_router<1>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);
+    if (T <= 16) return launch_router<2>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);
+    if (T <= 32) return launch_router<4>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);
+    return launch_router<8>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);
 }
 
 }  // namespace vade

@@ -21,4 +21,12 @@ const char* moe_route_small(const float* logits, long long part_stride, int n_pa
                             int n_local, int ns, int* ids, float* wts, float* sg, int* tasks_up, int* tasks_down, int* meta,
                             int* slot_row, cudaStream_t s);
 
+// Decode-class router: logits[8][T][ld] = K-range partials of x [T][K] (bf16) against the plain bf16
+// router rows w [n_rows][K] by warp-level mma.  With a ticket word (zero before the first call; the
+// kernel leaves it zero) and T <= 16 the last CTA also does the small-pass routing (outputs as in
+// moe_route_small, n_rows == E + 1).
+const char* router_rows(const void* w, int n_rows, int K, const void* x, int ldx, int T, float* logits, long long part_stride, int ld,
+                        unsigned int* ticket, int E, int k, bool renorm, int e0, int n_local, int ns, int* ids, float* wts, float* sg,
+                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, cudaStream_t s);
+
 }  // namespace vade

@@ -233,3 +233,37 @@ def test_moe_matches_reference(T):
     xb, hb = ref.combine_add_norm(y2, r2, x0.clone(), wn)
     _close(xa - x0, xb - x0, rtol=3e-2, atol=2e-2)
     _close(ha, hb, rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 16, 17, 40, 100])
+def test_decode_class_router_and_experts(T):
+    """Decode class end to end: warp-mma router (fused routing up to 16 rows), gate/up partials, SwiGLU folded
+    into the down projection's staging.  Also: a row's bits do not depend on the width of its pass."""
+    cfg = small_gpu_config()
+    mw, _, _ = _layer_setup(cfg, [(0, 0, [1])], "decode")
+    m = mw.layers[0].moe
+    ops, ref = _ops(cfg), RefOps(cfg, torch.bfloat16)
+    h = _x(T, cfg.hidden_size, seed=11)
+    r1 = ops.route(h, m, phase="decode")
+    ops.check_status()
+    logits = ref.linear(h, m.router, out_fp32=True)
+    r2 = ref.route_logits(logits, m)
+    srt = lambda ids, w: torch.sort(ids.long(), dim=1)
+    assert torch.equal(torch.sort(r1.ids.long(), 1).values, torch.sort(r2.ids.long(), 1).values), "top-k selection differs"
+    _close(r1.wts.sum(1), r2.wts.sum(1), rtol=1e-3, atol=1e-5)
+    y1, _ = ops.moe_experts(m, h, r1, phase="decode")
+    ops.check_status()
+    y2, _ = ref.moe_experts(m, h, r2)
+    x0 = torch.randn(T, cfg.hidden_size, device=DEV)
+    wn = torch.randn(cfg.hidden_size, device=DEV) * 0.1
+    xa, ha = ops.combine_add_norm(y1, r1, x0.clone(), wn)
+    xb, hb = ref.combine_add_norm(y2, r2, x0.clone(), wn)
+    _close(xa - x0, xb - x0, rtol=3e-2, atol=2e-2)
+    # one row alone gives the same bits as inside the wider pass
+    for row in sorted({0, T - 1}):
+        hr = h[row:row + 1].contiguous()
+        rr = ops.route(hr, m, phase="decode")
+        yr, _ = ops.moe_experts(m, hr, rr, phase="decode")
+        xr, _ = ops.combine_add_norm(yr, rr, x0[row:row + 1].clone(), wn)
+        assert torch.equal(rr.ids[0].sort().values, r1.ids[row].sort().values)
+        assert torch.equal(xr[0], xa[row]), f"row {row} of a {T}-row decode pass differs from the same row alone"

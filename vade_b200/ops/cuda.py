@@ -36,6 +36,7 @@ class CudaOps:
         if cfg.head_dim != 256 or cfg.linear_key_head_dim != 128 or cfg.linear_value_head_dim != 128:
             raise ValueError("the sm_100a kernels handle attention head_dim 256 and GDN head dims 128")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)   # last-CTA ticket of the fused router
         self.launches = 0
         self._moe_ws = {}
 
@@ -55,19 +56,21 @@ class CudaOps:
         return batch.dev
 
     def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0,
-              ex=None, ex_offset: int = 0, local_only_from: int = -1, rows: bool = False):
+              ex=None, ex_offset: int = 0, local_only_from: int = -1, rows: bool = False, x_parts=None):
         """ex: parallel.symm.Exchange -> the epilogue stores into every rank's buffer (+ ex_offset bytes).
         rows: decode class -> the register-dataflow kernel (NVFP4 weights, epilogue 0/1, <= 64 rows per task)."""
         nv = q.kind == "nvfp4"
         rows = bool(rows and nv and epilogue != 2 and (tasks is None or bn <= 64))
+        if x_parts is not None and not rows:
+            raise ValueError("a token operand from partials needs the decode-class kernel")
         self.launches += 1
         if ex is None:
             self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1, rows)
+                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1, rows, x_parts)
         else:
             self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
                           range_stride, tasks, meta, max_tasks, self.status, [p + ex_offset for p in ex.out], ex.flags,
-                          ex.local, ex.half_stride, ex.self_rank, local_only_from, rows)
+                          ex.local, ex.half_stride, ex.self_rank, local_only_from, rows, x_parts)
 
     # ---- basic
     def embed(self, w, tokens):
@@ -189,33 +192,57 @@ class CudaOps:
 
     # ---- MoE
     def route(self, h, mw, phase: str = "prefill"):
-        """Router product + top-k + the row layout of the grouped GEMM."""
+        """Router product + top-k + the row layout of the grouped GEMM.  Decode class: the router is a
+        warp-mma stream over the bf16 router rows in 8 K ranges; for up to 16 rows its last CTA routes too."""
         T = h.shape[0]
-        if phase == "decode" and T <= 16 and mw.router.k % (8 * 64) == 0:
-            return self.route_logits(self.linear_parts(h, mw.router, 8), mw, 8)
+        q = mw.router
+        if phase == "decode" and q.kind == "plain" and q.k % 512 == 0:
+            logits = torch.empty(8, T, q.n, dtype=torch.float32, device=self.device)
+            self.launches += 1
+            if T <= 16 and q.n == self.cfg.num_experts + 1:
+                r = self._route_small_alloc(T, mw)
+                self.ext.router_rows(q.w, h, logits, self.ticket, r.E, r.k, self.cfg.norm_topk_prob, mw.expert0, mw.n_local, r.ns,
+                                     r.ids, r.wts, r.sg, r.tasks, r.tasks_down, r.meta, r.slot_row)
+                return r
+            self.ext.router_rows(q.w, h, logits, None, 0, 0, False, 0, 0, 0, None, None, None, None, None, None, None)
+            return self.route_logits(logits, mw, 8)
         return self.route_logits(self.linear(h, mw.router, out_fp32=True), mw, 1)
+
+    def _route_base(self, T, mw, zero_meta: bool):
+        cfg = self.cfg
+        k, ns, E = cfg.num_experts_per_tok, mw.n_shared, cfg.num_experts
+        dev, i32 = self.device, torch.int32
+        meta = torch.zeros(8, dtype=i32, device=dev) if zero_meta else torch.empty(8, dtype=i32, device=dev)
+        return SimpleNamespace(
+            ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
+            sg=torch.empty(T, dtype=torch.float32, device=dev), meta=meta,
+            slot_row=torch.empty(T, k + ns, dtype=i32, device=dev), T=T, k=k, ns=ns, E=E, n_local=mw.n_local)
+
+    def _route_small_alloc(self, T, mw):
+        """Small pass: a 16-row block per active expert of the whole model, tasks for the experts held here,
+        no gather.  The routing kernel writes all eight meta words."""
+        r = self._route_base(T, mw, zero_meta=False)
+        i32 = torch.int32
+        r.small, r.bn = True, 16
+        r.max_tasks = min(mw.n_local, T * r.k) + r.ns
+        r.max_rows = (min(r.E, T * r.k) + r.ns) * 16
+        r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=self.device)
+        r.tasks_down = torch.empty(r.max_tasks, 4, dtype=i32, device=self.device)
+        return r
 
     def route_logits(self, logits, mw, n_parts: int = 1):
         cfg = self.cfg
         T = logits.shape[-2]
-        k, ns, E = cfg.num_experts_per_tok, mw.n_shared, cfg.num_experts
-        slots = k + ns
-        dev, i32 = self.device, torch.int32
-        r = SimpleNamespace(
-            ids=torch.empty(T, k, dtype=i32, device=dev), wts=torch.empty(T, k, dtype=torch.float32, device=dev),
-            sg=torch.empty(T, dtype=torch.float32, device=dev), meta=torch.zeros(8, dtype=i32, device=dev),
-            slot_row=torch.empty(T, slots, dtype=i32, device=dev), T=T, k=k, ns=ns, E=E, n_local=mw.n_local)
         if T <= 16:
-            # small pass: a 16-row block per active expert of the whole model, tasks for the experts held here, no gather
-            r.small, r.bn = True, 16
-            r.max_tasks = min(mw.n_local, T * k) + ns
-            r.max_rows = (min(E, T * k) + ns) * 16
-            r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
-            r.tasks_down = torch.empty(r.max_tasks, 4, dtype=i32, device=dev)
+            r = self._route_small_alloc(T, mw)
             self.launches += 1
-            self.ext.moe_route_small(logits, n_parts, E, k, cfg.norm_topk_prob, mw.expert0, mw.n_local, ns, r.ids, r.wts, r.sg,
+            self.ext.moe_route_small(logits, n_parts, r.E, r.k, cfg.norm_topk_prob, mw.expert0, mw.n_local, r.ns, r.ids, r.wts, r.sg,
                                      r.tasks, r.tasks_down, r.meta, r.slot_row)
             return r
+        r = self._route_base(T, mw, zero_meta=True)
+        k, ns, E = r.k, r.ns, r.E
+        slots = k + ns
+        dev, i32 = self.device, torch.int32
         r.small = False
         r.bn = bn = 32 if T <= 64 else 64
         r.max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
@@ -243,25 +270,34 @@ class CudaOps:
             xs = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
             self.launches += 1
             self.ext.gather_rows(h, r.row_token, r.meta, xs, r.max_rows)
-        mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
         P = self.DECODE_PARTS
-        if phase == "decode" and mw.gate_up.k % (P * 64) == 0:
+        dec = phase == "decode"
+        # decode class on packed weights: both products run in the register-dataflow kernel and the second one
+        # reads SwiGLU of the first one's partials while it stages its token operand (no kernel in between)
+        fused = dec and mw.gate_up.kind == "nvfp4" and mw.down.kind == "nvfp4" and mw.gate_up.k % (P * 64) == 0 and r.bn <= 64
+        bn = (8 if r.T <= 8 else 16) if (fused and r.small) else r.bn
+        gu = mid = None
+        if dec and mw.gate_up.k % (P * 64) == 0:
             gu = torch.empty(P, r.max_rows, I2, dtype=torch.float32, device=self.device)
-            self._gemm(xs, mw.gate_up, gu, 1, r.bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks, rows=True)
-            self.launches += 1
-            self.ext.swiglu_fold(gu, r.meta, mid)
+            self._gemm(xs, mw.gate_up, gu, 1, bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks, rows=True)
+            if not fused:
+                mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
+                self.launches += 1
+                self.ext.swiglu_fold(gu, r.meta, mid)
         else:
+            mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
             self._gemm(xs, mw.gate_up, mid, 2, r.bn, 1, r.max_rows, I2 // 2, 0, r.tasks, r.meta, r.max_tasks)
+        xd, xp = (h, gu) if fused else (mid, None)
         if self.symm is not None:
             ex = self.symm.ex["pairs"]
             if r.max_rows * H > ex.half_stride:
                 raise ValueError("pass has more (token, expert) rows than the symmetric pair buffer was sized for")
-            self._gemm(mid, mw.down, ex.buffer, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks,
-                       ex=ex, local_only_from=mw.n_local, rows=phase == "decode")
+            self._gemm(xd, mw.down, ex.buffer, 0, bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks,
+                       ex=ex, local_only_from=mw.n_local, rows=dec, x_parts=xp)
             r.ex = ex
             return ex.buffer, None
         y = torch.empty(r.max_rows, H, dtype=torch.bfloat16, device=self.device)
-        self._gemm(mid, mw.down, y, 0, r.bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks, rows=phase == "decode")
+        self._gemm(xd, mw.down, y, 0, bn, 1, r.max_rows, H, 0, r.tasks_down, r.meta, r.max_tasks, rows=dec, x_parts=xp)
         r.ex = None
         return y, (None if self.tp == 1 else r)
 
