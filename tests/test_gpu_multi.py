@@ -38,7 +38,7 @@ def _worker(rank, world, port, fused, n_new, q):
     from vade_b200.runtime.engine import Sequence
     par = make_parallel(tp=world, pp=1, int_device=f"cuda:{rank}", fused=fused)
     eng = build_engine(small_gpu_config(), device=f"cuda:{rank}", seed=0, tp=world, tp_rank=par.tp_rank, comm=par.comm,
-                       max_seq=512, prefill_chunk=128)
+                       max_seq=512, prefill_chunk=128, synth_on_device=True)   # weights keyed by global coordinates
     out = eng.generate(_prompt(), n_new).generated
     # the captured decode step must continue the same stream
     seq = Sequence(eng.cache.new_slot())
@@ -75,7 +75,7 @@ def _launch(world, fused, n_new=12):
 
 
 def _single(n_new=12):
-    eng = build_engine(small_gpu_config(), device="cuda:0", seed=0, max_seq=512, prefill_chunk=128)
+    eng = build_engine(small_gpu_config(), device="cuda:0", seed=0, max_seq=512, prefill_chunk=128, synth_on_device=True)
     return eng.generate(_prompt(), n_new).generated
 
 
