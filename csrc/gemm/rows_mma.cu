@@ -31,27 +31,37 @@ constexpr int kRowsThreads = 128;
 constexpr int kChunk = 8;                                  // K blocks kept in flight per thread
 constexpr int kXStride = kChunk * 128 + 64;                // bytes per staged token row (odd multiple of 64: conflict-free 16-byte reads)
 
-// One byte (two e2m1 values, low nibble first) -> bf16x2 of value * scale, where `mult` holds
+// Four bytes (eight e2m1 values, low nibble first) -> four bf16x2 of value * scale, where `mult` holds
 // bf16(scale * 2^112) in both halves: f16 bits >> 3 read as bf16 equal value * 2^-112 (exact).
-__device__ __forceinline__ uint32_t expand_pair(uint32_t word, int byte, uint32_t mult) {
-    uint32_t h2, out;
-    const uint16_t b = static_cast<uint16_t>((word >> (8 * byte)) & 0xFFu);
-    asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(b));
-    const uint32_t p = ((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u);
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(p), "r"(mult));
-    return out;
+__device__ __forceinline__ void expand_word(uint32_t word, uint32_t mult, uint32_t* out) {
+    uint32_t h[4];
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t p = ((h[b] >> 3) & 0x0FFF0FFFu) | (h[b] & 0x80008000u);
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(out[b]) : "r"(p), "r"(mult));
+    }
 }
 
-// Scale bytes `b` and `b + 2` of a row's four e4m3 block scales -> two bf16x2 multipliers (scale * 2^112).
+// bf16x2 multiplier (scale * 2^112 in both halves) of one unsigned e4m3 scale byte.  Normal codes are a
+// shift and an add of the exponent bias difference; the eight subnormal codes (m * 2^-9) take the slow way.
+__device__ __forceinline__ uint32_t scale_mult(uint32_t byte) {
+    uint32_t b;
+    if (byte >= 8u) {
+        b = (byte << 4) + ((112u + 127u - 7u) << 7);
+    } else {
+        b = __float_as_uint(static_cast<float>(byte) * 0x1p103f) >> 16;      // m * 2^-9 * 2^112, exact
+    }
+    return b * 0x10001u;
+}
+
+// Scale bytes `b` and `b + 2` of a row's four e4m3 block scales -> two bf16x2 multipliers.
 __device__ __forceinline__ void scale_mults(uint32_t scales, int b, uint32_t* m_half0, uint32_t* m_half1) {
-    const uint32_t pair = __byte_perm(scales, 0u, static_cast<uint32_t>(b | ((b + 2) << 4)) | 0x4400u);
-    uint32_t h01;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(static_cast<uint16_t>(pair & 0xFFFFu)));
-    const __half2 hh = *reinterpret_cast<const __half2*>(&h01);
-    const uint32_t b0 = __float_as_uint(__low2float(hh) * 0x1p112f) >> 16;     // exact: <= 4 significant bits
-    const uint32_t b1 = __float_as_uint(__high2float(hh) * 0x1p112f) >> 16;
-    *m_half0 = b0 | (b0 << 16);
-    *m_half1 = b1 | (b1 << 16);
+    *m_half0 = scale_mult((scales >> (8 * b)) & 0x7Fu);
+    *m_half1 = scale_mult((scales >> (8 * b + 16)) & 0x7Fu);
 }
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -165,17 +175,14 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t w0 = wq[i][2 * h], w1 = wq[i][2 * h + 1];
-                        uint32_t A[8];
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            A[2 * b] = expand_pair(w0, b, m0[h]);
-                            A[2 * b + 1] = expand_pair(w1, b, m1[h]);
-                        }
+                        uint32_t A0[4], A1[4];             // bytes 0..3 of the word of row g / row g + 8
+                        expand_word(w0, m0[h], A0);
+                        expand_word(w1, m1[h], A1);
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
                             const uint4 bx = *reinterpret_cast<const uint4*>(xs + (n * 8 + g) * kXStride + i * 128 + h * 64 + t * 16);
-                            mma_bf16(acc[n], A[0], A[1], A[2], A[3], bx.x, bx.y);
-                            mma_bf16(acc[n], A[4], A[5], A[6], A[7], bx.z, bx.w);
+                            mma_bf16(acc[n], A0[0], A1[0], A0[1], A1[1], bx.x, bx.y);
+                            mma_bf16(acc[n], A0[2], A1[2], A0[3], A1[3], bx.z, bx.w);
                         }
                     }
                 }
