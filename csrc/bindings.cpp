@@ -9,6 +9,7 @@
 #include "attn/attn.h"
 #include "gdn/gdn_scan.h"
 #include "gemm/umma_gemm.h"
+#include "comm/wait_probe.h"
 #include "head/head.h"
 #include "moe/route.h"
 #include "norm/rows.h"
@@ -175,6 +176,16 @@ void router_rows(torch::Tensor w, torch::Tensor x, torch::Tensor logits, c10::op
                             ptr<int>(slot_row), stream_of(x)));
 }
 
+// Runs the bounded consumer wait of an exchange on `flags` (int32 [n]); returns after at most limit_ms.
+void wait_probe(torch::Tensor flags, int64_t self, torch::Tensor status, double limit_ms, torch::Tensor half_out) {
+    need(flags.is_cuda() && flags.scalar_type() == torch::kInt32 && flags.is_contiguous() && status.scalar_type() == torch::kInt32 &&
+         half_out.scalar_type() == torch::kInt32 && status.is_cuda() && half_out.is_cuda(), "wait_probe arguments");
+    c10::cuda::CUDAGuard guard(flags.device());
+    check(vade::wait_probe(reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()), static_cast<int>(flags.numel()), static_cast<int>(self),
+                           reinterpret_cast<uint32_t*>(status.data_ptr<int>()), static_cast<unsigned long long>(limit_ms * 1e6),
+                           reinterpret_cast<uint32_t*>(half_out.data_ptr<int>()), stream_of(flags)));
+}
+
 void gdn_scan(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
               torch::Tensor dt_bias, torch::Tensor norm_w, torch::Tensor seq_slot, torch::Tensor seq_start, int64_t n_seq,
               torch::Tensor out, int64_t kh, int64_t vh, int64_t kd, int64_t vd, double eps, bool gate_silu) {
@@ -328,6 +339,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_route_small", &moe_route_small);
     m.def("router_rows", &router_rows);
+    m.def("wait_probe", &wait_probe);
     m.def("gdn_scan", &gdn_scan);
     m.def("gdn_prefill", &gdn_prefill);
     m.def("attn_prep", &attn_prep);

@@ -267,3 +267,25 @@ def test_decode_class_router_and_experts(T):
         xr, _ = ops.combine_add_norm(yr, rr, x0[row:row + 1].clone(), wn)
         assert torch.equal(rr.ids[0].sort().values, r1.ids[row].sort().values)
         assert torch.equal(xr[0], xa[row]), f"row {row} of a {T}-row decode pass differs from the same row alone"
+
+
+def test_bounded_exchange_wait_times_out_with_a_status_and_leaves_the_gpu_usable():
+    """The consumer wait of every fused exchange, run alone: a flag that nothing sets makes it give up after the
+    limit, raise the status word to 100 + the silent rank and return."""
+    import time
+    ops = _ops()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    half = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    flags = torch.tensor([3, 3, 3, 3], dtype=torch.int32, device=DEV)          # everyone published exchange 3
+    ops.ext.wait_probe(flags, 1, status, 50.0, half)
+    torch.cuda.synchronize()
+    assert int(status) == 0 and int(half) == 1
+    flags = torch.tensor([3, 3, 2, 3], dtype=torch.int32, device=DEV)          # rank 2 is one exchange behind and stays there
+    t0 = time.perf_counter()
+    ops.ext.wait_probe(flags, 1, status, 50.0, half)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert int(status) == 102, "the silent rank must be named in the status word"
+    assert 0.04 < dt < 1.0, f"the wait must end at its limit, took {dt:.3f} s"
+    y = torch.ones(8, device=DEV).sum()                                         # the context is still usable
+    assert float(y) == 8.0

@@ -186,6 +186,38 @@ def cmd_bench(a) -> int:
     return 0
 
 
+def cmd_profile(a) -> int:
+    """Device time per kernel and per kernel class of one prompt pass and of one captured decode step."""
+    import torch
+    from ..config import NAMED_CONFIGS
+    from ..runtime.build import build_engine
+    from ..runtime.engine import Sequence
+    from ..runtime.graphs import DecodeGraph
+    from ..utils.profile import device_profile, format_profile
+    cfg = NAMED_CONFIGS[a.config]()
+    eng = build_engine(cfg, device="cuda", slots=2, max_seq=a.context + 256, synth_on_device=True, with_mtp=False,
+                       prefill_chunk=a.prefill_chunk)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (a.context,), generator=g).tolist()
+    warm = Sequence(eng.cache.new_slot())
+    eng.prefill(warm, prompt[:256])
+    eng.cache.free_slot(warm.slot)
+    seq = Sequence(eng.cache.new_slot())
+    state = {}
+    p = device_profile(lambda: state.update(h=eng.prefill(seq, prompt)[1]))
+    print(format_profile(f"prompt pass, {a.context} tokens, tiles of {a.prefill_chunk}", p, a.top))
+    tok = int(eng.model.greedy(state["h"])[0])
+    eng.cache.ensure(seq.slot, a.context + 200)
+    gr = DecodeGraph(eng, [seq.slot], a.context + 200)
+    gr.capture([tok], [a.context])
+    for _ in range(5):
+        gr.replay()
+    p = device_profile(gr.replay, repeats=4)
+    print(format_profile(f"decode step (CUDA graph, batch 1, context {a.context}); programmatic dependent launch "
+                         f"{'off' if os.environ.get('VADE_PDL') == '0' else 'on: kernels overlap, so times include waiting'}", p, a.top))
+    return 0
+
+
 def cmd_doctor(a) -> int:
     import torch
     rep = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available()}
@@ -237,6 +269,8 @@ def main(argv=None) -> int:
     p.add_argument("--cohorts", type=int, nargs="*", default=[1, 4, 8]); p.add_argument("--cohort-tokens", type=int, default=256)
     p.add_argument("--draft", default="plain"); p.add_argument("--api-key", default=None); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("profile"); p.add_argument("--config", default="qwen3-next-80b-a3b"); p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--prefill-chunk", type=int, default=2048); p.add_argument("--top", type=int, default=24); p.set_defaults(fn=cmd_profile)
     p = sub.add_parser("gateway"); p.add_argument("upstream", nargs="+"); p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=8080); p.set_defaults(fn=cmd_gateway)
     a = ap.parse_args(argv)

@@ -19,8 +19,12 @@ engine/crates/engine/src/hybrid/tp_group.rs:20-25).
 """
 from __future__ import annotations
 
+import time
+
 import torch
 import torch.distributed as dist
+
+from ..utils import profile as _profile
 
 
 class LocalComm:
@@ -58,7 +62,16 @@ class TorchComm(LocalComm):
     def _all_gather(self, t: torch.Tensor) -> list:
         t = t.contiguous()
         outs = [torch.empty_like(t) for _ in range(self.tp)]
+        prof = _profile.collectives()
+        if prof is None:
+            dist.all_gather(outs, t, group=self.group)
+            return outs
+        # profiled: the host waits for the collective so the sample is its whole latency
+        t0 = time.perf_counter_ns()
         dist.all_gather(outs, t, group=self.group)
+        if t.is_cuda:
+            torch.cuda.current_stream(t.device).synchronize()
+        prof.note("gather", "nccl" if t.is_cuda else "gloo", time.perf_counter_ns() - t0, t.numel() * t.element_size() * self.tp)
         return outs
 
     def gather_partials(self, parts: torch.Tensor) -> torch.Tensor:

@@ -22,6 +22,8 @@ from dataclasses import dataclass, field
 
 import torch
 
+from . import watchdog
+
 from ..config import ModelConfig
 from ..models.hybrid import HybridModel
 from ..ops.api import Batch
@@ -110,10 +112,18 @@ class Engine:
         batch = Batch.make(items, self.device, "decode")
         return self._run(batch)
 
+    def read_ints(self, t: torch.Tensor) -> list:
+        """Device -> host read of a small integer tensor.  This is where the host blocks on the GPU, so the
+        wait carries a deadline (runtime/watchdog.py): a stuck device ends the process instead of holding it."""
+        if t.is_cuda:
+            with watchdog.wait("token read-back"):
+                return [int(v) for v in t.tolist()]
+        return [int(v) for v in t.tolist()]
+
     def choose(self, seq: Sequence, h_row: torch.Tensor, position: int, history: list | None = None) -> int:
         """The target's token for ``position`` from final-norm row ``h_row`` [1, H]."""
         if seq.sampling.plain_greedy:
-            return int(self.model.greedy(h_row)[0])
+            return self.read_ints(self.model.greedy(h_row))[0]
         logits = self.model.logits(h_row)[0]
         return sample(logits, seq.sampling, position, seq.tokens if history is None else history)
 
@@ -130,7 +140,7 @@ class Engine:
         for d in range(depth):
             batch = Batch.make([(seq.slot, base + d, [tok])], self.device, "decode")
             x, h = m.mtp_forward(batch, self.cache, hid)
-            tok = int(m.greedy(h)[0])
+            tok = self.read_ints(m.greedy(h))[0]
             drafts.append(tok)
             hid = x
         self.cache.length[seq.slot] = snap_len
@@ -176,7 +186,7 @@ class Engine:
             keep, targets = 1, [0]
             if last:
                 if len(rows) > 1 or seq.sampling.plain_greedy:
-                    targets = [int(t) for t in self.model.greedy(h)]
+                    targets = self.read_ints(self.model.greedy(h))
                 else:
                     targets = [self.choose(seq, h[-1:], len(seq.tokens) + 1, seq.tokens + rows)]
                 while keep < len(rows) and rows[keep] == targets[keep - 1]:

@@ -82,3 +82,7 @@ class DecodeGraph:
 
     def replay(self) -> None:
         self.graph.replay()
+
+    def read_tokens(self) -> list:
+        """The step's chosen tokens on the host (a deadline-guarded wait on the device)."""
+        return self.engine.read_ints(self.tokens)
