@@ -71,6 +71,56 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
     check(vade::umma_gemm(a, stream_of(x)));
 }
 
+// W8A8: x8 / w8 are e4m3 bytes, x_scale [rows, k/128], w_scale [e?, n_out, k/128] (fp32).
+void gemm_fp8(torch::Tensor x8, torch::Tensor x_scale, torch::Tensor w8, torch::Tensor w_scale, torch::Tensor out, int64_t k, int64_t n_out,
+              int64_t epilogue, int64_t bn, int64_t ranges, int64_t tokens, int64_t ldo, int64_t out_range_stride,
+              c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
+              c10::optional<torch::Tensor> status, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
+              int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from) {
+    need(x8.is_cuda() && x8.scalar_type() == torch::kUInt8 && x8.dim() == 2 && x8.is_contiguous() && x8.size(1) == k, "x8 must be e4m3 bytes [rows, k]");
+    need(w8.is_cuda() && w8.scalar_type() == torch::kUInt8 && w8.is_contiguous() && w8.size(-1) == k, "w8 must be e4m3 bytes [..., n, k]");
+    need(x_scale.scalar_type() == torch::kFloat32 && x_scale.is_contiguous() && x_scale.size(0) == x8.size(0) && x_scale.size(1) * 128 == k,
+         "x_scale must be fp32 [rows, k/128]");
+    need(w_scale.scalar_type() == torch::kFloat32 && w_scale.is_contiguous() && w_scale.size(-1) * 128 == k && w_scale.size(-2) == n_out,
+         "w_scale must be fp32 [..., n, k/128]");
+    c10::cuda::CUDAGuard guard(x8.device());
+    vade::GemmArgs a;
+    a.x = x8.data_ptr(); a.x_rows = static_cast<int>(x8.size(0)); a.ldx = static_cast<int>(k); a.k = static_cast<int>(k);
+    a.w = w8.data_ptr(); a.nvfp4 = false; a.n_out = static_cast<int>(n_out);
+    a.w_scale = w_scale.data_ptr<float>(); a.x_scale = x_scale.data_ptr<float>();
+    a.w_experts = w8.dim() == 3 ? static_cast<int>(w8.size(0)) : 1;
+    a.out = out.data_ptr(); a.ldo = static_cast<int>(ldo); a.out_range_stride = out_range_stride; a.epilogue = static_cast<int>(epilogue);
+    a.tokens = static_cast<int>(tokens); a.bn = static_cast<int>(bn); a.ranges = static_cast<int>(ranges);
+    if (tasks.has_value()) {
+        need(meta.has_value(), "grouped GEMM needs the task count");
+        a.tasks = tasks->data_ptr<int>(); a.num_tasks = meta->data_ptr<int>(); a.max_tasks = static_cast<int>(max_tasks);
+    }
+    a.status = status.has_value() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+    if (!peer_out.empty()) {
+        need(peer_out.size() <= 8 && peer_out.size() == peer_flags.size() && peer_local != 0, "peer exchange arguments");
+        a.peers = static_cast<int>(peer_out.size());
+        for (size_t i = 0; i < peer_out.size(); ++i) {
+            a.peer_out[i] = reinterpret_cast<void*>(peer_out[i]);
+            a.peer_flags[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+        }
+        a.peer_local = reinterpret_cast<uint32_t*>(peer_local);
+        a.peer_half_stride = peer_half_stride;
+        a.peer_self = static_cast<int>(peer_self);
+        a.peer_local_only_from = static_cast<int>(peer_local_only_from);
+    }
+    check(vade::fp8_gemm(a, stream_of(x8)));
+}
+
+void act_quant_fp8(torch::Tensor x, torch::Tensor q8, torch::Tensor scale) {
+    need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows");
+    need(q8.scalar_type() == torch::kUInt8 && q8.is_contiguous() && q8.size(0) == x.size(0) && q8.size(1) == x.size(1) &&
+         scale.scalar_type() == torch::kFloat32 && scale.is_contiguous() && scale.size(0) == x.size(0) && scale.size(1) * 128 == x.size(1),
+         "act_quant_fp8 outputs");
+    c10::cuda::CUDAGuard guard(x.device());
+    check(vade::act_quant_fp8(x.data_ptr(), static_cast<int>(x.stride(0)), static_cast<int>(x.size(1)), nullptr, static_cast<int>(x.size(0)),
+                              q8.data_ptr(), scale.data_ptr<float>(), stream_of(x)));
+}
+
 void embed(torch::Tensor table, torch::Tensor tokens, torch::Tensor x) {
     need(table.scalar_type() == torch::kBFloat16 && tokens.scalar_type() == torch::kInt64 && x.scalar_type() == torch::kFloat32, "embed dtypes");
     c10::cuda::CUDAGuard guard(x.device());
@@ -340,6 +390,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route_small", &moe_route_small);
     m.def("router_rows", &router_rows);
     m.def("wait_probe", &wait_probe);
+    m.def("gemm_fp8", &gemm_fp8);
+    m.def("act_quant_fp8", &act_quant_fp8);
     m.def("gdn_scan", &gdn_scan);
     m.def("gdn_prefill", &gdn_prefill);
     m.def("attn_prep", &attn_prep);

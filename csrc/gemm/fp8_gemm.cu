@@ -1,0 +1,345 @@
+// Block-scaled FP8 projection GEMM (W8A8) on 5th-generation tensor cores, sm_100a only.
+//
+//   D[m, n] = sum over K blocks b of 128 columns, ascending:
+//                 ( sum_{k in b} W8[m, k] * X8[n, k] ) * ( w_scale[m, b] * x_scale[n, b] )
+//
+// W8 / X8 are e4m3 bytes.  x_scale is the dynamic per-token 1 x 128 scale (max|x| / 448) written by
+// act_quant_fp8 below; w_scale is the checkpoint's 128 x 128 block scale, expanded at load to one value
+// per weight ROW and K block so that fused, interleaved and rank-sliced matrices keep their scales.
+// The association (block dot in fp32, times the product of the two scales, added in ascending block
+// order) is the reference's (engine/docs/flash-fp8-math.md:36-45; kernels fp8.rs, fp8_tc.rs).
+//
+// Swap-AB like the bf16 / NVFP4 kernel: weight rows are the M = 128 operand, token rows the N operand.
+//   warp 0      TMA producer: one 128 x 128-byte weight tile and one BN x 128-byte token tile per K block
+//   warp 1      issues 4 x tcgen05.mma kind::f8f6f4 (K = 32) per K block into one of TWO TMEM buffers
+//   warps 2..9  promotion: read the finished block from TMEM, scale, add into fp32 registers while the
+//               next block's MMAs run into the other buffer; afterwards the epilogue (as in umma_gemm.cu)
+// Every mbarrier wait is bounded; on a timeout the kernel raises the status word and exits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+#include <mutex>
+#include "../common/ptx.cuh"
+#include "../common/launch.h"
+#include "gemm_dev.h"
+
+namespace vade {
+
+constexpr int kF8TileK = 128;                    // bytes = elements per K block
+constexpr int kF8AStage = kTileM * kF8TileK;     // 16 KB
+constexpr int kF8Threads = 320;
+
+struct Fp8Dev {
+    const float* w_scale;        // [experts?][n_out][kb_total]
+    const float* x_scale;        // [x_rows][kb_total]
+    long long ws_expert_stride;  // floats between stacked matrices
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kF8Threads, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmDev a, const Fp8Dev f) {
+    constexpr int kBStage = BN * kF8TileK;
+    constexpr uint32_t kBufCols = BN < 32 ? 32 : BN;           // columns of one accumulator buffer
+    constexpr uint32_t kTmemCols = 2 * kBufCols;
+    constexpr uint32_t kTxBytes = kF8AStage + kBStage;
+    constexpr int kCols = BN >= 32 ? BN / 2 : BN;              // token columns owned by one promotion thread
+
+    chain_release();
+    const int mtile = blockIdx.x;
+    const int range = blockIdx.z;
+    const int kb0 = range * a.kb_per_range;
+    const int nkb = a.kb_per_range;
+
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = sA + STAGES * kF8AStage;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * kBStage);
+    uint64_t* full = bars;                      // [STAGES] tiles landed
+    uint64_t* empty = bars + STAGES;            // [STAGES] the stage's MMAs finished
+    uint64_t* tfull = bars + 2 * STAGES;        // [2] a block's MMAs finished into buffer b
+    uint64_t* tempty = tfull + 2;               // [2] the promotion threads have read buffer b (count 256)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* sXS = reinterpret_cast<float*>(tmem_slot + 4);   // [nkb][BN] token scales of this CTA's K range
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 256); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_d = *tmem_slot;
+
+    chain_wait();                                // token tiles, scales and tasks are the previous kernels' outputs
+    int expert = 0, row0, nrows, orow0;
+    bool active = true;
+    if (a.tasks != nullptr) {
+        active = static_cast<int>(blockIdx.y) < *a.num_tasks;
+        const int4 t = active ? a.tasks[blockIdx.y] : make_int4(0, 0, 0, 0);
+        expert = t.x; row0 = t.y; nrows = t.z; orow0 = t.w;
+    } else {
+        row0 = blockIdx.y * BN;
+        nrows = min(BN, a.tokens - row0);
+        orow0 = row0;
+    }
+    auto fail = [&](uint32_t code) {
+        *abort_flag = 1;
+        if (a.status != nullptr) atomicMax(a.status, code);
+    };
+
+    if (!active) {
+        // idle task slot
+    } else if (warp == 0) {
+        if (lane == 0) {
+            const int wrow0 = expert * a.rs_expert_stride + mtile * kTileM;       // stacked matrices are n_out rows apart
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { fail(11); break; }
+                mbar_expect_tx(&full[s], kTxBytes);
+                tma_load_2d(sA + s * kF8AStage, &tmap_w, (kb0 + i) * kF8TileK, wrow0, &full[s]);
+                tma_load_2d(sB + s * kBStage, &tmap_x, (kb0 + i) * kF8TileK, row0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_e4m3(kTileM, BN);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const int b = i & 1;
+                if (!mbar_wait(&full[s], (i / STAGES) & 1)) { fail(12); break; }
+                if (!mbar_wait(&tempty[b], ((i >> 1) & 1) ^ 1)) { fail(13); break; }
+                tc_fence_after_sync();
+                const uint64_t adesc = umma_desc_sw128(smem_u32(sA + s * kF8AStage));
+                const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + s * kBStage));
+#pragma unroll
+                for (int kk = 0; kk < kF8TileK / 32; ++kk)
+                    umma_f8(tmem_d + b * kBufCols, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk != 0 ? 1u : 0u);
+                umma_commit(&empty[s]);
+                umma_commit(&tfull[b]);
+            }
+        }
+    } else {
+        const int pt = threadIdx.x - 64;          // 0..255
+        const int half = pt >> 7;                 // which half of the token columns
+        const int q = warp & 3;                   // TMEM lane quadrant this warp may read
+        const int m = mtile * kTileM + q * 32 + lane;
+        // token scales of this K range -> shared memory [block][token]
+        for (int i = pt; i < nkb * BN; i += 256) {
+            const int kb = i / BN, c = i - kb * BN;
+            sXS[i] = c < nrows ? f.x_scale[static_cast<long long>(row0 + c) * a.kb_total + kb0 + kb] : 0.f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float* wsrow = f.w_scale + static_cast<long long>(expert) * f.ws_expert_stride
+                           + static_cast<long long>(m < a.n_out ? m : 0) * a.kb_total + kb0;
+        const int cbeg = BN >= 32 ? half * kCols : 0;
+        const bool works = BN >= 32 || half == 0;
+        float acc[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
+        bool ok = true;
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int b = i & 1;
+            const float ws = wsrow[i];
+            if (!mbar_wait(&tfull[b], (i >> 1) & 1)) { fail(14); ok = false; break; }
+            tc_fence_after_sync();
+            if (works) {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 16) {
+                    float v[16];
+                    tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + b * kBufCols + cbeg + c, v);
+                    const float4* xs4 = reinterpret_cast<const float4*>(sXS + i * BN + cbeg + c);
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        const float4 xs = xs4[j4];
+                        acc[c + 4 * j4 + 0] += v[4 * j4 + 0] * (ws * xs.x);
+                        acc[c + 4 * j4 + 1] += v[4 * j4 + 1] * (ws * xs.y);
+                        acc[c + 4 * j4 + 2] += v[4 * j4 + 2] * (ws * xs.z);
+                        acc[c + 4 * j4 + 3] += v[4 * j4 + 3] * (ws * xs.w);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty[b]);
+        }
+        ok = ok && (*abort_flag == 0);
+        // ---------------- epilogue
+        const long long px_base = a.px.n > 0 ? static_cast<long long>(exchange_parity(a.px)) * a.px.half_stride : 0;
+        const bool px_all = expert < a.px.local_only_from;
+        if (ok && works) {
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const int col = cbeg + c;
+                const float y = acc[c];
+                const long long tok = orow0 + col;
+                if (EPI == 2) {
+                    const float yb = bf16_round(y);
+                    const float other = __shfl_xor_sync(0xffffffffu, yb, 1);
+                    if ((lane & 1) == 0 && col < nrows && m < a.n_out)
+                        reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + (m >> 1)] = __float2bfloat16_rn(siluf_(yb) * other);
+                } else if (col < nrows && m < a.n_out) {
+                    if (a.px.n == 0) {
+                        if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
+                        else reinterpret_cast<float*>(a.out)[range * a.out_range_stride + tok * a.ldo + m] = y;
+                    } else {
+                        const long long at = px_base + (EPI == 0 ? 0 : range * a.out_range_stride) + tok * a.ldo + m;
+                        if (px_all) {
+                            for (int d = 0; d < a.px.n; ++d) {
+                                if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[d])[at] = __float2bfloat16_rn(y);
+                                else reinterpret_cast<float*>(a.px.out[d])[at] = y;
+                            }
+                        } else {
+                            if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.px.out[a.px.self])[at] = __float2bfloat16_rn(y);
+                            else reinterpret_cast<float*>(a.px.out[a.px.self])[at] = y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (a.px.n > 0) __threadfence_system();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
+    if (a.px.n > 0 && threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
+}
+
+// ------------------------------------------------------------------ dynamic activation quantisation
+// One warp per (token, 128-column group): scale = max|x| / 448 (an all-zero group has scale 0),
+// q = e4m3_rn_satfinite(x / max(scale, 1e-12)).
+__global__ void __launch_bounds__(256)
+act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int K, const int* __restrict__ n_rows, int max_rows,
+                     uint8_t* __restrict__ q8, float* __restrict__ scale) {
+    chain_release();
+    chain_wait();
+    const int groups = K / 128;
+    const int rows = n_rows != nullptr ? min(*n_rows, max_rows) : max_rows;
+    const int warp = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows * groups) return;
+    const int r = warp / groups, g = warp - r * groups;
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<long long>(r) * ldx + g * 128 + lane * 4);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    float mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float sc = mx / 448.0f;
+    const float den = fmaxf(sc, 1e-12f);
+    uint32_t out = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v[j] / den, __NV_SATFINITE, __NV_E4M3);
+        out |= static_cast<uint32_t>(b) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(q8 + static_cast<long long>(r) * K + g * 128 + lane * 4) = out;
+    if (lane == 0) scale[static_cast<long long>(r) * groups + g] = sc;
+}
+
+const char* act_quant_fp8(const void* x, int ldx, int K, const int* n_rows, int max_rows, void* q8, float* scale, cudaStream_t s) {
+    if (K % 128 != 0 || ldx % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 7) != 0) return "act_quant_fp8: K must be a multiple of 128 and rows 8-byte aligned";
+    const long long warps = static_cast<long long>(max_rows) * (K / 128);
+    if (warps <= 0) return "act_quant_fp8: empty";
+    launch_chained(act_quant_fp8_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0, s,
+                   static_cast<const __nv_bfloat16*>(x), ldx, K, n_rows, max_rows, static_cast<uint8_t*>(q8), scale);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "act_quant_fp8 launch failed";
+}
+
+// ------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn8 encode8() {
+    static EncodeTiledFn8 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn8>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows][K] with a {128, box_rows} box and the 128-byte swizzle.
+static bool make_tmap8(CUtensorMap* m, const void* base, uint64_t K, uint64_t rows, uint32_t box_rows) {
+    EncodeTiledFn8 fn = encode8();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {K};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kF8TileK), box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, int EPI>
+static const char* launch_f8(const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, const Fp8Dev& f, dim3 grid, int nkb, cudaStream_t s) {
+    const int smem = STAGES * (kF8AStage + BN * kF8TileK) + (2 * STAGES + 4) * 8 + 16 + nkb * BN * 4 + 1024;
+    if (smem > 220 * 1024) return "fp8 GEMM: K range too long for the token-scale table";
+    static int configured = 0;
+    auto kern = fp8_gemm_kernel<BN, STAGES, EPI>;
+    if (configured < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return "cannot raise shared memory limit";
+        configured = 220 * 1024;
+    }
+    launch_chained(kern, grid, dim3(kF8Threads), smem, s, tx, tw, d, f);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "kernel launch failed";
+}
+
+template <int EPI>
+static const char* launch_f8_bn(int bn, const CUtensorMap& tx, const CUtensorMap& tw, const GemmDev& d, const Fp8Dev& f, dim3 grid, int nkb, cudaStream_t s) {
+    switch (bn) {
+        case 16:  return launch_f8<16, 6, EPI>(tx, tw, d, f, grid, nkb, s);
+        case 32:  return launch_f8<32, 6, EPI>(tx, tw, d, f, grid, nkb, s);
+        case 64:  return launch_f8<64, 5, EPI>(tx, tw, d, f, grid, nkb, s);
+        case 128: return launch_f8<128, 4, EPI>(tx, tw, d, f, grid, nkb, s);
+        default:  return "fp8 token tile must be 16, 32, 64 or 128";
+    }
+}
+
+const char* fp8_gemm(const GemmArgs& h, cudaStream_t stream) {
+    if (h.k % kF8TileK != 0 || h.k <= 0) return "fp8 GEMM: K must be a positive multiple of 128";
+    const int kb_total = h.k / kF8TileK;
+    if (h.ranges < 1 || kb_total % h.ranges != 0) return "fp8 GEMM: K blocks must divide evenly into ranges";
+    if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
+    if (h.w_scale == nullptr || h.x_scale == nullptr) return "fp8 GEMM needs weight and token scales";
+    if (((reinterpret_cast<uintptr_t>(h.x) | reinterpret_cast<uintptr_t>(h.w)) & 15) != 0) return "fp8 operands must be 16-byte aligned";
+    if (h.x_rows <= 0 || h.n_out <= 0) return "empty problem";
+    GemmDev d;
+    if (const char* err = fill_gemm_dev(h, &d)) return err;
+    d.kb_total = kb_total;
+    d.kb_per_range = kb_total / h.ranges;
+    Fp8Dev f{h.w_scale, h.x_scale, static_cast<long long>(h.n_out) * kb_total};
+    const int stacked = h.tasks != nullptr ? (h.w_experts > 0 ? h.w_experts : 1) : 1;
+    CUtensorMap tx, tw;
+    if (!make_tmap8(&tx, h.x, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.x_rows), h.bn)) return "cuTensorMapEncodeTiled failed (tokens)";
+    if (!make_tmap8(&tw, h.w, static_cast<uint64_t>(h.k), static_cast<uint64_t>(h.n_out) * stacked, kTileM)) return "cuTensorMapEncodeTiled failed (weights)";
+    const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
+    const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + h.bn - 1) / h.bn;
+    if (y <= 0) return "empty grid";
+    const dim3 grid(m_tiles, y, h.ranges);
+    switch (h.epilogue) {
+        case 0: return launch_f8_bn<0>(h.bn, tx, tw, d, f, grid, d.kb_per_range, stream);
+        case 1: return launch_f8_bn<1>(h.bn, tx, tw, d, f, grid, d.kb_per_range, stream);
+        case 2: return launch_f8_bn<2>(h.bn, tx, tw, d, f, grid, d.kb_per_range, stream);
+    }
+    return "unsupported epilogue";
+}
+
+}  // namespace vade

@@ -30,6 +30,10 @@ struct GemmArgs {
     const float* x_parts = nullptr;
     long long x_part_stride = 0;
     int x_n_parts = 0;
+    // block-scaled FP8 (fp8_gemm.cu): x and w are e4m3 bytes [rows][k]; scales per (row, 128-column block)
+    const float* w_scale = nullptr;         // [experts?][n_out][k / 128]
+    const float* x_scale = nullptr;         // [x_rows][k / 128]
+    int w_experts = 0;                      // grouped: number of stacked matrices behind w
     bool rows_kernel = false;               // decode class: register-dataflow kernel (rows_mma.cu), bn = rows per task (<= 64)
     // grouped (MoE): tasks[i] = {expert, first x row, rows (<= bn), first output row}; CTAs with blockIdx.y >= *num_tasks exit
     const int* tasks = nullptr;
@@ -49,5 +53,10 @@ struct GemmArgs {
 
 // Returns nullptr on success or a static error text.
 const char* umma_gemm(const GemmArgs& args, cudaStream_t stream);
+
+// W8A8 block-scaled FP8 product (see fp8_gemm.cu) and the per-token 1 x 128 activation quantiser that
+// feeds it: x bf16 [max_rows][ldx] -> q8 [max_rows][K] e4m3, scale [max_rows][K / 128].
+const char* fp8_gemm(const GemmArgs& args, cudaStream_t stream);
+const char* act_quant_fp8(const void* x, int ldx, int K, const int* n_rows, int max_rows, void* q8, float* scale, cudaStream_t s);
 
 }  // namespace vade

@@ -289,3 +289,56 @@ def test_bounded_exchange_wait_times_out_with_a_status_and_leaves_the_gpu_usable
     assert 0.04 < dt < 1.0, f"the wait must end at its limit, took {dt:.3f} s"
     y = torch.ones(8, device=DEV).sum()                                         # the context is still usable
     assert float(y) == 8.0
+
+
+def _fp8(n, k, seed=0, e=0):
+    g = torch.Generator().manual_seed(seed)
+    mats = []
+    for _ in range(max(e, 1)):
+        w = torch.randn(n, k, generator=g) * 0.05
+        q8, sc = codecs.fp8_block_quantize_weight(w)
+        mats.append(W.QLinear(n, k, "fp8", packed=q8, scale=sc.repeat_interleave(128, 0)[:n].contiguous(),
+                              row_scale=torch.ones(n)))
+    q = W.stack(mats) if e else mats[0]
+    return q.to(DEV)
+
+
+@pytest.mark.parametrize("T", [1, 7, 16, 33, 100, 128, 300])
+def test_gemm_fp8_block_scaled_matches_reference(T):
+    """W8A8 on tcgen05 (kind::f8f6f4): per-token 1 x 128 activation scales, per-row K-block weight scales,
+    block dots added in ascending order."""
+    ops = _ops()
+    q = _fp8(384, 1024, seed=3)
+    x = _x(T, 1024, seed=5)
+    ref = R.fp8_dot(x.float(), q.packed, q.scale)
+    y = ops.linear(x, q, out_fp32=True)
+    ops.check_status()
+    _close(y, ref, rtol=1e-4, atol=1e-5)
+    parts = ops.linear_ranges(x, q, 4)
+    _close(parts, R.fp8_dot(x.float(), q.packed, q.scale, 4), rtol=1e-4, atol=1e-5)
+    _close(ops.linear(x, q), ref)
+    if T <= 16:
+        _close(ops.linear(x, q, phase="decode").sum(0), ref, rtol=1e-4, atol=1e-5)
+    ops.check_status()
+
+
+def test_act_quant_fp8_matches_the_codec_bit_for_bit():
+    ops = _ops()
+    x = _x(37, 512, seed=8)
+    x[3, 128:256] = 0                                   # an all-zero group has scale 0 and zero codes
+    q8 = torch.empty(37, 512, dtype=torch.uint8, device=DEV)
+    sc = torch.empty(37, 4, dtype=torch.float32, device=DEV)
+    ops.ext.act_quant_fp8(x, q8, sc)
+    rq, rs = codecs.fp8_quantize_activation(x.float().cpu())
+    assert torch.equal(sc.cpu(), rs)
+    assert torch.equal(q8.cpu(), rq.view(torch.uint8) if rq.dtype != torch.uint8 else rq)
+
+
+def test_gemm_fp8_rows_do_not_depend_on_batch():
+    ops = _ops()
+    q = _fp8(256, 1024, seed=6)
+    x = _x(200, 1024)
+    full = ops.linear(x, q, out_fp32=True)
+    for t in (1, 5, 16, 40, 130):
+        part = ops.linear(x[:t].contiguous(), q, out_fp32=True)
+        assert torch.equal(part, full[:t]), f"fp8 rows change with batch width {t}"

@@ -74,3 +74,30 @@ def test_prompt_slicing_does_not_change_tokens():
         outs.append(eng.generate(p, 12).generated)
         eng.model.ops.check_status()
     assert outs[0] == outs[1] == outs[2]
+
+
+def test_fp8_block_checkpoint_runs_w8a8_and_matches_reference_ops():
+    """A block-scaled FP8 model: every quantised projection runs the W8A8 tcgen05 kernel (dynamic 1 x 128
+    activation scales), matches the PyTorch statement, and decodes the same ids twice and with drafting."""
+    from vade_b200.config import QuantConfig
+    cfg = small_gpu_config()
+    cfg.quant = QuantConfig("fp8_block", 128, list(cfg.quant.ignore))
+    a = build_engine(cfg, device="cuda", seed=0, max_seq=512)
+    kinds = {q.kind for q in a.model.w.all_linears() if q is not None}
+    assert "fp8" in kinds and "nvfp4" not in kinds
+    b = build_engine(cfg, device="cuda", seed=0, max_seq=512, reference_ops=True)
+    ids = _prompt(96)
+    outs = []
+    for eng in (a, b):
+        s = eng.cache.new_slot()
+        eng.cache.ensure(s, len(ids))
+        x, h = eng.model.forward(Batch.make([(s, 0, ids)], "cuda", "prefill"), eng.cache)
+        outs.append(x)
+    a.model.ops.check_status()
+    rel = (outs[0] - outs[1]).norm() / outs[1].norm()
+    assert rel < 6e-2, f"residual stream differs: rel {rel}"
+    p = _prompt(70, seed=3)
+    t1 = a.generate(p, 16).generated
+    assert t1 == a.generate(p, 16).generated
+    assert t1 == a.generate(p, 16, draft_depth=3).generated
+    a.model.ops.check_status()

@@ -128,6 +128,25 @@ def case_gemm(ops, name, n, k, T, ranges=1, plain=False, phase="prefill"):
     return name, (lambda: op(q)), ok, nbytes, 2.0 * n * k * T, rotation
 
 
+def case_gemm_fp8(ops, name, n, k, T):
+    """Block-scaled W8A8: activation quantiser + tcgen05 kind::f8f6f4 product."""
+    from ..quant import codecs
+    dev = ops.device
+    gen = torch.Generator(device=dev).manual_seed(11)
+    w8 = torch.randint(0, 0x78, (n, k), dtype=torch.uint8, device=dev, generator=gen)          # positive finite e4m3 codes
+    w8 |= (torch.randint(0, 2, (n, k), dtype=torch.uint8, device=dev, generator=gen) << 7)
+    ws = torch.rand(n, k // 128, device=dev, generator=gen) * 1e-3 + 1e-4
+    q = W.QLinear(n, k, "fp8", packed=w8, scale=ws, row_scale=torch.ones(n, device=dev))
+    x = torch.randn(T, k, device=dev).to(torch.bfloat16)
+    fn = lambda: ops.linear(x, q, out_fp32=True)
+    got = fn()
+    rows = min(n, 256)
+    ref = R.fp8_dot(x[:, :].float(), w8[:rows], ws[:rows])
+    ok = torch.allclose(got[:, :rows], ref, rtol=1e-3, atol=1e-3 * float(ref.abs().max()))
+    nbytes = n * k + n * (k // 128) * 4 + T * k * 2 + T * k + T * n * 4
+    return name, fn, ok, nbytes, 2.0 * n * k * T
+
+
 def _layer_weights(ops, attention: bool):
     """One layer's weights of the 80B shape (random, generated on the device) and a cache for it."""
     from ..parallel.plan import make_plan
@@ -245,6 +264,8 @@ CASES = {
     "gemm_gdn_in_proj_decode_umma": lambda ops: case_gemm(ops, "NVFP4 12352x2048, 1 row, tcgen05 tile kernel", 12352, 2048, 1),
     "gemm_lm_head_decode": lambda ops: case_gemm(ops, "bf16 151936x2048, 1 row", 151936, 2048, 1, plain=True),
     "gemm_gdn_in_proj_prefill": lambda ops: case_gemm(ops, "NVFP4 12352x2048, 2048 rows", 12352, 2048, 2048),
+    "gemm_fp8_in_proj_prefill": lambda ops: case_gemm_fp8(ops, "FP8 W8A8 12352x2048, 2048 rows (quantiser + product)", 12352, 2048, 2048),
+    "gemm_fp8_in_proj_decode": lambda ops: case_gemm_fp8(ops, "FP8 W8A8 12352x2048, 1 row (quantiser + product)", 12352, 2048, 1),
     "gemm_out_proj_prefill": lambda ops: case_gemm(ops, "NVFP4 2048x4096, 8 ranges, 2048 rows", 2048, 4096, 2048, ranges=8),
 }
 

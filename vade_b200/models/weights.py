@@ -30,10 +30,12 @@ TILE_BYTES = TILE_M * TILE_K // 2 + TILE_M * (TILE_K // 16)     # 4096 nibble by
 
 @dataclass
 class QLinear:
-    """One [n, k] matrix (or a stack of ``e`` of them) in plain or NVFP4 storage."""
+    """One [n, k] matrix (or a stack of ``e`` of them) in plain, NVFP4 or block-scaled FP8 storage.
+    fp8: ``packed`` holds e4m3 bytes [e?, n, k] and ``scale`` fp32 [e?, n, k/128]: the checkpoint's
+    128 x 128 block scale repeated for each of its rows, so rows can be fused, interleaved and sliced."""
     n: int
     k: int
-    kind: str                                   # "plain" | "nvfp4"
+    kind: str                                   # "plain" | "nvfp4" | "fp8"
     w: torch.Tensor | None = None               # plain: [e?, n, k]
     packed: torch.Tensor | None = None          # nvfp4: [e?, n, k/2] uint8, low nibble = even column
     scale: torch.Tensor | None = None           # nvfp4: [e?, n, k/16] uint8 (e4m3 bits)
@@ -48,6 +50,8 @@ class QLinear:
             return w.float()
         p = self.packed if idx is None else self.packed[idx]
         s = self.scale if idx is None else self.scale[idx]
+        if self.kind == "fp8":
+            return codecs.e4m3_decode(p) * s.repeat_interleave(128, -1)
         return codecs.nvfp4_block_values(p, s)
 
     def rs(self, idx: int | None = None) -> torch.Tensor:
@@ -117,11 +121,17 @@ class _Reader:
             c1 = k if c1 is None else c1
             assert c0 % 16 == 0 and c1 % 16 == 0
             return kind, (p[:, c0 // 2:c1 // 2], s[:, c0 // 16:c1 // 16], g)
-        # block fp8 is expanded to plain storage at load (exact: e4m3 * fp32 scale)
+        # block fp8 (W8A8): e4m3 bytes + the 128 x 128 block scale repeated per row
         q = self.src.read(name).view(torch.uint8)
         sc = self.src.read(name + "_scale_inv").float()
-        w = codecs.fp8_block_dequantize_weight(q, sc)[r0:r1]
-        return "plain", (w[:, c0:c1].to(self.act),)
+        k = q.shape[1]
+        c1 = k if c1 is None else c1
+        if k % 128 != 0 or c0 % 128 != 0 or c1 % 128 != 0:
+            # a K extent that does not tile into 128-column blocks cannot use the block-scaled kernel: plain storage (exact)
+            w = codecs.fp8_block_dequantize_weight(q, sc)[r0:r1]
+            return "plain", (w[:, c0:c1].to(self.act),)
+        rows = sc.repeat_interleave(128, 0)[:q.shape[0]]
+        return "fp8", (q[r0:r1, c0:c1].contiguous(), rows[r0:r1, c0 // 128:c1 // 128].contiguous())
 
     def vec(self, name: str, r0: int = 0, r1: int | None = None) -> torch.Tensor:
         return self.src.read(name, r0, r1).float()
@@ -139,6 +149,9 @@ def fuse(segments: list) -> QLinear:
                        row_scale=torch.ones(w.shape[0], dtype=torch.float32))
     packed = torch.cat([p[0] for _, p in segments], 0).contiguous()
     scale = torch.cat([p[1] for _, p in segments], 0).contiguous()
+    if kind == "fp8":
+        return QLinear(packed.shape[0], packed.shape[1], "fp8", packed=packed, scale=scale,
+                       row_scale=torch.ones(packed.shape[0], dtype=torch.float32))
     rs = torch.cat([p[2].expand(p[0].shape[0]) for _, p in segments], 0).contiguous().float()
     return QLinear(packed.shape[0], packed.shape[1] * 2, "nvfp4", packed=packed, scale=scale, row_scale=rs)
 
@@ -148,7 +161,7 @@ def stack(mats: list) -> QLinear:
     if a.kind == "plain":
         return QLinear(a.n, a.k, "plain", w=torch.stack([m.w for m in mats]),
                        row_scale=torch.stack([m.row_scale for m in mats]), e=len(mats))
-    return QLinear(a.n, a.k, "nvfp4", packed=torch.stack([m.packed for m in mats]),
+    return QLinear(a.n, a.k, a.kind, packed=torch.stack([m.packed for m in mats]),
                    scale=torch.stack([m.scale for m in mats]),
                    row_scale=torch.stack([m.row_scale for m in mats]), e=len(mats))
 
@@ -159,7 +172,7 @@ def interleave_rows(g: QLinear, u: QLinear) -> QLinear:
         return torch.stack([a, b], 1).reshape(a.shape[0] * 2, *a.shape[1:]).contiguous()
     if g.kind == "plain":
         return QLinear(2 * g.n, g.k, "plain", w=il(g.w, u.w), row_scale=il(g.row_scale, u.row_scale))
-    return QLinear(2 * g.n, g.k, "nvfp4", packed=il(g.packed, u.packed), scale=il(g.scale, u.scale),
+    return QLinear(2 * g.n, g.k, g.kind, packed=il(g.packed, u.packed), scale=il(g.scale, u.scale),
                    row_scale=il(g.row_scale, u.row_scale))
 
 
@@ -311,6 +324,8 @@ def _hcat(rd: _Reader, a: str, b: str):
         raise ValueError("MTP fc matrices use different storage classes")
     if ka == "plain":
         return ka, (torch.cat([pa[0], pb[0]], 1),)
+    if ka == "fp8":
+        return ka, (torch.cat([pa[0], pb[0]], 1).contiguous(), torch.cat([pa[1], pb[1]], 1).contiguous())
     # two tensor scales over one row: fold the ratio into the block scales is not exact, so keep
     # plain storage for this small matrix
     wa = codecs.nvfp4_dequantize(pa[0], pa[1], pa[2])

@@ -62,10 +62,12 @@ class RefOps:
         return R.rmsnorm(x, w, self.cfg.rms_norm_eps, True, self.act)
 
     def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
-        y = R.dot_rows(h.float(), q.dense()) * q.row_scale
+        y = R.qdot(h.float(), q) * q.row_scale
         return y if out_fp32 else R._round(y, self.act)
 
     def linear_ranges(self, h, q, n_ranges: int, phase: str = "prefill"):
+        if q.kind == "fp8":
+            return R.fp8_dot(h.float(), q.packed, q.scale, n_ranges) * q.row_scale
         return R.linear_ranges(h.float(), q.dense(), n_ranges, 0, n_ranges) * q.row_scale
 
     def fold_add_norm(self, parts, x, w):
@@ -142,9 +144,9 @@ class RefOps:
         hf = h.float()
 
         def expert(le, rows):
-            gu = R._round(R.dot_rows(hf[rows], mw.gate_up.dense(le)) * mw.gate_up.rs(le), self.act)
+            gu = R._round(R.qdot(hf[rows], mw.gate_up, le) * mw.gate_up.rs(le), self.act)
             mid = R.swiglu(gu[:, 0::2], gu[:, 1::2], self.act)
-            return R._round(R.dot_rows(mid, mw.down.dense(le)) * mw.down.rs(le), self.act)
+            return R._round(R.qdot(mid.float(), mw.down, le) * mw.down.rs(le), self.act)
 
         for le in range(mw.n_local):
             t, j = torch.nonzero(ids == mw.expert0 + le, as_tuple=True)

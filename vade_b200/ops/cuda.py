@@ -64,13 +64,19 @@ class CudaOps:
         if x_parts is not None and not rows:
             raise ValueError("a token operand from partials needs the decode-class kernel")
         self.launches += 1
-        if ex is None:
-            self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                          range_stride, tasks, meta, max_tasks, self.status, [], [], 0, 0, 0, -1, rows, x_parts)
-        else:
-            self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                          range_stride, tasks, meta, max_tasks, self.status, [p + ex_offset for p in ex.out], ex.flags,
-                          ex.local, ex.half_stride, ex.self_rank, local_only_from, rows, x_parts)
+        peers = ([], [], 0, 0, 0, -1) if ex is None else ([p + ex_offset for p in ex.out], ex.flags, ex.local, ex.half_stride,
+                                                         ex.self_rank, local_only_from)
+        if q.kind == "fp8":
+            # W8A8: dynamic per-token 1 x 128 quantisation of the token operand, then the block-scaled product
+            x8 = torch.empty(x.shape[0], q.k, dtype=torch.uint8, device=self.device)
+            xs = torch.empty(x.shape[0], q.k // 128, dtype=torch.float32, device=self.device)
+            self.launches += 1
+            self.ext.act_quant_fp8(x, x8, xs)
+            self.ext.gemm_fp8(x8, xs, q.packed, q.scale, out, q.k, q.n, epilogue, min(bn, 128), ranges, tokens, ldo, range_stride,
+                              tasks, meta, max_tasks, self.status, *peers)
+            return
+        self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
+                      range_stride, tasks, meta, max_tasks, self.status, *peers, rows, x_parts)
 
     # ---- basic
     def embed(self, w, tokens):
@@ -94,7 +100,7 @@ class CudaOps:
 
     def linear(self, h, q, out_fp32: bool = False, phase: str = "prefill"):
         T = h.shape[0]
-        if phase == "decode" and not out_fp32 and q.k % (self.DECODE_PARTS * 64) == 0:
+        if phase == "decode" and not out_fp32 and q.k % (self.DECODE_PARTS * (128 if q.kind == "fp8" else 64)) == 0:
             return self.linear_parts(h, q, self.DECODE_PARTS, rows=True)
         out = torch.empty(T, q.n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=self.device)
         self._gemm(h, q, out, 1 if out_fp32 else 0, _bn_for(T), 1, T, q.n, 0, rows=phase == "decode")

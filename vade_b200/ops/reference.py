@@ -59,6 +59,36 @@ def fold_tree(parts: torch.Tensor) -> torch.Tensor:
     return parts[0]
 
 
+def fp8_dot(x: torch.Tensor, w8: torch.Tensor, wscale: torch.Tensor, ranges: int = 1) -> torch.Tensor:
+    """Block-scaled W8A8 product: x (fp32 [T, K]) is quantised per token and 128-column group
+    (scale = max|x|/448), each K block's e4m3 x e4m3 dot is accumulated in fp32, multiplied by
+    (token scale * weight scale) and added in ascending block order.  ``ranges`` > 1 returns the
+    partial sums of equal runs of K blocks, fp32 [ranges, T, N]; else fp32 [T, N].
+    w8: e4m3 bytes [N, K]; wscale: fp32 [N, K/128] (engine/docs/flash-fp8-math.md:36-45)."""
+    from ..quant import codecs
+    T, K = x.shape
+    kb = K // 128
+    q, s = codecs.fp8_quantize_activation(x.float().cpu())
+    xa = codecs.e4m3_decode(q).view(T, kb, 128).to(x.device)
+    s = s.to(x.device)
+    wa = codecs.e4m3_decode(w8.cpu()).view(w8.shape[0], kb, 128).to(x.device)
+    per = kb // ranges
+    outs = []
+    for r in range(ranges):
+        acc = torch.zeros(T, w8.shape[0], dtype=torch.float32, device=x.device)
+        for b in range(r * per, (r + 1) * per):
+            acc = acc + dot_rows(xa[:, b], wa[:, b]) * (s[:, b, None] * wscale[None, :, b].float())
+        outs.append(acc)
+    return outs[0] if ranges == 1 else torch.stack(outs)
+
+
+def qdot(x: torch.Tensor, q, idx: int | None = None) -> torch.Tensor:
+    """x [T, K] times the rows of a stored matrix, WITHOUT its row scale, in that storage's arithmetic."""
+    if q.kind == "fp8":
+        return fp8_dot(x, q.packed if idx is None else q.packed[idx], q.scale if idx is None else q.scale[idx])
+    return dot_rows(x.float(), q.dense(idx))
+
+
 def linear_ranges(x: torch.Tensor, w: torch.Tensor, ranges: int, r0: int = 0, r1: int | None = None) -> torch.Tensor:
     """Row-parallel product as ``ranges`` partial sums over equal K slices.
     Returns fp32 [r1-r0, T, N]; ``w`` and ``x`` hold only the K columns of ranges [r0, r1)."""
