@@ -209,11 +209,13 @@ __global__ void gdn_hist_kernel(const __nv_bfloat16* __restrict__ proj, int ld, 
 }
 
 // One CTA owns 32 state columns of one value head; the 128 state rows of a column are split over
-// 8 adjacent lanes (16 rows each), so a row of the tile costs each thread 16 + 16 multiply-adds and two
-// 3-step butterflies.  Columns are independent, so a head's four column groups run on four SMs.
+// 16 adjacent lanes (8 rows each), so a row of the tile costs each thread 8 multiplies, 24 multiply-adds and
+// one 4-step butterfly over TWO values: the output of the previous row (which feeds nothing) is reduced
+// together with the memory read-out of this row, so only the state recurrence is on the critical path.
+// Columns are independent, so a head's four column groups run on four SMs; 16 warps per CTA hide latency.
 constexpr int kLeanCols = 32;
-constexpr int kLeanParts = 8;
-constexpr int kLeanRows = kD / kLeanParts;          // 16 state rows per thread
+constexpr int kLeanParts = 16;
+constexpr int kLeanRows = kD / kLeanParts;          // 8 state rows per thread
 
 constexpr int kLeanAhead = 8;                       // rows in flight (asynchronous copies)
 constexpr int kLeanRing = kLeanAhead + 1;           // one spare slot: a single barrier per row is enough
@@ -236,17 +238,17 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
     const int vhead = blockIdx.x / groups, cg = blockIdx.x % groups, b = blockIdx.y;
     const int khead = vhead / (vh / kh);
     const int part = threadIdx.x & (kLeanParts - 1);
-    const int lcol = threadIdx.x >> 3;
+    const int lcol = threadIdx.x / kLeanParts;
     const int col = cg * kLeanCols + lcol;
-    // thread `part` owns state rows 4 * (part + 8 * jj) + c (jj, c in 0..3): the eight lanes of a column read
-    // eight consecutive float4 of k / q, which is bank-conflict free
+    // thread `part` owns state rows 4 * (part + 16 * jj) + c (jj in 0..1, c in 0..3): the sixteen lanes of a column
+    // read sixteen consecutive float4 of k / q, which is bank-conflict free (the other half warp reads the same words)
     const int slot = seq_slot[b];
     const int r0 = seq_start[b], r1 = seq_start[b + 1];
     if (r0 >= r1) return;
     float S[kLeanRows];
     float* sp = state + ((static_cast<long long>(slot) * vh + vhead) * kD) * kD + col;
 #pragma unroll
-    for (int i = 0; i < kLeanRows; ++i) S[i] = sp[(4 * (part + 8 * (i >> 2)) + (i & 3)) * kD];
+    for (int i = 0; i < kLeanRows; ++i) S[i] = sp[(4 * (part + kLeanParts * (i >> 2)) + (i & 3)) * kD];
     // row rr of the tile -> ring slot (rr - r0) % kLeanRing, one commit group per row (empty past the end)
     auto stage = [&](int rr) {
         if (rr < r1) {
@@ -260,44 +262,55 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int i = 0; i < kLeanAhead; ++i) stage(r0 + i);
-    for (int r = r0; r < r1; ++r) {
+    float4 qp[kLeanRows / 4];                                       // q of the previous row (its output is still owed)
+#pragma unroll
+    for (int i = 0; i < kLeanRows / 4; ++i) qp[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = r0; r <= r1; ++r) {                                // one extra turn pays the last row's output
+        const bool live = r < r1;
         asm volatile("cp.async.wait_group %0;" ::"n"(kLeanAhead - 1) : "memory");      // the group of row r has landed
         __syncthreads();                                                                // ... for every thread; row r - 1 is fully consumed
         stage(r + kLeanAhead);                                                          // overwrites the slot of row r - 1
         const int sl = (r - r0) % kLeanRing;
         const float4* q4 = reinterpret_cast<const float4*>(qk[sl]) + part;
         const float4* k4 = reinterpret_cast<const float4*>(qk[sl] + kD) + part;
-        const float v = vs[sl][lcol], bt = bd[sl][0], dc = bd[sl][1];
-        float4 kk[kLeanRows / 4];
+        float v = 0.f, bt = 0.f, dc = 1.f;
+        float4 kk[kLeanRows / 4], qq[kLeanRows / 4];
 #pragma unroll
-        for (int i = 0; i < kLeanRows / 4; ++i) kk[i] = k4[8 * i];
+        for (int i = 0; i < kLeanRows / 4; ++i) { kk[i] = make_float4(0.f, 0.f, 0.f, 0.f); qq[i] = kk[i]; }
+        if (live) {
+            v = vs[sl][lcol]; bt = bd[sl][0]; dc = bd[sl][1];
+#pragma unroll
+            for (int i = 0; i < kLeanRows / 4; ++i) { kk[i] = k4[kLeanParts * i]; qq[i] = q4[kLeanParts * i]; }
+        }
+        // output of row r - 1 from the state as row r - 1 left it
+        float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kLeanRows / 4; ++i) {
+            o0 += S[4 * i] * qp[i].x; o1 += S[4 * i + 1] * qp[i].y; o0 += S[4 * i + 2] * qp[i].z; o1 += S[4 * i + 3] * qp[i].w;
+        }
         float m0 = 0.f, m1 = 0.f;
 #pragma unroll
         for (int i = 0; i < kLeanRows / 4; ++i) {
             S[4 * i] *= dc; S[4 * i + 1] *= dc; S[4 * i + 2] *= dc; S[4 * i + 3] *= dc;
             m0 += S[4 * i] * kk[i].x; m1 += S[4 * i + 1] * kk[i].y; m0 += S[4 * i + 2] * kk[i].z; m1 += S[4 * i + 3] * kk[i].w;
         }
-        float mem = m0 + m1;
-        mem += __shfl_xor_sync(0xffffffffu, mem, 1);
-        mem += __shfl_xor_sync(0xffffffffu, mem, 2);
-        mem += __shfl_xor_sync(0xffffffffu, mem, 4);
+        float mem = m0 + m1, o = o0 + o1;
+#pragma unroll
+        for (int sh = 1; sh < kLeanParts; sh <<= 1) {
+            mem += __shfl_xor_sync(0xffffffffu, mem, sh);
+            o += __shfl_xor_sync(0xffffffffu, o, sh);
+        }
         const float delta = (v - mem) * bt;
-        float o0 = 0.f, o1 = 0.f;
 #pragma unroll
         for (int i = 0; i < kLeanRows / 4; ++i) {
-            const float4 qq = q4[8 * i];
             S[4 * i] += kk[i].x * delta; S[4 * i + 1] += kk[i].y * delta; S[4 * i + 2] += kk[i].z * delta; S[4 * i + 3] += kk[i].w * delta;
-            o0 += S[4 * i] * qq.x; o1 += S[4 * i + 1] * qq.y; o0 += S[4 * i + 2] * qq.z; o1 += S[4 * i + 3] * qq.w;
+            qp[i] = qq[i];
         }
-        float o = o0 + o1;
-        o += __shfl_xor_sync(0xffffffffu, o, 1);
-        o += __shfl_xor_sync(0xffffffffu, o, 2);
-        o += __shfl_xor_sync(0xffffffffu, o, 4);
-        if (part == 0) o_out[(static_cast<long long>(r) * vh + vhead) * kD + col] = o;
+        if (part == 0 && r > r0) o_out[(static_cast<long long>(r - 1) * vh + vhead) * kD + col] = o;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < kLeanRows; ++i) sp[(4 * (part + 8 * (i >> 2)) + (i & 3)) * kD] = S[i];
+    for (int i = 0; i < kLeanRows; ++i) sp[(4 * (part + kLeanParts * (i >> 2)) + (i & 3)) * kD] = S[i];
 }
 
 __global__ void __launch_bounds__(128)

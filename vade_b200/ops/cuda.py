@@ -250,7 +250,10 @@ class CudaOps:
         slots = k + ns
         dev, i32 = self.device, torch.int32
         r.small = False
-        r.bn = bn = 32 if T <= 64 else 64
+        # token tile of the grouped GEMMs: about the mean number of rows per expert, so a weight tile is expanded
+        # once for as many rows as the routing gives it (wide prompt tiles -> wide token tiles)
+        mean = T * k / max(E, 1)
+        r.bn = bn = 32 if T <= 64 else 64 if mean <= 80 else 128 if (mean <= 200 or mw.gate_up.kind == "fp8") else 256
         r.max_tasks = min(mw.n_local, T * k) + (T * k) // bn + ns * (-(-T // bn))
         r.max_rows = T * slots
         counts = torch.empty(E, dtype=i32, device=dev)
