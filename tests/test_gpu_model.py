@@ -101,3 +101,11 @@ def test_fp8_block_checkpoint_runs_w8a8_and_matches_reference_ops():
     assert t1 == a.generate(p, 16).generated
     assert t1 == a.generate(p, 16, draft_depth=3).generated
     a.model.ops.check_status()
+
+
+def test_determinism_gate_on_the_gpu_including_the_captured_graph():
+    from vade_b200.cli.gate import run_gate
+    eng = build_engine(small_gpu_config(), device="cuda", seed=0, slots=17, max_seq=1024, prefill_chunk=256, synth_on_device=True)
+    lines = []
+    assert run_gate(eng, tokens=12, out=lines.append, graph=True), "\n".join(lines)
+    eng.model.ops.check_status()

@@ -1,0 +1,182 @@
+"""Determinism gate: one chat's token ids must not depend on anything but its own prompt and sampling.
+
+    python -m vade_b200.cli.main test determinism [--config small] [--device cuda] [--tokens 24]
+
+A reference chat is generated alone, cold.  Then the same chat is generated again under every condition
+that could change its arithmetic if a rule of the exactness contract were broken, and its ids are compared
+(sha256 and position of the first difference on a mismatch):
+
+    repeat            the same call again
+    width N           beside N - 1 other chats in one decode batch (N = 2, 8, 16), homogeneous prompts
+    mixed widths      beside chats of other prompt lengths that join and leave while it runs
+    slices S          prompt processed in tiles of S rows instead of the default
+    prefix cache      second turn resumes from a 64-token checkpoint of the first turn
+    draft D           exact speculative decoding with D drafted tokens per cycle (accept and rollback happen)
+    sampled           seeded sampling (temperature / top-p / top-k): same seed -> same ids alone and batched
+    cancelled peer    a neighbour is cancelled in the middle of the batch (the host-side "poison" case): the
+                      survivors' ids are unchanged
+    graph             the captured CUDA-graph decode step against the eager step (GPU only)
+
+Exit status 0 only if every case matches.  Parity: the reference's determinism gate
+(cli/docs/test.md:118-220, engine/src/bin/flash-bench/gate.rs:22-43); its poison case rejects a row inside
+a kernel, here the rejected row is a host-side cancellation.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+
+import torch
+
+from ..runtime.sampler import Sampling
+from ..runtime.scheduler import Request, Scheduler, SchedulerConfig
+
+
+def _sha(ids: list) -> str:
+    return hashlib.sha256(",".join(str(i) for i in ids).encode()).hexdigest()[:16]
+
+
+def _prompt(n: int, vocab: int, seed: int) -> list:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, max(vocab - 8, 2), (n,), generator=g).tolist()
+
+
+def _drain(sched: Scheduler, reqs: list, hook=None) -> None:
+    steps = 0
+    while any(r.state != "done" for r in reqs):
+        if hook is not None:
+            hook(steps)
+        if not sched.tick():
+            sched._reap()
+        steps += 1
+        if steps > 200000:
+            raise RuntimeError("gate: the scheduler made no progress")
+
+
+def run_gate(engine, tokens: int = 24, prompt_len: int = 150, out=print, graph: bool = False) -> bool:
+    cfg = engine.model.cfg
+    V = cfg.vocab_size
+    main = _prompt(prompt_len, V, 1)
+    slots = engine.cache.slots
+    results = []
+
+    def sched(**kw):
+        return Scheduler(engine, SchedulerConfig(reserve_foreground=0, **kw), eos_id=None)
+
+    def one(s: Scheduler, **kw) -> Request:
+        return s.submit(Request(prompt=list(main), max_tokens=tokens, ignore_eos=True, **kw))
+
+    def check(name: str, got: list, want: list) -> None:
+        ok = got == want
+        where = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), min(len(got), len(want)))
+        results.append({"case": name, "ok": ok, "sha": _sha(got), "first_difference": None if ok else where})
+        out(f"gate {name:28s} {'ok      ' if ok else 'MISMATCH'} sha={_sha(got)}" + ("" if ok else f" first difference at token {where}"))
+
+    # --- cold reference
+    s = sched()
+    r = one(s)
+    _drain(s, [r])
+    ref = list(r.output)
+    out(f"gate {'reference (alone, cold)':28s} ids={len(ref)} sha={_sha(ref)}")
+    if len(ref) != tokens:
+        out("gate: the reference run stopped early")
+        return False
+
+    s = sched()
+    r = one(s)
+    _drain(s, [r])
+    check("repeat", r.output, ref)
+
+    for width in (2, 8, 16):
+        if width > slots:
+            continue
+        s = sched()
+        reqs = [one(s)] + [s.submit(Request(prompt=_prompt(prompt_len, V, 100 + i), max_tokens=tokens, ignore_eos=True))
+                           for i in range(width - 1)]
+        _drain(s, reqs)
+        check(f"width {width}", reqs[0].output, ref)
+
+    if slots >= 4:
+        s = sched()
+        r = one(s)
+        others = [s.submit(Request(prompt=_prompt(20 + 37 * i, V, 200 + i), max_tokens=3 + 5 * i, ignore_eos=True)) for i in range(3)]
+        late = []
+
+        def join(step):
+            if step == 6 and not late:
+                late.append(s.submit(Request(prompt=_prompt(70, V, 300), max_tokens=9, ignore_eos=True)))
+        _drain(s, [r] + others, hook=join)
+        _drain(s, late)
+        check("mixed widths, join + leave", r.output, ref)
+
+    for chunk in (64, 128):
+        old = engine.prefill_chunk
+        engine.prefill_chunk = chunk
+        try:
+            s = sched(prefill_slice=chunk)
+            r = one(s)
+            _drain(s, [r])
+            check(f"prompt slices of {chunk}", r.output, ref)
+        finally:
+            engine.prefill_chunk = old
+
+    s = sched(prefix_cache_entries=8)
+    first = s.submit(Request(prompt=list(main[:128]), max_tokens=4, ignore_eos=True, cache=True))
+    _drain(s, [first])
+    r = one(s, cache=True)
+    _drain(s, [r])
+    check(f"prefix cache ({r.cached_tokens} cached)", r.output, ref)
+
+    if engine.model.w.mtp is not None:
+        for depth in (3, 7):
+            s = sched()
+            r = one(s, draft="strict", mtp_depth=depth)
+            _drain(s, [r])
+            check(f"draft {depth} ({r.accepted}/{r.drafted} kept)", r.output, ref)
+
+    samp = dict(temperature=0.8, top_p=0.9, top_k=40, seed=1234)
+    s = sched()
+    a = one(s, sampling=Sampling(**samp))
+    _drain(s, [a])
+    s = sched()
+    reqs = [one(s, sampling=Sampling(**samp))] + [s.submit(Request(prompt=_prompt(60, V, 400 + i), max_tokens=tokens, ignore_eos=True,
+                                                                      sampling=Sampling(temperature=1.0, seed=i)))
+                                                  for i in range(min(3, slots - 1))]
+    _drain(s, reqs)
+    check("sampled, alone == batched", reqs[0].output, list(a.output))
+
+    if slots >= 3:
+        s = sched()
+        r = one(s)
+        victim = s.submit(Request(prompt=_prompt(90, V, 500), max_tokens=tokens, ignore_eos=True))
+        keep = s.submit(Request(prompt=_prompt(40, V, 501), max_tokens=tokens, ignore_eos=True))
+        s2 = sched()
+        alone = s2.submit(Request(prompt=_prompt(40, V, 501), max_tokens=tokens, ignore_eos=True))
+
+        def poison(step):
+            if step == 8:
+                s.cancel(victim.id)
+        _drain(s, [r, keep], hook=poison)
+        _drain(s2, [alone])
+        check("cancelled peer: survivor 1", r.output, ref)
+        check("cancelled peer: survivor 2", keep.output, list(alone.output))
+
+    if graph and engine.device.type == "cuda":
+        from ..runtime.engine import Sequence
+        from ..runtime.graphs import DecodeGraph
+        seq = Sequence(engine.cache.new_slot())
+        _, h = engine.prefill(seq, list(main))
+        tok = engine.read_ints(engine.model.greedy(h))[0]
+        engine.cache.ensure(seq.slot, prompt_len + tokens + 8)
+        g = DecodeGraph(engine, [seq.slot], prompt_len + tokens + 8)
+        g.capture([tok], [len(seq.tokens)])
+        ids = [tok]
+        for _ in range(tokens - 1):
+            g.replay()
+            ids.append(g.read_tokens()[0])
+        engine.cache.free_slot(seq.slot)
+        check("captured graph == eager", ids, ref)
+
+    ok = all(r["ok"] for r in results)
+    out("gate " + ("PASSED" if ok else "FAILED") + " " + json.dumps({"cases": len(results), "reference_sha": _sha(ref)}))
+    return ok

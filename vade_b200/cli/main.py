@@ -218,6 +218,20 @@ def cmd_profile(a) -> int:
     return 0
 
 
+def cmd_test(a) -> int:
+    """`test determinism`: the determinism gate on a synthetic model of the named configuration."""
+    from ..config import NAMED_CONFIGS
+    from ..runtime.build import build_engine
+    from .gate import run_gate
+    if a.what != "determinism":
+        print(f"unknown gate {a.what!r}; available: determinism", file=sys.stderr)
+        return 2
+    cfg = NAMED_CONFIGS[a.config]()
+    on_gpu = a.device.startswith("cuda")
+    eng = build_engine(cfg, device=a.device, seed=a.seed, slots=17, max_seq=1024, prefill_chunk=256, synth_on_device=on_gpu)
+    return 0 if run_gate(eng, tokens=a.tokens, graph=on_gpu) else 1
+
+
 def cmd_doctor(a) -> int:
     import torch
     rep = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available()}
@@ -269,6 +283,9 @@ def main(argv=None) -> int:
     p.add_argument("--cohorts", type=int, nargs="*", default=[1, 4, 8]); p.add_argument("--cohort-tokens", type=int, default=256)
     p.add_argument("--draft", default="plain"); p.add_argument("--api-key", default=None); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("test"); p.add_argument("what", choices=["determinism"]); p.add_argument("--config", default="tiny")
+    p.add_argument("--device", default="cpu"); p.add_argument("--tokens", type=int, default=24); p.add_argument("--seed", type=int, default=0)
+    p.set_defaults(fn=cmd_test)
     p = sub.add_parser("profile"); p.add_argument("--config", default="qwen3-next-80b-a3b"); p.add_argument("--context", type=int, default=8192)
     p.add_argument("--prefill-chunk", type=int, default=2048); p.add_argument("--top", type=int, default=24); p.set_defaults(fn=cmd_profile)
     p = sub.add_parser("gateway"); p.add_argument("upstream", nargs="+"); p.add_argument("--host", default="127.0.0.1")
