@@ -321,6 +321,18 @@ void swiglu_fold(torch::Tensor parts, torch::Tensor meta, torch::Tensor mid) {
                       static_cast<int>(parts.size(1)), static_cast<int>(mid.size(1)), stream_of(parts));
 }
 
+// vals [rows, k] fp32 and ids [rows, k] int64: the k best logits of each row, canonical order.
+void topk_rows(torch::Tensor logits, int64_t k, torch::Tensor vals, torch::Tensor ids) {
+    need(logits.is_cuda() && logits.scalar_type() == torch::kFloat32 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 rows");
+    need(vals.scalar_type() == torch::kFloat32 && ids.scalar_type() == torch::kInt64 && vals.is_contiguous() && ids.is_contiguous() &&
+         vals.size(0) == logits.size(0) && vals.size(1) == k && ids.size(0) == logits.size(0) && ids.size(1) == k, "top-k outputs");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t chunks = (logits.size(1) + vade::argmax_chunk() - 1) / vade::argmax_chunk();
+    auto cand = torch::empty({logits.size(0) * chunks * 64}, torch::dtype(torch::kInt64).device(logits.device()));
+    check(vade::topk_rows(logits.data_ptr<float>(), logits.stride(0), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                          static_cast<int>(k), cand.data_ptr(), vals.data_ptr<float>(), reinterpret_cast<long long*>(ids.data_ptr<int64_t>()), stream_of(logits)));
+}
+
 void argmax_rows(torch::Tensor logits, int64_t id0, torch::Tensor best_val, torch::Tensor best_id,
                  c10::optional<torch::Tensor> cand, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
                  int64_t peer_half_stride, int64_t peer_self, c10::optional<torch::Tensor> status) {
@@ -398,6 +410,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attn_rows", &attn_rows);
     m.def("attn_prefill", &attn_prefill);
     m.def("argmax_rows", &argmax_rows);
+    m.def("topk_rows", &topk_rows);
     m.def("attn_split_keys", &vade::attn_split_keys);
     m.def("argmax_chunk", &vade::argmax_chunk);
     m.def("symm_alloc", &symm_alloc);

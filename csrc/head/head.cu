@@ -138,4 +138,105 @@ void argmax_rows(const float* logits, long long ld, int rows, int n, int id0, fl
 
 int argmax_chunk() { return kChunk; }
 
+// ------------------------------------------------------------------ compact top-k (k <= 64)
+// The k best logits of a row in canonical order (descending value, ascending id among equals), so a sampled
+// request moves k (value, id) pairs to the host instead of a whole vocabulary row.  Keys are 64-bit:
+// order-preserving bits of the value above the complemented id, so the largest key is the best candidate.
+// Stage 1: one CTA per 4096-logit chunk keeps its keys in shared memory and extracts its k best by k block-wide
+// maxima.  Stage 2: one CTA per row does the same over the chunks' k candidates each.  Fixed order, no atomics.
+__device__ __forceinline__ unsigned long long topk_key(float v, unsigned int id) {
+    unsigned int b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return (static_cast<unsigned long long>(b) << 32) | (0xFFFFFFFFu - id);
+}
+__device__ __forceinline__ float topk_value(unsigned long long key) {
+    unsigned int b = static_cast<unsigned int>(key >> 32);
+    b = (b & 0x80000000u) ? (b & 0x7FFFFFFFu) : ~b;
+    return __uint_as_float(b);
+}
+
+// Extracts the k largest keys of keys[0..n) (shared memory, destroyed) into out[0..k) by all 256 threads.
+__device__ void extract_topk(unsigned long long* keys, int n, int k, unsigned long long* out, unsigned long long* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int r = 0; r < k; ++r) {
+        unsigned long long best = 0ull;
+        int at = -1;
+        for (int i = threadIdx.x; i < n; i += 256) {
+            const unsigned long long v = keys[i];
+            if (v > best) { best = v; at = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > best) { best = ov; at = oa; }
+        }
+        if (lane == 0) { red[2 * warp] = best; red[2 * warp + 1] = static_cast<unsigned long long>(static_cast<long long>(at)); }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long b = 0ull;
+            long long a = -1;
+            for (int w = 0; w < 8; ++w)
+                if (red[2 * w] > b) { b = red[2 * w]; a = static_cast<long long>(red[2 * w + 1]); }
+            out[r] = b;
+            if (a >= 0) keys[a] = 0ull;                  // distinct ids make keys distinct: exactly one owner
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256)
+topk_chunks_kernel(const float* __restrict__ logits, long long ld, int n, int k, unsigned long long* __restrict__ cand, int n_chunks) {
+    chain_release();
+    chain_wait();
+    __shared__ unsigned long long keys[kChunk];
+    __shared__ unsigned long long red[16];
+    __shared__ unsigned long long best[64];
+    const int chunk = blockIdx.x, row = blockIdx.y;
+    const int base = chunk * kChunk;
+    const int m = min(kChunk, n - base);
+    for (int i = threadIdx.x; i < kChunk; i += 256)
+        keys[i] = i < m ? topk_key(logits[row * ld + base + i], static_cast<unsigned int>(base + i)) : 0ull;
+    __syncthreads();
+    extract_topk(keys, kChunk, k, best, red);
+    if (threadIdx.x < k) cand[(static_cast<long long>(row) * n_chunks + chunk) * 64 + threadIdx.x] = best[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(256)
+topk_join_kernel(const unsigned long long* __restrict__ cand, int n_chunks, int k, float* __restrict__ vals, long long* __restrict__ ids) {
+    chain_release();
+    chain_wait();
+    extern __shared__ unsigned long long jkeys[];        // [n_chunks * k]
+    __shared__ unsigned long long red[16];
+    __shared__ unsigned long long best[64];
+    const int row = blockIdx.x;
+    const int total = n_chunks * k;
+    for (int i = threadIdx.x; i < total; i += 256) {
+        const int c = i / k, j = i - c * k;
+        jkeys[i] = cand[(static_cast<long long>(row) * n_chunks + c) * 64 + j];
+    }
+    __syncthreads();
+    extract_topk(jkeys, total, k, best, red);
+    if (threadIdx.x < k) {
+        const unsigned long long key = best[threadIdx.x];
+        vals[row * k + threadIdx.x] = topk_value(key);
+        ids[row * k + threadIdx.x] = static_cast<long long>(0xFFFFFFFFu - static_cast<unsigned int>(key & 0xFFFFFFFFull));
+    }
+}
+
+const char* topk_rows(const float* logits, long long ld, int rows, int n, int k, void* cand, float* vals, long long* ids, cudaStream_t s) {
+    if (k < 1 || k > 64 || k > n) return "compact top-k takes 1 <= k <= 64";
+    const int n_chunks = (n + kChunk - 1) / kChunk;
+    const size_t sm = static_cast<size_t>(n_chunks) * k * sizeof(unsigned long long);
+    if (sm > 200 * 1024) return "vocabulary too large for the compact top-k join";
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(topk_join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured = true;
+    }
+    launch_chained(topk_chunks_kernel, dim3(n_chunks, rows), dim3(256), 0, s, logits, ld, n, k, static_cast<unsigned long long*>(cand), n_chunks);
+    launch_chained(topk_join_kernel, dim3(rows), dim3(256), sm, s, static_cast<const unsigned long long*>(cand), n_chunks, k, vals, ids);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "top-k launch failed";
+}
+
 }  // namespace vade

@@ -23,4 +23,8 @@ void argmax_rows(const float* logits, long long ld, int rows, int n, int id0, fl
                  void* cand, const HeadExchange* hx, uint32_t* status, cudaStream_t s);
 int argmax_chunk();
 
+// Compact top-k (k <= 64) of each row in canonical order (descending value, ascending id among equals).
+// cand: rows * ceil(n / argmax_chunk()) * 64 eight-byte words of scratch.  Returns an error text or nullptr.
+const char* topk_rows(const float* logits, long long ld, int rows, int n, int k, void* cand, float* vals, long long* ids, cudaStream_t s);
+
 }  // namespace vade

@@ -342,3 +342,26 @@ def test_gemm_fp8_rows_do_not_depend_on_batch():
     for t in (1, 5, 16, 40, 130):
         part = ops.linear(x[:t].contiguous(), q, out_fp32=True)
         assert torch.equal(part, full[:t]), f"fp8 rows change with batch width {t}"
+
+
+def test_compact_topk_is_canonical_and_sampling_through_it_is_exact():
+    """Device top-k (k <= 64): descending value, ascending id among equals; a draw through it equals the draw
+    from the full row."""
+    from vade_b200.runtime.sampler import Sampling, sample, sample_compact
+    ops = _ops()
+    g = torch.Generator().manual_seed(4)
+    V = 151936
+    logits = (torch.randn(3, V, generator=g) * 4).to(DEV)
+    logits[0, torch.randint(0, V, (300,), generator=g).to(DEV)] = float(logits[0].max())      # many ties at the top
+    logits[1, 5000:5003] = 50.0
+    for k in (1, 7, 40, 64):
+        vals, ids = ops.topk_logits(logits, k)
+        for r in range(3):
+            order = torch.sort(logits[r].double().cpu(), descending=True, stable=True).indices[:k]
+            assert torch.equal(ids[r].cpu(), order), f"row {r} k {k}: ids differ from the canonical order"
+            assert torch.equal(vals[r].cpu(), logits[r].cpu()[order])
+    s = Sampling(temperature=0.8, top_p=0.9, top_k=40, seed=99)
+    vals, ids = ops.topk_logits(logits, 40)
+    for r in range(3):
+        for pos in (0, 17, 4096):
+            assert sample_compact(vals[r], ids[r], s, pos) == sample(logits[r], s, pos)

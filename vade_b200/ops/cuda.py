@@ -327,6 +327,15 @@ class CudaOps:
     def head_logits(self, h, lm_head):
         return self.linear(h, lm_head, out_fp32=True)
 
+    def topk_logits(self, logits, k: int):
+        """(values, ids) of the k <= 64 best logits of each row, canonical order, on the device."""
+        logits = logits.contiguous()
+        vals = torch.empty(logits.shape[0], k, dtype=torch.float32, device=self.device)
+        ids = torch.empty(logits.shape[0], k, dtype=torch.int64, device=self.device)
+        self.launches += 2
+        self.ext.topk_rows(logits, k, vals, ids)
+        return vals, ids
+
     def head_argmax(self, h, lm_head, vocab0: int):
         """Greedy ids.  With a symmetric arena every rank exchanges its chunk winners and ends with the
         same global winners (the caller's merge is then the identity)."""

@@ -28,7 +28,7 @@ from ..config import ModelConfig
 from ..models.hybrid import HybridModel
 from ..ops.api import Batch
 from .cache import Cache, PAGE
-from .sampler import Sampling, sample
+from .sampler import Sampling, compact_ok, sample, sample_compact
 
 
 @dataclass
@@ -124,8 +124,15 @@ class Engine:
         """The target's token for ``position`` from final-norm row ``h_row`` [1, H]."""
         if seq.sampling.plain_greedy:
             return self.read_ints(self.model.greedy(h_row))[0]
-        logits = self.model.logits(h_row)[0]
-        return sample(logits, seq.sampling, position, seq.tokens if history is None else history)
+        logits = self.model.logits(h_row)
+        ops = self.model.ops
+        if logits.is_cuda and hasattr(ops, "topk_logits") and compact_ok(seq.sampling, logits.shape[1]):
+            # compact path: top_k (value, id) pairs leave the device instead of the vocabulary row; same draw
+            vals, ids = ops.topk_logits(logits, seq.sampling.top_k)
+            with watchdog.wait("top-k read-back"):
+                vals, ids = vals[0].cpu(), ids[0].cpu()
+            return sample_compact(vals, ids, seq.sampling, position)
+        return sample(logits[0], seq.sampling, position, seq.tokens if history is None else history)
 
     # ------------------------------------------------------------------ MTP
     def propose(self, seq: Sequence, first: int, depth: int) -> list:

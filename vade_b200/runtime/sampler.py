@@ -100,6 +100,36 @@ def candidates(logits: torch.Tensor, s: Sampling):
     return idx[order], w
 
 
+def candidates_from_topk(vals: torch.Tensor, ids: torch.Tensor, s: Sampling):
+    """The same filtered support as ``candidates`` when the row's top_k best logits are already known in
+    canonical order (vals descending, ids ascending among equals): identical float64 arithmetic on k values."""
+    l64 = vals.detach().cpu().to(torch.float64)
+    ids = ids.detach().cpu().to(torch.int64)
+    w = torch.exp((l64 - l64[0]) / s.temperature)
+    if s.top_p < 1.0:
+        total = float(w.sum())
+        c = torch.cumsum(w, 0)
+        keep = int(torch.searchsorted(c, torch.tensor(s.top_p * total, dtype=torch.float64), right=False)) + 1
+        keep = max(1, min(keep, w.numel()))
+        ids, w = ids[:keep], w[:keep]
+    if s.min_p > 0.0:
+        m = w >= s.min_p
+        ids, w = ids[m], w[m]
+    return ids, w
+
+
+def compact_ok(s: Sampling, vocab: int) -> bool:
+    """The compact device top-k path gives exactly the full path's draw: top_k in 1..64 and no penalty that
+    could reorder the candidates."""
+    return (not s.greedy and 0 < s.top_k <= 64 and s.top_k < vocab and s.repetition_penalty == 1.0
+            and s.presence_penalty == 0.0 and s.frequency_penalty == 0.0)
+
+
+def sample_compact(vals: torch.Tensor, ids: torch.Tensor, s: Sampling, position: int) -> int:
+    cid, w = candidates_from_topk(vals, ids, s)
+    return draw(cid, w, uniform(s.seed, position))
+
+
 def draw(ids: torch.Tensor, w: torch.Tensor, u: float) -> int:
     mass = float(w.sum())
     if not (mass > 0.0) or mass != mass or mass == float("inf"):
