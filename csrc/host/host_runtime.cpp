@@ -1,0 +1,242 @@
+// Native host-side runtime pieces (no CUDA): the shard reader, the streaming file hash and the KV page ledger.
+//
+//  * read_ranges   N byte ranges of one file -> caller-provided memory (pinned staging or plain), by a small
+//                  pool of reader threads; tries O_DIRECT with 4 KiB-aligned bounce reads and falls back to
+//                  buffered pread when the file system refuses it.  The loader never keeps a host copy.
+//                  Parity: engine/crates/gpu/src/load.rs (4 reader threads, pinned staging, O_DIRECT with fallback).
+//  * sha256_file   streaming SHA-256 of a file with a byte counter (checkpoint manifests and receipts).
+//                  Parity: engine/crates/hash/src/lib.rs:13-40.
+//  * PageLedger    LIFO free list of KV pages with reference counts (shared prefix pages are counted, not
+//                  copied), plus per-owner charges so admission can refuse by pages.
+//                  Parity: engine/crates/serve/src/kv_pages.rs (page geometry and ledger).
+#include <torch/extension.h>
+#include <fcntl.h>
+#include <unistd.h>
+#include <sys/stat.h>
+#include <atomic>
+#include <cerrno>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+namespace {
+
+// ------------------------------------------------------------------ ranged reads
+struct Range { int64_t offset, size; uint8_t* dst; };
+
+bool read_buffered(int fd, const Range& r) {
+    int64_t done = 0;
+    while (done < r.size) {
+        const ssize_t got = pread(fd, r.dst + done, static_cast<size_t>(r.size - done), r.offset + done);
+        if (got < 0 && errno == EINTR) continue;
+        if (got <= 0) return false;
+        done += got;
+    }
+    return true;
+}
+
+// O_DIRECT wants aligned offsets, sizes and memory: read the covering aligned span into a bounce buffer.
+bool read_direct(int fd, const Range& r, uint8_t* bounce, int64_t bounce_bytes) {
+    constexpr int64_t A = 4096;
+    int64_t pos = r.offset, left = r.size;
+    uint8_t* out = r.dst;
+    while (left > 0) {
+        const int64_t a0 = pos / A * A;
+        int64_t span = std::min<int64_t>(bounce_bytes, (pos + left - a0 + A - 1) / A * A);
+        const ssize_t got = pread(fd, bounce, static_cast<size_t>(span), a0);
+        if (got < 0 && errno == EINTR) continue;
+        if (got <= 0) return false;
+        const int64_t usable = std::min<int64_t>(left, got - (pos - a0));
+        if (usable <= 0) return false;
+        std::memcpy(out, bounce + (pos - a0), static_cast<size_t>(usable));
+        out += usable; pos += usable; left -= usable;
+    }
+    return true;
+}
+
+// Returns {bytes read, 1 if O_DIRECT served the reads else 0}.
+std::vector<int64_t> read_ranges(const std::string& path, const std::vector<int64_t>& offsets, const std::vector<int64_t>& sizes,
+                                 const std::vector<int64_t>& dst_addrs, int64_t threads, bool try_direct) {
+    if (offsets.size() != sizes.size() || offsets.size() != dst_addrs.size()) throw std::runtime_error("read_ranges: list lengths differ");
+    std::vector<Range> ranges;
+    int64_t total = 0;
+    for (size_t i = 0; i < offsets.size(); ++i) {
+        if (offsets[i] < 0 || sizes[i] < 0) throw std::runtime_error("read_ranges: negative range");
+        // split big ranges so that several threads share one tensor
+        constexpr int64_t kPiece = 32ll << 20;
+        for (int64_t o = 0; o < sizes[i]; o += kPiece)
+            ranges.push_back({offsets[i] + o, std::min(kPiece, sizes[i] - o), reinterpret_cast<uint8_t*>(dst_addrs[i]) + o});
+        total += sizes[i];
+    }
+    int fd_direct = -1;
+    if (try_direct) fd_direct = open(path.c_str(), O_RDONLY | O_DIRECT);
+    const int fd = open(path.c_str(), O_RDONLY);
+    if (fd < 0) { if (fd_direct >= 0) close(fd_direct); throw std::runtime_error("read_ranges: cannot open " + path); }
+    const int n_threads = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(threads, static_cast<int64_t>(ranges.size()))));
+    std::atomic<size_t> next{0};
+    std::atomic<bool> failed{false};
+    std::atomic<bool> direct_ok{fd_direct >= 0};
+    auto work = [&]() {
+        constexpr int64_t kBounce = 8ll << 20;
+        uint8_t* bounce = nullptr;
+        if (fd_direct >= 0 && posix_memalign(reinterpret_cast<void**>(&bounce), 4096, kBounce) != 0) bounce = nullptr;
+        for (;;) {
+            const size_t i = next.fetch_add(1);
+            if (i >= ranges.size() || failed.load()) break;
+            bool ok = false;
+            if (bounce != nullptr && direct_ok.load()) {
+                ok = read_direct(fd_direct, ranges[i], bounce, kBounce);
+                if (!ok) direct_ok.store(false);                       // the file system refused: buffered from here on
+            }
+            if (!ok) ok = read_buffered(fd, ranges[i]);
+            if (!ok) failed.store(true);
+        }
+        free(bounce);
+    };
+    {
+        pybind11::gil_scoped_release release;
+        std::vector<std::thread> pool;
+        for (int t = 1; t < n_threads; ++t) pool.emplace_back(work);
+        work();
+        for (auto& t : pool) t.join();
+    }
+    close(fd);
+    if (fd_direct >= 0) close(fd_direct);
+    if (failed.load()) throw std::runtime_error("read_ranges: short read of " + path);
+    return {total, (fd_direct >= 0 && direct_ok.load()) ? 1 : 0};
+}
+
+// ------------------------------------------------------------------ SHA-256
+struct Sha256 {
+    uint32_t h[8] = {0x6a09e667, 0xbb67ae85, 0x3c6ef372, 0xa54ff53a, 0x510e527f, 0x9b05688c, 0x1f83d9ab, 0x5be0cd19};
+    uint8_t block[64];
+    size_t fill = 0;
+    uint64_t bytes = 0;
+
+    static uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+    void compress(const uint8_t* p) {
+        static const uint32_t K[64] = {
+            0x428a2f98, 0x71374491, 0xb5c0fbcf, 0xe9b5dba5, 0x3956c25b, 0x59f111f1, 0x923f82a4, 0xab1c5ed5, 0xd807aa98, 0x12835b01, 0x243185be,
+            0x550c7dc3, 0x72be5d74, 0x80deb1fe, 0x9bdc06a7, 0xc19bf174, 0xe49b69c1, 0xefbe4786, 0x0fc19dc6, 0x240ca1cc, 0x2de92c6f, 0x4a7484aa,
+            0x5cb0a9dc, 0x76f988da, 0x983e5152, 0xa831c66d, 0xb00327c8, 0xbf597fc7, 0xc6e00bf3, 0xd5a79147, 0x06ca6351, 0x14292967, 0x27b70a85,
+            0x2e1b2138, 0x4d2c6dfc, 0x53380d13, 0x650a7354, 0x766a0abb, 0x81c2c92e, 0x92722c85, 0xa2bfe8a1, 0xa81a664b, 0xc24b8b70, 0xc76c51a3,
+            0xd192e819, 0xd6990624, 0xf40e3585, 0x106aa070, 0x19a4c116, 0x1e376c08, 0x2748774c, 0x34b0bcb5, 0x391c0cb3, 0x4ed8aa4a, 0x5b9cca4f,
+            0x682e6ff3, 0x748f82ee, 0x78a5636f, 0x84c87814, 0x8cc70208, 0x90befffa, 0xa4506ceb, 0xbef9a3f7, 0xc67178f2};
+        uint32_t w[64];
+        for (int i = 0; i < 16; ++i) w[i] = (uint32_t(p[4 * i]) << 24) | (uint32_t(p[4 * i + 1]) << 16) | (uint32_t(p[4 * i + 2]) << 8) | p[4 * i + 3];
+        for (int i = 16; i < 64; ++i) {
+            const uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+            const uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+            w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+        }
+        uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+        for (int i = 0; i < 64; ++i) {
+            const uint32_t t1 = hh + (rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25)) + ((e & f) ^ (~e & g)) + K[i] + w[i];
+            const uint32_t t2 = (rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+            hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+        }
+        h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+    }
+    void update(const uint8_t* p, size_t n) {
+        bytes += n;
+        while (n > 0) {
+            if (fill == 0 && n >= 64) { compress(p); p += 64; n -= 64; continue; }
+            const size_t take = std::min(n, 64 - fill);
+            std::memcpy(block + fill, p, take);
+            fill += take; p += take; n -= take;
+            if (fill == 64) { compress(block); fill = 0; }
+        }
+    }
+    std::string hex() {
+        const uint64_t bits = bytes * 8;
+        uint8_t pad[72] = {0x80};
+        const size_t padlen = (fill < 56 ? 56 : 120) - fill;
+        uint8_t len[8];
+        for (int i = 0; i < 8; ++i) len[i] = static_cast<uint8_t>(bits >> (56 - 8 * i));
+        const uint64_t keep = bytes;
+        update(pad, padlen);
+        update(len, 8);
+        bytes = keep;
+        static const char* d = "0123456789abcdef";
+        std::string s;
+        for (int i = 0; i < 8; ++i)
+            for (int j = 3; j >= 0; --j) { const uint8_t v = static_cast<uint8_t>(h[i] >> (8 * j)); s += d[v >> 4]; s += d[v & 15]; }
+        return s;
+    }
+};
+
+std::pair<std::string, int64_t> sha256_file(const std::string& path) {
+    const int fd = open(path.c_str(), O_RDONLY);
+    if (fd < 0) throw std::runtime_error("sha256_file: cannot open " + path);
+    Sha256 s;
+    std::vector<uint8_t> buf(4 << 20);
+    {
+        pybind11::gil_scoped_release release;
+        for (;;) {
+            const ssize_t got = read(fd, buf.data(), buf.size());
+            if (got < 0 && errno == EINTR) continue;
+            if (got <= 0) break;
+            s.update(buf.data(), static_cast<size_t>(got));
+        }
+    }
+    close(fd);
+    const int64_t n = static_cast<int64_t>(s.bytes);
+    return {s.hex(), n};
+}
+
+std::string sha256_bytes(const std::string& data) {
+    Sha256 s;
+    s.update(reinterpret_cast<const uint8_t*>(data.data()), data.size());
+    return s.hex();
+}
+
+// ------------------------------------------------------------------ KV page ledger
+class PageLedger {
+public:
+    explicit PageLedger(int64_t pages) : refs_(static_cast<size_t>(pages), 0) {
+        if (pages < 0) throw std::runtime_error("PageLedger: negative size");
+        free_.reserve(static_cast<size_t>(pages));
+        for (int64_t p = pages - 1; p >= 0; --p) free_.push_back(static_cast<int32_t>(p));
+    }
+    int64_t alloc() {
+        if (free_.empty()) return -1;
+        const int32_t p = free_.back();
+        free_.pop_back();
+        refs_[static_cast<size_t>(p)] = 1;
+        return p;
+    }
+    void retain(int64_t p) { check(p); ++refs_[static_cast<size_t>(p)]; }
+    void release(int64_t p) {
+        check(p);
+        if (--refs_[static_cast<size_t>(p)] == 0) free_.push_back(static_cast<int32_t>(p));
+    }
+    int64_t refs(int64_t p) const { return (p >= 0 && static_cast<size_t>(p) < refs_.size()) ? refs_[static_cast<size_t>(p)] : -1; }
+    int64_t available() const { return static_cast<int64_t>(free_.size()); }
+    int64_t total() const { return static_cast<int64_t>(refs_.size()); }
+private:
+    void check(int64_t p) const {
+        if (p < 0 || static_cast<size_t>(p) >= refs_.size() || refs_[static_cast<size_t>(p)] <= 0) throw std::runtime_error("PageLedger: page is not held");
+    }
+    std::vector<int32_t> free_;
+    std::vector<int32_t> refs_;
+};
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("read_ranges", &read_ranges, "parallel ranged reads of one file into caller memory");
+    m.def("sha256_file", &sha256_file, "(hex digest, bytes) of a file");
+    m.def("sha256_bytes", [](pybind11::bytes b) { return sha256_bytes(std::string(b)); });
+    pybind11::class_<PageLedger>(m, "PageLedger")
+        .def(pybind11::init<int64_t>())
+        .def("alloc", &PageLedger::alloc)
+        .def("retain", &PageLedger::retain)
+        .def("release", &PageLedger::release)
+        .def("refs", &PageLedger::refs)
+        .def_property_readonly("available", &PageLedger::available)
+        .def_property_readonly("total", &PageLedger::total);
+}

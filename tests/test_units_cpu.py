@@ -224,3 +224,65 @@ def test_gateway_affinity_key():
     m1 = affinity_key(json.dumps({"messages": [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}, {"role": "user", "content": "later"}]}).encode())
     m2 = affinity_key(json.dumps({"messages": [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}]}).encode())
     assert m1 == m2 and affinity_key(b"{\"prompt\": \"short\"}") is None
+
+
+def test_native_host_runtime_matches_the_python_statements(tmp_path):
+    """Shard reader threads, streaming SHA-256 and the page ledger (C++) against hashlib / file reads / the list ledger."""
+    import hashlib
+    import os
+    import random
+    from vade_b200.runtime.cache import OutOfPages, PageAllocator
+    from vade_b200.utils.native import host
+    m = host()
+    if m is None:
+        pytest.skip("no compiler for the native host module on this machine")
+    data = os.urandom(9_000_017)
+    p = tmp_path / "blob.bin"
+    p.write_bytes(data)
+    digest, n = m.sha256_file(str(p))
+    assert digest == hashlib.sha256(data).hexdigest() and n == len(data)
+    for msg in (b"", b"abc", b"a" * 55, b"a" * 56, b"a" * 64, b"a" * 119, b"a" * 120):
+        assert m.sha256_bytes(msg) == hashlib.sha256(msg).hexdigest()
+    buf = torch.empty(6_000_000, dtype=torch.uint8)
+    for direct in (True, False):
+        buf.zero_()
+        total, _ = m.read_ranges(str(p), [1, 4097, 8_000_000], [2_000_000, 3_000_000, 1_000_000],
+                                 [buf.data_ptr(), buf.data_ptr() + 2_000_000, buf.data_ptr() + 5_000_000], 4, direct)
+        assert total == 6_000_000
+        want = data[1:2_000_001] + data[4097:3_004_097] + data[8_000_000:9_000_000]
+        assert bytes(buf.numpy()) == want
+    with pytest.raises(RuntimeError):
+        m.read_ranges(str(p), [len(data) - 10], [100], [buf.data_ptr()], 1, False)      # past the end: a short read is an error
+    # ledger: the native and the list implementation make the same decisions on a random trace
+    a, b = PageAllocator(16, native=True), PageAllocator(16, native=False)
+    assert a._ledger is not None and b._ledger is None
+    rng, held = random.Random(3), []
+    for _ in range(2000):
+        op = rng.random()
+        if op < 0.5:
+            try:
+                pa = a.alloc()
+            except OutOfPages:
+                with pytest.raises(OutOfPages):
+                    b.alloc()
+                continue
+            assert pa == b.alloc()
+            held.append(pa)
+        elif held and op < 0.7:
+            pg = rng.choice(held)
+            a.retain(pg), b.retain(pg)
+            held.append(pg)
+        elif held:
+            pg = held.pop(rng.randrange(len(held)))
+            a.release(pg), b.release(pg)
+        assert a.available == b.available
+
+
+def test_large_tensors_go_through_the_native_reader(tmp_path):
+    from vade_b200.checkpoint import safetensors as st
+    t = {"big": torch.arange(3_000_000, dtype=torch.int32).view(3000, 1000), "small": torch.ones(4)}
+    path = str(tmp_path / "x.safetensors")
+    st.save_file(t, path)
+    f = st.TensorFile(path)
+    assert torch.equal(f.read_range("big", 100, 2900), t["big"][100:2900])
+    assert torch.equal(f.read("small"), t["small"])

@@ -18,6 +18,12 @@ _CHUNK = 8 << 20
 
 
 def digest_file(path: str) -> str:
+    """Streaming SHA-256 of a file: the native reader (csrc/host/host_runtime.cpp) for anything large, hashlib otherwise."""
+    if os.path.getsize(path) >= (1 << 20):
+        from ..utils.native import host
+        m = host()
+        if m is not None:
+            return m.sha256_file(path)[0]
     h = hashlib.sha256()
     with open(path, "rb", buffering=0) as f:
         while True:

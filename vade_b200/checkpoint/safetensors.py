@@ -34,6 +34,10 @@ class Limits:
     name_bytes: int = 1024
 
 
+NATIVE_READ_BYTES = 4 << 20      # ranges at least this large go through the native reader threads
+READER_THREADS = 4
+
+
 class SafetensorsError(ValueError):
     pass
 
@@ -158,7 +162,19 @@ class TensorFile:
             row_bytes = (info.numel // rows if rows else 0) * info.itemsize
             shape = (row1 - row0,) + info.shape[1:]
         nbytes = (row1 - row0) * row_bytes
-        self._f.seek(self.header.data_start + info.begin + row0 * row_bytes)
+        start = self.header.data_start + info.begin + row0 * row_bytes
+        if nbytes >= NATIVE_READ_BYTES:
+            from ..utils.native import host
+            m = host()
+            if m is not None:
+                # reader threads fill a (pinned, when a GPU is present) staging tensor; no other host copy is made
+                flat = torch.empty(nbytes, dtype=torch.uint8, pin_memory=torch.cuda.is_available())
+                try:
+                    m.read_ranges(self.path, [start], [nbytes], [flat.data_ptr()], READER_THREADS, True)
+                except RuntimeError as e:
+                    raise SafetensorsError(f"{self.path}: {e}") from None
+                return flat.view(info.torch_dtype).reshape(shape)
+        self._f.seek(start)
         buf = bytearray(nbytes)
         got = self._f.readinto(buf)
         if got != nbytes:

@@ -29,14 +29,28 @@ class OutOfPages(RuntimeError):
 
 
 class PageAllocator:
-    """LIFO free list with reference counts (shared prefix pages are counted, not copied)."""
+    """LIFO free list with reference counts (shared prefix pages are counted, not copied).  The ledger itself
+    is the native ``PageLedger`` (csrc/host/host_runtime.cpp) when that module is available; the Python lists
+    below state the same behaviour and are what the tests compare it with."""
 
-    def __init__(self, pages: int):
+    def __init__(self, pages: int, native: bool = True):
         self.total = pages
-        self.free = list(range(pages - 1, -1, -1))
-        self.refs = [0] * pages
+        self._ledger = None
+        if native:
+            from ..utils.native import host
+            m = host()
+            if m is not None:
+                self._ledger = m.PageLedger(pages)
+        if self._ledger is None:
+            self.free = list(range(pages - 1, -1, -1))
+            self.refs = [0] * pages
 
     def alloc(self) -> int:
+        if self._ledger is not None:
+            p = self._ledger.alloc()
+            if p < 0:
+                raise OutOfPages("KV page pool exhausted")
+            return p
         if not self.free:
             raise OutOfPages("KV page pool exhausted")
         p = self.free.pop()
@@ -44,18 +58,27 @@ class PageAllocator:
         return p
 
     def retain(self, p: int) -> None:
+        if self._ledger is not None:
+            self._ledger.retain(p)
+            return
         assert self.refs[p] > 0
         self.refs[p] += 1
 
     def release(self, p: int) -> None:
+        if self._ledger is not None:
+            self._ledger.release(p)
+            return
         assert self.refs[p] > 0
         self.refs[p] -= 1
         if self.refs[p] == 0:
             self.free.append(p)
 
+    def count(self, p: int) -> int:
+        return self._ledger.refs(p) if self._ledger is not None else self.refs[p]
+
     @property
     def available(self) -> int:
-        return len(self.free)
+        return self._ledger.available if self._ledger is not None else len(self.free)
 
 
 @dataclass

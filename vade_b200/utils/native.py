@@ -1,0 +1,55 @@
+"""The native host runtime module (csrc/host/host_runtime.cpp): shard reader threads, streaming SHA-256, KV page
+ledger.  Built in-tree next to the CUDA extension; ``host()`` returns the module or None when it cannot be built
+(then the callers use their Python statements of the same behaviour, which the tests compare with it)."""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+
+from . import events
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_SRC = os.path.join(_ROOT, "csrc", "host", "host_runtime.cpp")
+_OUT = os.path.join(_ROOT, "vade_b200", "_ext", "host")
+_NAME = "_vade_host"
+_mod = None
+_tried = False
+
+
+def _current() -> bool:
+    so = os.path.join(_OUT, _NAME + ".so")
+    return os.path.exists(so) and os.path.getmtime(so) >= os.path.getmtime(_SRC)
+
+
+def build(verbose: bool = False):
+    global _mod, _tried
+    from torch.utils import cpp_extension
+    os.makedirs(_OUT, exist_ok=True)
+    _mod = cpp_extension.load(name=_NAME, sources=[_SRC], extra_cflags=["-O2", "-std=c++17"], build_directory=_OUT,
+                              with_cuda=False, verbose=verbose)
+    _tried = True
+    return _mod
+
+
+def host():
+    global _mod, _tried
+    if _mod is not None or _tried:
+        return _mod
+    _tried = True
+    if os.environ.get("VADE_NATIVE_HOST", "1") == "0":
+        return None
+    try:
+        if _current():
+            import torch  # noqa: F401
+            spec = importlib.util.spec_from_file_location(_NAME, os.path.join(_OUT, _NAME + ".so"))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            sys.modules[_NAME] = mod
+            _mod = mod
+        else:
+            build()
+    except Exception as e:                       # no compiler, read-only tree, ...: the Python paths remain
+        events.note("native_host_unavailable", f"native_host_unavailable reason={type(e).__name__}")
+        _mod = None
+    return _mod
