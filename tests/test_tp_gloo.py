@@ -75,3 +75,10 @@ def test_tp2_pp2_speculative_matches_single():
     ref = _single()
     outs = _launch(2, 2, draft=2)
     assert all(o == ref for o in outs.values())
+
+
+def test_tp4_with_replicated_kv_heads_matches_single():
+    """Four ranks: one query head each, the single KV head replicated, two canonical K ranges per rank."""
+    ref = _single(n_new=12)
+    outs = _launch(4, 1, n_new=12)
+    assert all(o == ref for o in outs.values())
