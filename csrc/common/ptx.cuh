@@ -181,7 +181,7 @@ __device__ __forceinline__ uint32_t exchange_parity(const PeerExchange& px) {
 }
 
 // Called by ONE thread per CTA after a CTA-wide barrier that follows the CTA's peer stores (each
-// storing thread ran __threadfence_system() before the barrier).  The last CTA to arrive publishes.
+// fence below is cumulative over them: no per-thread fence is needed).  The last CTA to arrive publishes.
 __device__ __forceinline__ void exchange_arrive(const PeerExchange& px, uint32_t total_ctas) {
     __threadfence_system();
     const uint32_t prev = atomicAdd(px.local + 1, 1u);

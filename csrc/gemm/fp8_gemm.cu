@@ -209,7 +209,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             }
         }
     }
-    if (a.px.n > 0) __threadfence_system();
+    // peer stores of all threads are ordered before thread 0's system fence in exchange_arrive by the barrier below
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);

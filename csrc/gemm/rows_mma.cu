@@ -225,8 +225,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
         }
     }
     if (a.px.n > 0) {
-        __threadfence_system();
-        __syncthreads();
+        __syncthreads();                           // orders every thread's peer stores before thread 0's system fence
         if (threadIdx.x == 0) exchange_arrive(a.px, gridDim.x * gridDim.y * gridDim.z);
     }
 }

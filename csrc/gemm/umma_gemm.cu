@@ -255,7 +255,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             }
         }
     }
-    if (a.px.n > 0) __threadfence_system();
+    // peer stores of all threads are ordered before thread 0's system fence in exchange_arrive by the barrier below
     tc_fence_before_sync();
     __syncthreads();
     chain_wait();                                 // the weight producer never waited; a no-op for the rest

@@ -83,7 +83,6 @@ argmax_chunks_kernel(const float* __restrict__ logits, long long ld, int n, int 
             const long long at = static_cast<long long>(exchange_parity(px)) * px.half_stride
                                + (static_cast<long long>(px.self) * rows + row) * n_chunks + blockIdx.x;
             for (int d = 0; d < px.n; ++d) reinterpret_cast<uint2*>(px.out[d])[at] = c;
-            __threadfence_system();
             exchange_arrive(px, gridDim.x * gridDim.y);
         }
     }

@@ -27,6 +27,41 @@ def _free_port():
     return p
 
 
+def _pp_worker(rank, world, port, n_new, q):
+    """Layer pipeline over `world` GPUs: eager generation and the captured step (residual rows and the token
+    feedback travel inside the graph) must both give the single-GPU ids."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    from vade_b200.parallel.groups import make_parallel
+    from vade_b200.runtime.graphs import DecodeGraph
+    from vade_b200.runtime.engine import Sequence
+    par = make_parallel(tp=1, pp=world, int_device=f"cuda:{rank}")
+    eng = build_engine(small_gpu_config(), device=f"cuda:{rank}", seed=0, pp=world, pp_rank=par.pp_rank, pp_comm=par.pp_comm,
+                       max_seq=512, prefill_chunk=128, synth_on_device=True)
+    out = eng.generate(_prompt(), n_new).generated
+    seq = Sequence(eng.cache.new_slot())
+    _, h = eng.prefill(seq, _prompt())
+    first = eng._bcast([int(eng.model.greedy(h)[0])] if h is not None else [])[0]
+    eng.cache.ensure(seq.slot, 400)
+    g = DecodeGraph(eng, [seq.slot], 400)
+    g.capture([first], [len(seq.tokens)])
+    toks = [first]
+    for _ in range(n_new - 1):
+        g.replay()
+        toks.append(int(g.tokens[0]))           # valid on the first and the last stage
+    eng.model.ops.check_status()
+    q.put((rank, out, toks))
+    dist.barrier()
+    torch.cuda.synchronize()
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
 def _worker(rank, world, port, fused, n_new, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -74,6 +109,20 @@ def _launch(world, fused, n_new=12):
     return outs
 
 
+def _launch_pp(world, n_new=12):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_worker, args=(r, world, port, n_new, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    return outs
+
+
 def _single(n_new=12):
     eng = build_engine(small_gpu_config(), device="cuda:0", seed=0, max_seq=512, prefill_chunk=128, synth_on_device=True)
     return eng.generate(_prompt(), n_new).generated
@@ -89,3 +138,15 @@ def test_tp_matches_single_gpu(fused):
     for rank, out, toks in _launch(world, fused):
         assert out == ref, f"rank {rank} eager tokens differ from the single-GPU run"
         assert toks == ref, f"rank {rank} graph tokens differ from the single-GPU run"
+
+
+def test_pipeline_stages_match_single_gpu():
+    world = torch.cuda.device_count()
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if world < 4 else 4
+    ref = _single()
+    for rank, out, toks in _launch_pp(world):
+        assert out == ref, f"stage {rank}: eager tokens differ from the single-GPU run"
+        if rank in (0, world - 1):
+            assert toks == ref, f"stage {rank}: captured-step tokens differ from the single-GPU run"

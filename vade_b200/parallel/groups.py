@@ -53,5 +53,5 @@ def make_parallel(tp: int = 1, pp: int = 1, int_device="cpu", fused: bool = Fals
     if pp > 1:
         prev = (stage - 1) * tp + tr if stage > 0 else None
         nxt = (stage + 1) * tp + tr if stage < pp - 1 else None
-        pp_comm = PipelineComm(stage, pp, prev, nxt, (pp - 1) * tp + tr, pp_group, int_device)
+        pp_comm = PipelineComm(stage, pp, prev, nxt, (pp - 1) * tp + tr, pp_group, int_device, first_rank=tr)
     return Parallel(tp, pp, tr, stage, comm, pp_comm, tp_group)

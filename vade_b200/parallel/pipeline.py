@@ -15,9 +15,10 @@ import torch.distributed as dist
 
 class PipelineComm:
     def __init__(self, stage: int, stages: int, prev_rank: int | None, next_rank: int | None, last_rank: int,
-                 group=None, int_device="cpu"):
+                 group=None, int_device="cpu", first_rank: int = 0):
         self.stage, self.stages = stage, stages
         self.prev, self.next, self.last = prev_rank, next_rank, last_rank
+        self.first = first_rank
         self.group = group
         self.int_device = int_device
         self.sent_bytes = 0
@@ -31,6 +32,16 @@ class PipelineComm:
         buf = torch.empty(rows, hidden, dtype=torch.float32, device=device)
         dist.recv(buf, self.prev)
         return buf
+
+    def feed_back(self, tokens: torch.Tensor) -> None:
+        """The last stage's chosen token rows reach the first stage (which embeds them next step) on the device,
+        with no host round trip: capturable inside a CUDA graph."""
+        if self.stages == 1:
+            return
+        if self.stage == self.stages - 1:
+            dist.send(tokens, self.first)
+        elif self.stage == 0:
+            dist.recv(tokens, self.last)
 
     def broadcast_ints(self, values: list) -> list:
         """The last stage's list reaches every stage of this pipeline (length first, then values)."""

@@ -43,10 +43,22 @@ class DecodeGraph:
         return b
 
     def _step(self):
+        """One decode step of this rank.  With pipeline stages the fp32 residual rows arrive from the previous
+        stage and leave for the next one inside the step, and the last stage's tokens go back to the first
+        stage on the device, so a captured step needs no host round trip on any stage."""
         eng = self.engine
-        x, h = eng.model.forward(self._batch(), eng.cache)
-        nxt = eng.model.greedy(h)
-        self.tokens.copy_(nxt)
+        pp, plan = eng.pp, eng.model.plan
+        hidden = None
+        if pp is not None and not plan.first_stage:
+            hidden = pp.recv_rows(self.width, eng.cfg.hidden_size, eng.device)
+        x, h = eng.model.forward(self._batch(), eng.cache, hidden)
+        if pp is not None and not plan.last_stage:
+            pp.send_rows(x)
+        if pp is None or plan.last_stage:
+            nxt = eng.model.greedy(h)
+            self.tokens.copy_(nxt)
+        if pp is not None:
+            pp.feed_back(self.tokens)
         self.positions.add_(1)
         return x, h
 
