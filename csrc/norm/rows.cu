@@ -212,6 +212,44 @@ combine_add_norm_kernel(const __nv_bfloat16* __restrict__ y_in, const int* __res
     }
 }
 
+// The norm of an fp32 residual row with EXACTLY the arithmetic of the norm fused into combine_add_norm_kernel
+// (thread v owns columns 8v..8v+7, the same block size, the same block_sum tree), so a layer that starts a
+// pipeline stage, where the row arrives from another GPU and is normalised here, gets the bits that the fused
+// kernel of the previous layer would have produced on one GPU.
+__global__ void __launch_bounds__(1024)
+rmsnorm_pieces_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ h, int H, float eps,
+                      int ldh, int h_off) {
+    chain_release();
+    chain_wait();
+    __shared__ float red[32];
+    const long long t = blockIdx.x;
+    const int v = threadIdx.x;
+    const bool mine = v < H / 8;
+    float xs8[8];
+    float ss = 0.f;
+    if (mine) {
+        const float* xp = x + t * H + v * 8;
+        const float4 xa = *reinterpret_cast<const float4*>(xp), xb = *reinterpret_cast<const float4*>(xp + 4);
+        xs8[0] = xa.x; xs8[1] = xa.y; xs8[2] = xa.z; xs8[3] = xa.w; xs8[4] = xb.x; xs8[5] = xb.y; xs8[6] = xb.z; xs8[7] = xb.w;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) ss += xs8[c] * xs8[c];
+    }
+    const float4 wa = mine ? *reinterpret_cast<const float4*>(w + v * 8) : make_float4(0, 0, 0, 0);
+    const float4 wb = mine ? *reinterpret_cast<const float4*>(w + v * 8 + 4) : make_float4(0, 0, 0, 0);
+    const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+    if (mine) {
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(xs8[2 * c] * inv * (1.f + wv[2 * c]), xs8[2 * c + 1] * inv * (1.f + wv[2 * c + 1]));
+            op[c] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(h + t * ldh + h_off + v * 8) = o;
+    }
+}
+
 // rows of xs = rows of x picked by row_token (the MoE dispatch gather into expert-sorted order)
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
                                    const int* __restrict__ meta, __nv_bfloat16* __restrict__ xs, int H) {
@@ -257,6 +295,9 @@ void embed(const void* table, const long long* tokens, float* x, int rows, int H
 void rmsnorm(const void* x, bool x_is_bf16, const float* w, void* h, int rows, int H, float eps, int ldh, int h_off, cudaStream_t s) {
     if (x_is_bf16)
         launch_chained(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(kRowThreads), 0, s, static_cast<const __nv_bfloat16*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
+    else if (H % 8 == 0 && H <= 8192 && ldh % 8 == 0 && h_off % 8 == 0)
+        launch_chained(rmsnorm_pieces_kernel, dim3(rows), dim3(((H / 8 + 31) / 32) * 32), 0, s, static_cast<const float*>(x), w,
+                       static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
     else
         launch_chained(rmsnorm_kernel<float>, dim3(rows), dim3(kRowThreads), 0, s, static_cast<const float*>(x), w, static_cast<__nv_bfloat16*>(h), H, eps, ldh, h_off);
 }
