@@ -89,7 +89,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-next-80b-a3b")
     ap.add_argument("--prompt-len", type=int, default=8192)
-    ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--prefill-chunk", type=int, default=0,
+                    help="prompt tile rows (multiple of 64); 0 = one tile on a single GPU (each expert's weights are expanded once), "
+                         "2048 / 1024 rows with pipeline stages so that tiles overlap across stages")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="tensor/expert-parallel exchanges: fused into the kernels over peer memory, or NCCL collectives (baseline)")
@@ -122,6 +124,8 @@ def main() -> None:
         os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
         dist.init_process_group("nccl", device_id=torch.device(dev))
     use_pp = world > 1 and args.parallel == "pp"
+    if args.prefill_chunk <= 0:
+        args.prefill_chunk = (2048 if world <= 4 else 1024) if use_pp else min(8192, -(-args.prompt_len // 64) * 64)
     if use_pp and args.no_graph:
         raise SystemExit("--parallel pp runs the captured step only")
     par = make_parallel(tp=1 if use_pp else world, pp=world if use_pp else 1, int_device=dev, fused=(args.comm == "fused"))
@@ -269,7 +273,7 @@ def main() -> None:
             "scaling": "strong", "vs_baseline": round(tok_s / BASELINE_TOK_S.get(n, 41.8), 2), "dtype": "bf16 activations, NVFP4 weights",
             "data": "synthetic: random-init weights generated on device, uniform-random prompt ids (seed 1)",
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
-                       "parallelism": ("single" if n == 1 else f"pp{n}" if use_pp else f"tp{n}+ep{n}"), "cuda_graph": graph is not None,
+                       "parallelism": ("single" if n == 1 else f"pp{n}" if use_pp else f"tp{n}+ep{n}"), "cuda_graph": graph is not None, "prompt_tile_rows": args.prefill_chunk,
                        "exchanges": ("none" if n == 1 else "nccl send/recv of residual rows between stages" if use_pp else args.comm),
                        "l2": "each step streams >2 GB of weights, larger than the 126 MB L2"},
             "ttft_s": round(ttft_s, 4), "ttft_vs_baseline": round(BASELINE_TTFT_S.get(n, 1.933) / ttft_s, 2),
