@@ -109,3 +109,23 @@ def test_determinism_gate_on_the_gpu_including_the_captured_graph():
     lines = []
     assert run_gate(eng, tokens=12, out=lines.append, graph=True), "\n".join(lines)
     eng.model.ops.check_status()
+
+
+def test_scheduler_replays_captured_steps_and_matches_eager():
+    """The serving loop's decode passes go through the per-width graph pool; ids equal the eager scheduler's."""
+    from vade_b200.runtime.scheduler import Request, Scheduler, SchedulerConfig
+    eng = build_engine(small_gpu_config(), device="cuda", seed=0, slots=8, max_seq=512, prefill_chunk=128, synth_on_device=True)
+
+    def run(graphs):
+        s = Scheduler(eng, SchedulerConfig(reserve_foreground=0, decode_graphs=graphs))
+        reqs = [s.submit(Request(prompt=_prompt(40 + 13 * i, seed=20 + i), max_tokens=10 + i, ignore_eos=True)) for i in range(5)]
+        while any(r.state != "done" for r in reqs):
+            if not s.tick():
+                s._reap()
+        return [list(r.output) for r in reqs], s
+
+    eager, _ = run(False)
+    pooled, s = run(True)
+    assert s.pool is not None and s.pool.replays > 0, "the decode passes did not use the captured steps"
+    assert pooled == eager
+    eng.model.ops.check_status()

@@ -23,6 +23,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import watchdog
+from ..utils.env import flag
 
 from ..config import ModelConfig
 from ..models.hybrid import HybridModel
@@ -51,6 +52,7 @@ class Engine:
         self.cfg: ModelConfig = model.cfg
         self.prefill_chunk = prefill_chunk
         self.pp = pp_comm
+        self._pool = None
         self.device = cache.device
         self.steps = 0
 
@@ -111,6 +113,20 @@ class Engine:
             items.append((seq.slot, pos, toks))
         batch = Batch.make(items, self.device, "decode")
         return self._run(batch)
+
+    def decode_pool(self):
+        """The engine's pool of captured per-width decode steps (GPU, single pipeline stage, VADE_DECODE_GRAPHS != 0),
+        created on first use and shared by every scheduler over this engine; None where it does not apply."""
+        if self.device.type != "cuda" or self.pp is not None or not flag("VADE_DECODE_GRAPHS", True):
+            return None
+        if self._pool is None:
+            from .graphs import GraphPool
+            try:
+                self._pool = GraphPool(self)
+            except Exception:                     # no free slot for the scratch sequence: stay eager
+                self._pool = None
+                return None
+        return self._pool
 
     def read_ints(self, t: torch.Tensor) -> list:
         """Device -> host read of a small integer tensor.  This is where the host blocks on the GPU, so the

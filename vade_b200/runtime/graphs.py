@@ -95,6 +95,71 @@ class DecodeGraph:
     def replay(self) -> None:
         self.graph.replay()
 
+    def set_rows(self, slots: list, tokens: list, positions: list) -> None:
+        """New rows for the next replay (same width): cache slot, token and position of each row."""
+        assert len(slots) == self.width
+        dev = self.engine.device
+        self.row_slot.copy_(torch.tensor(slots, dtype=torch.int32).pin_memory(), non_blocking=True)
+        self.tokens.copy_(torch.tensor(tokens, dtype=torch.int64).pin_memory(), non_blocking=True)
+        self.positions.copy_(torch.tensor(positions, dtype=torch.int32).pin_memory(), non_blocking=True)
+        self.slots = list(slots)
+
     def read_tokens(self) -> list:
         """The step's chosen tokens on the host (a deadline-guarded wait on the device)."""
         return self.engine.read_ints(self.tokens)
+
+
+class GraphPool:
+    """Captured decode steps of the serving loop, one per padded width (1, 2, 4, 8, 16 rows).
+
+    A decode pass of W chats replays the graph of the next width up; the padding rows decode token 0 at
+    position 0 of a scratch sequence that nothing reads.  Row contents (slot, token, position) are device
+    tensors that are rewritten before every replay, so one graph serves any set of chats of its width.
+    A row's arithmetic does not depend on the rows beside it, so padded, captured and eager passes give the
+    same bits (the determinism gate checks this through the scheduler).
+    Parity: engine/crates/engine/src/flash/next_pool.rs:304,345 (pooled rows replaying per-width graphs).
+    """
+
+    WIDTHS = (1, 2, 4, 8, 16)
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.max_len = engine.cache.max_pages * 64
+        self.graphs: dict = {}
+        self.scratch = engine.cache.new_slot()
+        engine.cache.ensure(self.scratch, 1)
+        self.replays = 0
+
+    def close(self) -> None:
+        self.graphs.clear()
+        self.engine.cache.free_slot(self.scratch)
+
+    def width_for(self, rows: int) -> int | None:
+        for w in self.WIDTHS:
+            if rows <= w:
+                return w
+        return None
+
+    def step(self, slots: list, tokens: list, positions: list):
+        """One decode step of len(slots) chats.  Returns (x, h, next greedy tokens) for the real rows, as views
+        of buffers that the next step overwrites (callers copy what they keep), or None if the pass is too wide."""
+        n = len(slots)
+        width = self.width_for(n)
+        if width is None:
+            return None
+        eng = self.engine
+        for s, p in zip(slots, positions):
+            eng.cache.ensure(s, p + 1)
+        pad = width - n
+        all_slots = list(slots) + [self.scratch] * pad
+        all_tokens = list(tokens) + [0] * pad
+        all_pos = list(positions) + [0] * pad
+        g = self.graphs.get(width)
+        if g is None:
+            g = DecodeGraph(eng, all_slots, self.max_len)
+            g.capture(all_tokens, all_pos)
+            self.graphs[width] = g
+        g.set_rows(all_slots, all_tokens, all_pos)
+        g.replay()
+        self.replays += 1
+        return g.x[:n], g.h[:n], g.tokens[:n]

@@ -43,6 +43,7 @@ class SchedulerConfig:
     request_timeout_s: float = 600.0
     draft_depth: int = 3                 # default MTP depth when a request asks for drafting
     max_queue: int = 256
+    decode_graphs: bool = True           # GPU: decode passes replay captured per-width steps (runtime/graphs.py GraphPool)
 
 
 @dataclass
@@ -142,6 +143,7 @@ class Scheduler:
         self.stop_flag = False
         self.ticks = 0
         self.fatal: str | None = None
+        self.pool = engine.decode_pool() if self.cfg.decode_graphs else None
 
     # ------------------------------------------------------------------ client side (any thread)
     def submit(self, req: Request) -> Request:
@@ -326,10 +328,20 @@ class Scheduler:
         if solo_draft:
             self._draft_cycle(rows_of[0])
             return True
-        x, h = eng.step([r.seq for r in rows_of], [[r.next_token] for r in rows_of])
+        pooled = None
+        if self.pool is not None:
+            # captured step of the padded width: no per-kernel launch cost on the host
+            pooled = self.pool.step([r.seq.slot for r in rows_of], [r.next_token for r in rows_of], [len(r.seq.tokens) for r in rows_of])
         greedy = None
-        if all(r.sampling.plain_greedy for r in rows_of):
-            greedy = [int(t) for t in eng.model.greedy(h)]
+        if pooled is not None:
+            x, h, nxt = pooled
+            if all(r.sampling.plain_greedy for r in rows_of):
+                greedy = eng.read_ints(nxt)
+            x = x.clone()
+        else:
+            x, h = eng.step([r.seq for r in rows_of], [[r.next_token] for r in rows_of])
+            if all(r.sampling.plain_greedy for r in rows_of):
+                greedy = eng.read_ints(eng.model.greedy(h))
         for i, r in enumerate(rows_of):
             r.seq.tokens.append(r.next_token)
             eng.cache.length[r.seq.slot] = len(r.seq.tokens)
