@@ -7,9 +7,15 @@
 // MMA, commit, TMEM read-back) is pure latency.  This kernel is a register dataflow instead:
 //   global -> registers   every thread issues ALL of its 32-bit weight words for up to 8 K blocks up
 //                         front (before it waits for the previous kernel: weights are immutable);
-//   registers -> bf16     e2m1 pairs expand to bf16x2 and take their e4m3 block scale exactly
-//                         (cvt.rn.f16x2.e2m1x2, a bit shift, mul.rn.bf16x2);
-//   bf16 -> fp32          warp-level mma (m16n8k16, fp32 accumulate); no barrier in the main loop.
+//   registers -> f16      e2m1 pairs expand to f16x2 and take their e4m3 block scale, both exactly
+//                         (cvt.rn.f16x2.e2m1x2, cvt.rn.f16x2.e4m3x2, mul.rn.f16x2: the product has at most
+//                         6 significant bits and lies in 2^-10 .. 2688): three instructions per pair;
+//   f16 -> fp32           warp-level mma (m16n8k16, f16 operands, fp32 accumulate); no barrier in the main loop.
+// Token rows are staged as f16 too: x * 2^s with one power of two per (row, staged K chunk), chosen so that
+// the chunk's largest magnitude lands in [2^13, 2^14); bf16 -> f16 is then exact for every element within
+// 2^27 of that maximum (f16 carries more significand bits than bf16), smaller ones lose low bits or vanish,
+// far below one fp32 ulp of the chunk's leading products.  The chunk's sum is multiplied by 2^-s (exact)
+// when it is added to the row's total.  This is the decode class's arithmetic for packed weights.
 // The 16 K slots of one mma are a fixed permutation of 16 columns (the same permutation is applied to
 // the token operand), chosen so that a thread's four A registers of two consecutive mmas are the four
 // bytes of ONE 32-bit word of the packed row: thread (g, t) owns columns 8t..8t+7 of each 32-column half.
@@ -31,8 +37,7 @@ constexpr int kRowsThreads = 128;
 constexpr int kChunk = 8;                                  // K blocks kept in flight per thread
 constexpr int kXStride = kChunk * 128 + 64;                // bytes per staged token row (odd multiple of 64: conflict-free 16-byte reads)
 
-// Four bytes (eight e2m1 values, low nibble first) -> four bf16x2 of value * scale, where `mult` holds
-// bf16(scale * 2^112) in both halves: f16 bits >> 3 read as bf16 equal value * 2^-112 (exact).
+// Four bytes (eight e2m1 values, low nibble first) -> four f16x2 of value * scale (exact), `mult` = f16x2(scale, scale).
 __device__ __forceinline__ void expand_word(uint32_t word, uint32_t mult, uint32_t* out) {
     uint32_t h[4];
     asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
@@ -40,32 +45,20 @@ __device__ __forceinline__ void expand_word(uint32_t word, uint32_t mult, uint32
         "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
         : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        const uint32_t p = ((h[b] >> 3) & 0x0FFF0FFFu) | (h[b] & 0x80008000u);
-        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(out[b]) : "r"(p), "r"(mult));
-    }
+    for (int b = 0; b < 4; ++b) asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[b]) : "r"(h[b]), "r"(mult));
 }
 
-// bf16x2 multiplier (scale * 2^112 in both halves) of one unsigned e4m3 scale byte.  Normal codes are a
-// shift and an add of the exponent bias difference; the eight subnormal codes (m * 2^-9) take the slow way.
-__device__ __forceinline__ uint32_t scale_mult(uint32_t byte) {
-    uint32_t b;
-    if (byte >= 8u) {
-        b = (byte << 4) + ((112u + 127u - 7u) << 7);
-    } else {
-        b = __float_as_uint(static_cast<float>(byte) * 0x1p103f) >> 16;      // m * 2^-9 * 2^112, exact
-    }
-    return b * 0x10001u;
-}
-
-// Scale bytes `b` and `b + 2` of a row's four e4m3 block scales -> two bf16x2 multipliers.
+// Scale bytes `b` and `b + 2` of a row's four e4m3 block scales -> two f16x2 multipliers (scale in both halves).
 __device__ __forceinline__ void scale_mults(uint32_t scales, int b, uint32_t* m_half0, uint32_t* m_half1) {
-    *m_half0 = scale_mult((scales >> (8 * b)) & 0x7Fu);
-    *m_half1 = scale_mult((scales >> (8 * b + 16)) & 0x7Fu);
+    const uint32_t pair = __byte_perm(scales, 0u, static_cast<uint32_t>(b | ((b + 2) << 4)) | 0x4400u);
+    uint32_t h01;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(static_cast<uint16_t>(pair & 0xFFFFu)));
+    *m_half0 = __byte_perm(h01, 0u, 0x1010u);
+    *m_half1 = __byte_perm(h01, 0u, 0x3232u);
 }
 
-__device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+__device__ __forceinline__ void mma_f16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -81,7 +74,9 @@ __global__ void __launch_bounds__(kRowsThreads, NT > 2 ? 3 : XP ? 4 : 6)
 rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ xparts,
                 long long xpart_stride, int x_nparts) {
     chain_release();
-    extern __shared__ __align__(16) uint8_t xs[];          // [NT * 8 token rows][kXStride]
+    extern __shared__ __align__(16) uint8_t xs[];          // [NT * 8 token rows][kXStride], then per row: max bits, 2^-s
+    uint32_t* row_max = reinterpret_cast<uint32_t*>(xs + NT * 8 * kXStride);
+    float* row_inv = reinterpret_cast<float*>(row_max + NT * 8);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2;
@@ -107,9 +102,12 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
         orow0 = row0;
     }
 
-    float acc[NT][4];
+    float acc[NT][4], tot[NT][4];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    for (int n = 0; n < NT; ++n) {
+        acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        tot[n][0] = tot[n][1] = tot[n][2] = tot[n][3] = 0.f;
+    }
 
     if (active) {
         const uint8_t* wb = a.w_tiles + static_cast<long long>(expert) * a.w_expert_stride
@@ -134,6 +132,8 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                 waited = true;
             }
             if (c0 > 0) __syncthreads();                   // the previous chunk's token columns are no longer read
+            if (threadIdx.x < NT * 8) row_max[threadIdx.x] = 0u;
+            __syncthreads();
             const int pieces = nc * 8;                     // 16-byte pieces per staged token row
             for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRowsThreads) {
                 const int j = p / pieces;
@@ -164,6 +164,32 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                     }
                 }
                 *reinterpret_cast<uint4*>(xs + j * kXStride + q * 16) = v;
+                // largest magnitude of the piece (bf16 bits compare like the values once the signs are cleared)
+                const uint32_t a0 = v.x & 0x7FFF7FFFu, a1 = v.y & 0x7FFF7FFFu, a2 = v.z & 0x7FFF7FFFu, a3 = v.w & 0x7FFF7FFFu;
+                uint32_t mx = max(max(a0 & 0xFFFFu, a0 >> 16), max(a1 & 0xFFFFu, a1 >> 16));
+                mx = max(mx, max(max(a2 & 0xFFFFu, a2 >> 16), max(a3 & 0xFFFFu, a3 >> 16)));
+                if (mx != 0u) atomicMax(&row_max[j], mx);          // integer maximum: the result does not depend on the order
+            }
+            __syncthreads();
+            // second pass: bf16 -> f16 of x * 2^s, s = 13 - exponent of the row's maximum (clamped), in place
+            for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRowsThreads) {
+                const int j = p / pieces;
+                const int q = p - j * pieces;
+                const int e = static_cast<int>(row_max[j] >> 7) - 127;             // floor(log2(max)) of a normal bf16
+                const int sh = row_max[j] == 0u ? 0 : min(100, max(-100, 13 - e));
+                const float up = __uint_as_float(static_cast<uint32_t>(sh + 127) << 23);
+                uint4* cell = reinterpret_cast<uint4*>(xs + j * kXStride + q * 16);
+                const uint4 v = *cell;
+                const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float lo = __uint_as_float(in[u] << 16) * up, hi = __uint_as_float(in[u] & 0xFFFF0000u) * up;
+                    const __half2 hh = __floats2half2_rn(lo, hi);
+                    o[u] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                *cell = make_uint4(o[0], o[1], o[2], o[3]);
+                if (q == 0) row_inv[j] = __uint_as_float(static_cast<uint32_t>(127 - sh) << 23);
             }
             __syncthreads();
 #pragma unroll
@@ -181,11 +207,19 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
                             const uint4 bx = *reinterpret_cast<const uint4*>(xs + (n * 8 + g) * kXStride + i * 128 + h * 64 + t * 16);
-                            mma_bf16(acc[n], A0[0], A1[0], A0[1], A1[1], bx.x, bx.y);
-                            mma_bf16(acc[n], A0[2], A1[2], A0[3], A1[3], bx.z, bx.w);
+                            mma_f16(acc[n], A0[0], A1[0], A0[1], A1[1], bx.x, bx.y);
+                            mma_f16(acc[n], A0[2], A1[2], A0[3], A1[3], bx.z, bx.w);
                         }
                     }
                 }
+            }
+            // the chunk's sums leave the scaled domain (2^-s is exact) and join the row totals
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const float i0 = row_inv[n * 8 + 2 * t], i1 = row_inv[n * 8 + 2 * t + 1];
+                tot[n][0] += acc[n][0] * i0; tot[n][1] += acc[n][1] * i1;
+                tot[n][2] += acc[n][2] * i0; tot[n][3] += acc[n][3] * i1;
+                acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
             }
         }
 
@@ -203,7 +237,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                 for (int e = 0; e < 2; ++e) {
                     const int j = n * 8 + 2 * t + e;
                     if (j >= nrows) continue;
-                    const float y = acc[n][2 * r + e] * rs;
+                    const float y = tot[n][2 * r + e] * rs;
                     const long long tok = orow0 + j;
                     if (a.px.n == 0) {
                         if (EPI == 0) reinterpret_cast<__nv_bfloat16*>(a.out)[tok * a.ldo + m] = __float2bfloat16_rn(y);
@@ -232,7 +266,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
 
 template <int NT, int EPI, bool XP>
 static const char* launch_rows(const GemmArgs& h, const GemmDev& d, dim3 grid, cudaStream_t stream) {
-    constexpr int smem = NT * 8 * kXStride;
+    constexpr int smem = NT * 8 * kXStride + NT * 8 * 8;
     static bool configured = false;
     auto kern = rows_mma_kernel<NT, EPI, XP>;
     if (!configured) {
