@@ -174,7 +174,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const uint4 q = *reinterpret_cast<const uint4*>(raw + half * 2048 + t * 16);
                 const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 4096 + t * 4);
                 if (!mbar_wait(&empty[s], ph ^ 1)) { fail(7); break; }   // the MMAs of the stage's previous use are done
-                // two e4m3 block scales -> bf16x2 multipliers (scale * 2^112)
+                // two e4m3 block scales -> bf16x2 multipliers (scale * 2^112).  The A tile stays bf16: tcgen05.mma kind::f16
+                // with an f16 A and a bf16 B operand (cheaper to produce, still exact) is an illegal instruction on sm_100a
                 uint32_t mult[2];
                 {
                     uint32_t h01;
