@@ -24,7 +24,7 @@ import sys
 import tempfile
 import time
 
-BASELINE_TOK_S = {1: 27.9, 2: 36.1, 4: 41.8, 8: 41.8}      # published plain decode, 1/2/4 Sparks
+BASELINE_TOK_S = {1: 27.9, 2: 36.1, 4: 41.8, 8: 41.8}      # the reference's published plain decode rates on 1 / 2 / 4 DGX Sparks
 BASELINE_TTFT_S = {1: 3.773, 2: 2.119, 4: 1.933, 8: 1.933}
 
 
