@@ -1,0 +1,78 @@
+"""Scheduler policy on the tiny CPU model: queueing when slots run out, backfill, queue limit, context limit,
+cancellation of queued and running requests, and that a crowded server still gives every chat its solo ids."""
+import pytest
+import torch
+
+from vade_b200.config import tiny_config
+from vade_b200.runtime.build import build_engine
+from vade_b200.runtime.scheduler import Request, Scheduler, SchedulerConfig
+
+
+def _ids(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 4000, (n,), generator=g).tolist()
+
+
+def _drain(s, reqs, hook=None, limit=100000):
+    steps = 0
+    while any(r.state != "done" for r in reqs):
+        if hook:
+            hook(steps)
+        if not s.tick():
+            s._reap()
+        steps += 1
+        assert steps < limit, "the scheduler made no progress"
+
+
+@pytest.fixture(scope="module")
+def engine():
+    return build_engine(tiny_config(), device="cpu", seed=0, slots=3, max_seq=256, prefill_chunk=64)
+
+
+def test_more_requests_than_slots_queue_and_every_chat_keeps_its_solo_ids(engine):
+    prompts = [_ids(30 + 7 * i, 40 + i) for i in range(6)]
+    solo = []
+    for p in prompts:
+        s = Scheduler(engine, SchedulerConfig(reserve_foreground=0))
+        r = s.submit(Request(prompt=p, max_tokens=6, ignore_eos=True))
+        _drain(s, [r])
+        solo.append(list(r.output))
+    s = Scheduler(engine, SchedulerConfig(reserve_foreground=0, max_active=3))
+    reqs = [s.submit(Request(prompt=p, max_tokens=6, ignore_eos=True)) for p in prompts]
+    s.tick()
+    assert sum(r.state != "queued" for r in reqs) <= 3, "more chats were started than there are slots"
+    _drain(s, reqs)
+    assert [list(r.output) for r in reqs] == solo
+    assert all(r.finish_reason == "length" for r in reqs)
+    assert len(engine.cache.free_slots) == 3, "a finished chat did not give its slot back"
+
+
+def test_queue_limit_context_limit_and_empty_prompt_are_refused(engine):
+    s = Scheduler(engine, SchedulerConfig(max_queue=2))
+    s.submit(Request(prompt=_ids(10, 1), max_tokens=2))
+    s.submit(Request(prompt=_ids(10, 2), max_tokens=2))
+    with pytest.raises(OverflowError):
+        s.submit(Request(prompt=_ids(10, 3), max_tokens=2))
+    s2 = Scheduler(engine, SchedulerConfig())
+    with pytest.raises(ValueError):
+        s2.submit(Request(prompt=_ids(250, 4), max_tokens=100))            # beyond the 256-token context
+    with pytest.raises(ValueError):
+        s2.submit(Request(prompt=[], max_tokens=4))
+    _drain(s, list(s.queue) + list(s.active))
+
+
+def test_cancel_a_queued_and_a_running_request(engine):
+    s = Scheduler(engine, SchedulerConfig(reserve_foreground=0, max_active=1))
+    a = s.submit(Request(prompt=_ids(40, 5), max_tokens=30, ignore_eos=True))
+    b = s.submit(Request(prompt=_ids(40, 6), max_tokens=5, ignore_eos=True))
+    c = s.submit(Request(prompt=_ids(40, 7), max_tokens=5, ignore_eos=True))
+    assert s.cancel(b.id)                                                # still queued
+
+    def hook(step):
+        if step == 6:
+            s.cancel(a.id)                                               # running: stops between passes
+    _drain(s, [a, b, c], hook=hook)
+    assert a.finish_reason == "cancelled" and len(a.output) < 30
+    assert b.finish_reason == "cancelled" and b.output == []
+    assert c.finish_reason == "length" and len(c.output) == 5
+    assert len(engine.cache.free_slots) == 3

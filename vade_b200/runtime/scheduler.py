@@ -213,6 +213,7 @@ class Scheduler:
                 if r.cancelled:
                     self.queue.remove(r)
                     r.finish_reason = "cancelled"
+                    r.state = "done"
                     r.push(("done", "cancelled"))
 
     # ---- 2. admission
