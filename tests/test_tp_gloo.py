@@ -82,3 +82,41 @@ def test_tp4_with_replicated_kv_heads_matches_single():
     ref = _single(n_new=12)
     outs = _launch(4, 1, n_new=12)
     assert all(o == ref for o in outs.values())
+
+
+def _fp8_worker(rank, world, port, q):
+    import os
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vade_b200.config import QuantConfig
+    from vade_b200.parallel.groups import make_parallel
+    cfg = tiny_config()
+    cfg.quant = QuantConfig("fp8_block", 128, list(cfg.quant.ignore))
+    par = make_parallel(tp=world, pp=1)
+    eng = build_engine(cfg, seed=0, tp=world, tp_rank=par.tp_rank, comm=par.comm, max_seq=512)
+    kinds = {m.kind for m in eng.model.w.all_linears() if m is not None}
+    q.put((rank, eng.generate(_prompt(), 10).generated, sorted(kinds)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fp8_block_checkpoint_under_tp2_matches_single():
+    """Block-scaled FP8 storage (W8A8 oracle arithmetic) sharded over two ranks: rows and 128-column K blocks keep
+    their scales, activation groups never straddle ranks, ids equal the unsharded run."""
+    import torch.multiprocessing as mp
+    from vade_b200.config import QuantConfig
+    cfg = tiny_config()
+    cfg.quant = QuantConfig("fp8_block", 128, list(cfg.quant.ignore))
+    ref = build_engine(cfg, seed=0, max_seq=512).generate(_prompt(), 10).generated
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fp8_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    outs = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(60)
+    for rank, toks, kinds in outs:
+        assert "fp8" in kinds, kinds
+        assert toks == ref, f"rank {rank}: FP8 tokens differ under TP2"
