@@ -286,3 +286,25 @@ def test_large_tensors_go_through_the_native_reader(tmp_path):
     f = st.TensorFile(path)
     assert torch.equal(f.read_range("big", 100, 2900), t["big"][100:2900])
     assert torch.equal(f.read("small"), t["small"])
+
+
+def test_chat_templates_follow_the_tokenizers_markers():
+    from types import SimpleNamespace
+    from vade_b200.serve.tokenizer import TokenizerError, chat_family, render_chat
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"},
+            {"role": "assistant", "content": "hello"}, {"role": "user", "content": [{"type": "text", "text": "bye"}]}]
+    mk = lambda names: SimpleNamespace(special={n: i for i, n in enumerate(names)})
+    llama = mk(["<|begin_of_text|>", "<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"])
+    assert chat_family(llama) == "llama3"
+    assert render_chat(msgs, llama).endswith("<|start_header_id|>user<|end_header_id|>\n\nbye<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n")
+    gemma = mk(["<bos>", "<start_of_turn>", "<end_of_turn>"])
+    text = render_chat(msgs, gemma)
+    assert text.startswith("<bos><start_of_turn>user\nbe brief\n\nhi<end_of_turn>\n<start_of_turn>model\nhello<end_of_turn>\n") and text.endswith("<start_of_turn>model\n")
+    phi = mk(["<|system|>", "<|user|>", "<|assistant|>", "<|end|>"])
+    assert render_chat(msgs, phi) == "<|system|>\nbe brief<|end|>\n<|user|>\nhi<|end|>\n<|assistant|>\nhello<|end|>\n<|user|>\nbye<|end|>\n<|assistant|>\n"
+    with pytest.raises(TokenizerError):
+        render_chat(msgs, mk([]))                                           # no markers: refuse, never guess
+    with pytest.raises(TokenizerError):
+        render_chat(msgs, llama, tools=[{"name": "f"}])                      # tools are a ChatML feature here
+    with pytest.raises(TokenizerError):
+        render_chat([{"role": "wizard", "content": "x"}], gemma)

@@ -184,11 +184,87 @@ class StreamDecoder:
 ROLES = ("system", "user", "assistant", "tool")
 
 
+def _text_of(m: dict) -> str:
+    """The text of one message; refuses non-text content parts."""
+    content = m.get("content")
+    if isinstance(content, list):
+        texts = []
+        for part in content:
+            if not isinstance(part, dict) or part.get("type") not in ("text", "input_text", "output_text"):
+                raise TokenizerError("only text content parts are supported")
+            texts.append(part.get("text", ""))
+        content = "".join(texts)
+    if content is None:
+        content = ""
+    if not isinstance(content, str):
+        raise TokenizerError("message content must be text")
+    return content
+
+
+def chat_family(tok) -> str:
+    """Which hand-coded template a tokenizer's special tokens call for (the family is never guessed from a name):
+    chatml (Qwen, hybrid), llama3, gemma, phi.  Parity: engine/crates/tokenizer/src/chat.rs, templates/*.jinja."""
+    sp = tok.special
+    if "<|im_start|>" in sp and "<|im_end|>" in sp:
+        return "chatml"
+    if "<|start_header_id|>" in sp and "<|eot_id|>" in sp:
+        return "llama3"
+    if "<start_of_turn>" in sp and "<end_of_turn>" in sp:
+        return "gemma"
+    if "<|user|>" in sp and "<|assistant|>" in sp and "<|end|>" in sp:
+        return "phi"
+    raise TokenizerError("the checkpoint's tokenizer has no known chat markers; refusing to guess a chat template")
+
+
+def _render_other(family: str, messages: list, tok, add_generation_prompt: bool) -> str:
+    out = []
+    if family == "llama3":
+        out.append("<|begin_of_text|>" if "<|begin_of_text|>" in tok.special else "")
+        for m in messages:
+            role = m.get("role")
+            if role not in ROLES:
+                raise TokenizerError(f"unknown chat role {role!r}")
+            out.append(f"<|start_header_id|>{'ipython' if role == 'tool' else role}<|end_header_id|>\n\n{_text_of(m).strip()}<|eot_id|>")
+        if add_generation_prompt:
+            out.append("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    elif family == "gemma":
+        out.append("<bos>" if "<bos>" in tok.special else "")
+        system = ""
+        for m in messages:
+            role = m.get("role")
+            if role not in ROLES:
+                raise TokenizerError(f"unknown chat role {role!r}")
+            text = _text_of(m).strip()
+            if role == "system":                         # Gemma has no system turn: the text leads the next user turn
+                system = text + "\n\n"
+                continue
+            who = "model" if role == "assistant" else "user"
+            out.append(f"<start_of_turn>{who}\n{system if who == 'user' else ''}{text}<end_of_turn>\n")
+            if who == "user":
+                system = ""
+        if add_generation_prompt:
+            out.append("<start_of_turn>model\n")
+    else:                                                # phi
+        for m in messages:
+            role = m.get("role")
+            if role not in ROLES:
+                raise TokenizerError(f"unknown chat role {role!r}")
+            tag = {"system": "<|system|>", "user": "<|user|>", "assistant": "<|assistant|>", "tool": "<|user|>"}[role]
+            out.append(f"{tag}\n{_text_of(m)}<|end|>\n")
+        if add_generation_prompt:
+            out.append("<|assistant|>\n")
+    return "".join(out)
+
+
 def render_chat(messages: list, tok, add_generation_prompt: bool = True, enable_thinking: bool = False, tools: list | None = None) -> str:
-    """ChatML rendering; refuses (fails closed) when the tokenizer lacks the ChatML markers or a
-    message has an unknown role or non-text content."""
-    if "<|im_start|>" not in tok.special or "<|im_end|>" not in tok.special:
-        raise TokenizerError("the checkpoint's tokenizer has no ChatML markers; refusing to guess a chat template")
+    """Chat rendering with the template the tokenizer's markers select (ChatML for the Qwen / hybrid family, Llama-3,
+    Gemma, Phi); refuses (fails closed) when no known markers exist or a message has an unknown role or non-text
+    content.  Tool declarations and tool calls are rendered for ChatML only."""
+    family = chat_family(tok)
+    if family != "chatml":
+        if tools:
+            raise TokenizerError(f"tool declarations are not supported with the {family} template")
+        return _render_other(family, messages, tok, add_generation_prompt)
     out = []
     if tools:
         decl = "\n".join(json.dumps(t, separators=(",", ":"), sort_keys=True) for t in tools)
