@@ -308,3 +308,19 @@ def test_chat_templates_follow_the_tokenizers_markers():
         render_chat(msgs, llama, tools=[{"name": "f"}])                      # tools are a ChatML feature here
     with pytest.raises(TokenizerError):
         render_chat([{"role": "wizard", "content": "x"}], gemma)
+
+
+def test_published_qwen3_next_config_json_parses_to_the_builtin_80b_configuration():
+    from vade_b200.config import ModelConfig, qwen3_next_80b_config
+    hf = {"architectures": ["Qwen3NextForCausalLM"], "model_type": "qwen3_next", "attention_bias": False, "decoder_sparse_step": 1,
+          "full_attention_interval": 4, "head_dim": 256, "hidden_act": "silu", "hidden_size": 2048, "intermediate_size": 5120,
+          "linear_conv_kernel_dim": 4, "linear_key_head_dim": 128, "linear_num_key_heads": 16, "linear_num_value_heads": 32,
+          "linear_value_head_dim": 128, "max_position_embeddings": 262144, "mlp_only_layers": [], "moe_intermediate_size": 512,
+          "norm_topk_prob": True, "num_attention_heads": 16, "num_experts": 512, "num_experts_per_tok": 10, "num_hidden_layers": 48,
+          "num_key_value_heads": 2, "partial_rotary_factor": 0.25, "rms_norm_eps": 1e-06, "rope_scaling": None, "rope_theta": 10000000,
+          "shared_expert_intermediate_size": 512, "tie_word_embeddings": False, "torch_dtype": "bfloat16", "vocab_size": 151936}
+    c = ModelConfig.from_json(hf)
+    c.validate()
+    r = qwen3_next_80b_config("none")
+    assert {k for k in c.__dataclass_fields__ if getattr(c, k) != getattr(r, k)} == set()
+    assert c.rotary_dim == 64 and [c.is_attention_layer(i) for i in range(4)] == [False, False, False, True]
