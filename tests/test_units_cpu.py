@@ -324,3 +324,26 @@ def test_published_qwen3_next_config_json_parses_to_the_builtin_80b_configuratio
     r = qwen3_next_80b_config("none")
     assert {k for k in c.__dataclass_fields__ if getattr(c, k) != getattr(r, k)} == set()
     assert c.rotary_dim == 64 and [c.is_attention_layer(i) for i in range(4)] == [False, False, False, True]
+
+
+def test_memory_budget_follows_the_shard_plan():
+    from vade_b200.config import hybrid_200b_config, qwen3_next_80b_config
+    from vade_b200.parallel.budget import layout_budget, rank_weight_bytes
+    from vade_b200.parallel.plan import make_plan
+    cfg = qwen3_next_80b_config("nvfp4")
+    one = rank_weight_bytes(cfg, make_plan(cfg), with_mtp=False)
+    four = [rank_weight_bytes(cfg, make_plan(cfg, 4, r), with_mtp=False) for r in range(4)]
+    routed = lambda w: w["experts"] - 48 * 3 * 512 * 2048 * 0.5625                     # without the replicated shared expert
+    assert abs(sum(routed(w) for w in four) - routed(one)) < 1e-3 * routed(one)        # whole experts: a partition
+    assert all(w["router"] == one["router"] and w["embed"] == one["embed"] for w in four)
+    assert sum(w["head"] for w in four) == one["head"]
+    assert sum(w["gdn"] for w in four) == pytest.approx(one["gdn"])                      # GDN heads divide evenly
+    assert sum(w["attention"] for w in four) > one["attention"]                         # 2 KV heads on 4 ranks: replicated
+    stages = [rank_weight_bytes(cfg, make_plan(cfg, 1, 0, 8, s), with_mtp=False) for s in range(8)]
+    assert sum(w["experts"] for w in stages) == pytest.approx(one["experts"])
+    assert stages[0]["embed"] > 0 and stages[0]["head"] == 0 and stages[7]["head"] > 0 and stages[3]["embed"] == 0
+    assert 40e9 < one["total"] < 50e9                                                   # the 80B model in NVFP4
+    assert layout_budget(cfg, 1, 1, 8192)["fits"]
+    big = hybrid_200b_config("nvfp4")
+    assert layout_budget(big, 4, 2, 32768)["fits"] and layout_budget(big, 4, 2, 32768)["sequences"] > 100
+    assert not layout_budget(hybrid_200b_config("none"), 1, 1, 32768)["fits"]           # bf16 on one GPU does not

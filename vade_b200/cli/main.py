@@ -232,6 +232,16 @@ def cmd_test(a) -> int:
     return 0 if run_gate(eng, tokens=a.tokens, graph=on_gpu) else 1
 
 
+def cmd_plan(a) -> int:
+    """Per-rank memory budget of a layout (weights, KV per token, state per sequence, sequences that fit)."""
+    from ..config import NAMED_CONFIGS
+    from ..parallel.budget import layout_budget
+    cfg = NAMED_CONFIGS[a.config](a.quant) if a.config in ("qwen3-next-80b-a3b", "hybrid-200b") else NAMED_CONFIGS[a.config]()
+    b = layout_budget(cfg, a.tp, a.pp, a.context, hbm=int(a.hbm_gb * 1e9))
+    print(json.dumps(b, indent=1))
+    return 0 if b["fits"] else 1
+
+
 def cmd_doctor(a) -> int:
     import torch
     rep = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available()}
@@ -283,6 +293,9 @@ def main(argv=None) -> int:
     p.add_argument("--cohorts", type=int, nargs="*", default=[1, 4, 8]); p.add_argument("--cohort-tokens", type=int, default=256)
     p.add_argument("--draft", default="plain"); p.add_argument("--api-key", default=None); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("plan"); p.add_argument("--config", default="qwen3-next-80b-a3b"); p.add_argument("--quant", default="nvfp4")
+    p.add_argument("--tp", type=int, default=1); p.add_argument("--pp", type=int, default=1); p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--hbm-gb", type=float, default=180.0); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("test"); p.add_argument("what", choices=["determinism"]); p.add_argument("--config", default="tiny")
     p.add_argument("--device", default="cpu"); p.add_argument("--tokens", type=int, default=24); p.add_argument("--seed", type=int, default=0)
     p.set_defaults(fn=cmd_test)

@@ -1,0 +1,73 @@
+"""Per-rank memory budget of a layout: resident weight bytes, KV bytes per token, recurrent-state bytes per
+sequence, and how many sequences / context tokens fit beside the weights in one GPU's memory.
+
+Everything is computed from the configuration and the shard plan alone (no checkpoint, no GPU): the same
+ownership rules as the loader (heads, whole experts, vocabulary rows, layer intervals), storage bytes per weight
+of the quantisation class, and the cache geometry of runtime/cache.py.  ``python -m vade_b200.cli.main plan``
+prints it for every rank of a layout.  Parity: the reference's ownership and cache-byte calculators
+(engine/crates/model/src/flash/shard.rs:303-349 ``cache_bytes``, model/src/split/mod.rs workspace reserves,
+tp/src/flash/next_batched_service.rs:150-162 cache room agreement).
+"""
+from __future__ import annotations
+
+from ..config import ModelConfig
+from .plan import ShardPlan, cache_bytes_per_token, make_plan, state_bytes_per_sequence
+
+HBM_BYTES = 180 * 10**9            # one B200
+
+
+def bytes_per_weight(cfg: ModelConfig) -> float:
+    m = cfg.quant.method
+    if m == "nvfp4":
+        return 0.5 + 1.0 / 16          # nibbles + one e4m3 scale per 16 columns (kernel tiles: 4608 B per 128 x 64)
+    if m == "fp8_block":
+        return 1.0 + 4.0 / 128         # e4m3 + one fp32 scale per row and 128 columns
+    return 2.0                         # bf16
+
+
+def rank_weight_bytes(cfg: ModelConfig, plan: ShardPlan, with_mtp: bool = True) -> dict:
+    """Bytes of the tensors this rank holds, by group."""
+    H, hd = cfg.hidden_size, cfg.head_dim
+    bw = bytes_per_weight(cfg)
+    nq = plan.q_heads[1] - plan.q_heads[0]
+    nkv = plan.kv_heads[1] - plan.kv_heads[0]
+    gk = plan.gdn_k_heads[1] - plan.gdn_k_heads[0]
+    gv = plan.gdn_v_heads[1] - plan.gdn_v_heads[0]
+    ne = plan.experts[1] - plan.experts[0]
+    nv = plan.vocab[1] - plan.vocab[0]
+    kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    I, Is = cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    attn = (2 * nq * hd + 2 * nkv * hd) * H + H * (nq * hd)                    # q + gate, k, v rows; o_proj columns of this rank
+    gdn = (2 * gk * kd + 2 * gv * vd + 2 * gv) * H + H * (gv * vd)              # q, k, v, z, beta, a rows; out_proj columns
+    moe = ne * 3 * I * H + 3 * Is * H                                          # routed experts held whole + replicated shared expert
+    router = (cfg.num_experts + (1 if Is else 0)) * H * 2                      # bf16, replicated
+    layers = range(*plan.layers)
+    n_attn = sum(1 for i in layers if cfg.is_attention_layer(i))
+    n_gdn = len(layers) - n_attn
+    out = {"attention": n_attn * attn * bw, "gdn": n_gdn * gdn * bw, "experts": len(layers) * moe * bw, "router": len(layers) * router,
+           "embed": cfg.vocab_size * H * 2 if plan.first_stage else 0, "head": nv * H * 2 if plan.last_stage else 0, "mtp": 0}
+    if with_mtp and plan.last_stage and cfg.mtp_num_hidden_layers > 0:
+        out["mtp"] = (attn + moe) * bw + router + 2 * H * H * bw + (0 if plan.first_stage else cfg.vocab_size * H * 2)
+    out["total"] = sum(out.values())
+    return out
+
+
+def rank_budget(cfg: ModelConfig, tp: int, tp_rank: int, pp: int, pp_rank: int, context: int, hbm: int = HBM_BYTES,
+                workspace: int = 8 * 10**9, with_mtp: bool = True) -> dict:
+    plan = make_plan(cfg, tp, tp_rank, pp, pp_rank)
+    w = rank_weight_bytes(cfg, plan, with_mtp)
+    kv_tok = cache_bytes_per_token(cfg, plan)
+    state = state_bytes_per_sequence(cfg, plan)
+    room = hbm - w["total"] - workspace
+    per_seq = state + kv_tok * context
+    return {"tp_rank": tp_rank, "pp_rank": pp_rank, "layers": list(plan.layers), "weights_gb": round(w["total"] / 1e9, 2),
+            "weights_by_group_gb": {k: round(v / 1e9, 3) for k, v in w.items() if k != "total"},
+            "kv_bytes_per_token": kv_tok, "state_bytes_per_sequence": state, "workspace_gb": workspace / 1e9,
+            "free_gb": round(room / 1e9, 2), "sequences_at_context": int(room // per_seq) if room > 0 and per_seq > 0 else 0,
+            "fits": room > per_seq}
+
+
+def layout_budget(cfg: ModelConfig, tp: int, pp: int, context: int, **kw) -> dict:
+    ranks = [rank_budget(cfg, tp, t, pp, s, context, **kw) for s in range(pp) for t in range(tp)]
+    return {"tp": tp, "pp": pp, "context": context, "quant": cfg.quant.method, "fits": all(r["fits"] for r in ranks),
+            "sequences": min(r["sequences_at_context"] for r in ranks), "ranks": ranks}
