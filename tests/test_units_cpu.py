@@ -347,3 +347,24 @@ def test_memory_budget_follows_the_shard_plan():
     big = hybrid_200b_config("nvfp4")
     assert layout_budget(big, 4, 2, 32768)["fits"] and layout_budget(big, 4, 2, 32768)["sequences"] > 100
     assert not layout_budget(hybrid_200b_config("none"), 1, 1, 32768)["fits"]           # bf16 on one GPU does not
+
+
+def test_adaptive_draft_depth_follows_acceptance_and_is_a_cost_decision_only():
+    from vade_b200.runtime.draft import DepthChooser
+    c = DepthChooser()
+    assert c.choose() >= 1                               # an optimistic start: try a shallow draft
+    for _ in range(30):
+        c.record(c.choose() or 1, 0)                     # every draft misses
+    assert c.choose() == 0                               # plain decoding wins
+    probes = [c.choose() for _ in range(40)]
+    assert 1 in probes and probes.count(0) > 30          # ... with an occasional shallow probe
+    c = DepthChooser()
+    for _ in range(40):
+        d = c.choose() or 1
+        c.record(d, d)                                   # every draft lands
+    assert c.choose() >= 5
+    c = DepthChooser()
+    for _ in range(60):
+        d = c.choose() or 1
+        c.record(d, min(d, 2))                           # the third drafted token always misses
+    assert c.choose() == 2

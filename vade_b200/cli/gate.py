@@ -128,11 +128,11 @@ def run_gate(engine, tokens: int = 24, prompt_len: int = 150, out=print, graph: 
     check(f"prefix cache ({r.cached_tokens} cached)", r.output, ref)
 
     if engine.model.w.mtp is not None:
-        for depth in (3, 7):
+        for depth in (3, 7, 0):                      # 0 = adaptive depth (runtime/draft.py)
             s = sched()
             r = one(s, draft="strict", mtp_depth=depth)
             _drain(s, [r])
-            check(f"draft {depth} ({r.accepted}/{r.drafted} kept)", r.output, ref)
+            check(f"draft {depth or 'auto'} ({r.accepted}/{r.drafted} kept)", r.output, ref)
 
     samp = dict(temperature=0.8, top_p=0.9, top_k=40, seed=1234)
     s = sched()

@@ -1,0 +1,81 @@
+"""Adaptive depth of exact speculative decoding.
+
+Drafting never changes tokens (the trunk verifies every drafted row itself), so the depth is a pure cost decision:
+a cycle of depth d costs ``d`` draft steps plus one verify pass of ``d + 1`` rows and emits ``1 + accepted`` tokens.
+``DepthChooser`` keeps, per request, a running per-position acceptance estimate and picks the depth that maximises
+expected tokens per unit cost under a linear cost model (measured at start-up or left at the defaults); depth 0
+(plain decoding) wins when drafts keep missing.  The choice depends only on the request's own history, so it
+cannot make one chat's ids depend on another chat.
+Parity: engine/crates/engine/src/draft.rs:117-140 (depth from cost curves and acceptance), draft_steps.rs (stop rule).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+MAX_DEPTH = 7
+
+
+@dataclass
+class CostModel:
+    """Costs in units of one plain decode step."""
+    draft_step: float = 0.12        # one MTP step: one layer + the shared head, against 48 layers + head
+    verify_base: float = 1.0        # a verify pass of one row is a plain step
+    verify_row: float = 0.03        # each further row of the pass (the step is latency-bound, rows are nearly free)
+    rollback: float = 1.0           # a rejected draft replays the kept rows from the snapshot
+
+
+@dataclass
+class DepthChooser:
+    cost: CostModel = field(default_factory=CostModel)
+    prior: float = 0.6              # acceptance assumed for positions not yet observed
+    decay: float = 0.9              # weight of the history against the newest cycle
+    tried: list = field(default_factory=lambda: [0.0] * MAX_DEPTH)
+    kept: list = field(default_factory=lambda: [0.0] * MAX_DEPTH)
+    probe_every: int = 16           # while plain decoding wins, one shallow draft every so many cycles keeps the estimate alive
+    idle: int = 0
+
+    def acceptance(self, pos: int) -> float:
+        """P(draft position pos is accepted | every earlier position was), from this request's cycles."""
+        n = self.tried[pos]
+        # a position with little history of its own leans on the one before it (a little more pessimistic), so the
+        # chooser explores deeper while shallow drafts keep landing and backs off as soon as they stop
+        prior = self.prior if pos == 0 else 0.9 * self.acceptance(pos - 1)
+        return (self.kept[pos] + prior) / (n + 1.0)
+
+    def expected(self, depth: int) -> tuple:
+        """(expected tokens, expected cost) of one cycle at ``depth``."""
+        tokens, reach, p_all = 1.0, 1.0, 1.0
+        for i in range(depth):
+            reach *= self.acceptance(i)
+            tokens += reach
+        p_all = reach
+        cost = depth * self.cost.draft_step + self.cost.verify_base + depth * self.cost.verify_row
+        if depth > 0:
+            cost += (1.0 - p_all) * self.cost.rollback
+        return tokens, cost
+
+    def choose(self, limit: int = MAX_DEPTH) -> int:
+        best, best_rate = 0, 1.0 / self.cost.verify_base
+        for d in range(1, max(0, min(limit, MAX_DEPTH)) + 1):
+            t, c = self.expected(d)
+            if t / c > best_rate + 1e-12:
+                best, best_rate = d, t / c
+        if best == 0 and limit >= 1:
+            self.idle += 1
+            if self.idle >= self.probe_every:
+                self.idle = 0
+                return 1
+        else:
+            self.idle = 0
+        return best
+
+    def record(self, depth: int, accepted: int) -> None:
+        """One finished cycle: ``accepted`` of ``depth`` drafted tokens were kept (a prefix)."""
+        for i in range(MAX_DEPTH):
+            self.tried[i] *= self.decay
+            self.kept[i] *= self.decay
+        for i in range(min(depth, MAX_DEPTH)):
+            if i <= accepted:                     # position i was reached (all earlier ones were accepted)
+                self.tried[i] += 1.0
+                if i < accepted:
+                    self.kept[i] += 1.0

@@ -30,6 +30,7 @@ import torch
 from ..utils import events
 from .cache import PAGE, OutOfPages
 from .engine import Engine, Sequence
+from .draft import MAX_DEPTH, DepthChooser
 from .sampler import Sampling, sample
 
 
@@ -78,6 +79,7 @@ class Request:
     cancelled: bool = False
     pages_reserved: int = 0
     text_tail: str = ""
+    chooser: DepthChooser = field(default_factory=DepthChooser)      # adaptive draft depth (runtime/draft.py)
 
     def push(self, ev) -> None:
         self.events.append(ev)
@@ -359,7 +361,10 @@ class Scheduler:
         eng = self.engine
         seq = r.seq
         remaining = r.max_tokens - len(r.output)
-        depth = max(0, min(r.mtp_depth or self.cfg.draft_depth, remaining - 1))
+        if r.mtp_depth:
+            depth = max(0, min(r.mtp_depth, remaining - 1))                      # the client fixed the depth
+        else:
+            depth = r.chooser.choose(max(0, min(MAX_DEPTH, remaining - 1)))       # adaptive: a cost decision, never a token decision
         drafts = eng.propose(seq, r.next_token, depth) if depth > 0 else []
         rows = [r.next_token] + drafts
         snap = eng.cache.snapshot(seq.slot) if drafts else None
@@ -378,6 +383,8 @@ class Scheduler:
         seq.last_x = x[keep - 1:keep].clone()
         r.drafted += len(drafts)
         r.accepted += keep - 1
+        if not r.mtp_depth and drafts:
+            r.chooser.record(len(drafts), keep - 1)
         for t in rows[1:keep]:
             if self._emit(r, t):
                 return
