@@ -76,3 +76,12 @@ def test_cancel_a_queued_and_a_running_request(engine):
     assert b.finish_reason == "cancelled" and b.output == []
     assert c.finish_reason == "length" and len(c.output) == 5
     assert len(engine.cache.free_slots) == 3
+
+
+def test_serving_load_benchmark_reproduces_solo_runs_on_the_tiny_model():
+    from vade_b200.cli.serve_bench import run
+    eng = build_engine(tiny_config(), device="cpu", seed=0, slots=6, max_seq=256, prefill_chunk=64)
+    lines = []
+    res = run(eng, 8, 20, 80, 8, 0.7, 0.95, 3, 4, out=lines.append)
+    assert res["incomplete"] == 0 and res["solo_identical"] == res["solo_checked"] == 3
+    assert res["output_tokens"] == 64 and res["ttft_p99_s"] >= res["ttft_p50_s"] > 0
