@@ -150,6 +150,41 @@ class Engine:
             return sample_compact(vals, ids, seq.sampling, position)
         return sample(logits[0], seq.sampling, position, seq.tokens if history is None else history)
 
+    def choose_many(self, seqs: list, h: torch.Tensor, positions: list) -> list:
+        """Tokens for several rows of one decode pass (row i belongs to seqs[i] at positions[i]) with ONE head product,
+        one compact top-k launch and one read-back for all sampled rows.  Each row's draw is the one ``choose`` makes for
+        it alone: the head product and the top-k are row-independent, and the sampler is keyed by (seed, position)."""
+        n = len(seqs)
+        if all(s.sampling.plain_greedy for s in seqs):
+            return self.read_ints(self.model.greedy(h))
+        logits = self.model.logits(h)                                     # [n, V], one pass over the head
+        ops = self.model.ops
+        out = [None] * n
+        compact = [i for i in range(n) if logits.is_cuda and hasattr(ops, "topk_logits") and not seqs[i].sampling.plain_greedy
+                   and compact_ok(seqs[i].sampling, logits.shape[1])]
+        if compact:
+            k = max(seqs[i].sampling.top_k for i in compact)
+            vals, ids = ops.topk_logits(logits[compact] if len(compact) < n else logits, k)
+            with watchdog.wait("top-k read-back"):
+                vals, ids = vals.cpu(), ids.cpu()
+            for j, i in enumerate(compact):
+                kk = seqs[i].sampling.top_k                               # a prefix of the canonical order is the smaller top-k
+                out[i] = sample_compact(vals[j, :kk], ids[j, :kk], seqs[i].sampling, positions[i])
+        rest = [i for i in range(n) if out[i] is None]
+        if rest:
+            greedy_rows = [i for i in rest if seqs[i].sampling.plain_greedy]
+            if greedy_rows:
+                toks = self.read_ints(self.model.greedy(h[greedy_rows]))
+                for i, t in zip(greedy_rows, toks):
+                    out[i] = t
+            full = [i for i in rest if out[i] is None]
+            if full:
+                with watchdog.wait("logits read-back"):
+                    rows = logits[full].float().cpu()
+                for j, i in enumerate(full):
+                    out[i] = sample(rows[j], seqs[i].sampling, positions[i], seqs[i].tokens)
+        return out
+
     # ------------------------------------------------------------------ MTP
     def propose(self, seq: Sequence, first: int, depth: int) -> list:
         """Draft ``depth`` tokens after ``first`` (the already chosen next token) with the MTP block.

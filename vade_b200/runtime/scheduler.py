@@ -335,24 +335,22 @@ class Scheduler:
         if self.pool is not None:
             # captured step of the padded width: no per-kernel launch cost on the host
             pooled = self.pool.step([r.seq.slot for r in rows_of], [r.next_token for r in rows_of], [len(r.seq.tokens) for r in rows_of])
-        greedy = None
         if pooled is not None:
             x, h, nxt = pooled
-            if all(r.sampling.plain_greedy for r in rows_of):
-                greedy = eng.read_ints(nxt)
             x = x.clone()
+            chosen = eng.read_ints(nxt) if all(r.sampling.plain_greedy for r in rows_of) else None
         else:
             x, h = eng.step([r.seq for r in rows_of], [[r.next_token] for r in rows_of])
-            if all(r.sampling.plain_greedy for r in rows_of):
-                greedy = eng.read_ints(eng.model.greedy(h))
-        for i, r in enumerate(rows_of):
+            chosen = None
+        for r in rows_of:
             r.seq.tokens.append(r.next_token)
             eng.cache.length[r.seq.slot] = len(r.seq.tokens)
+        if chosen is None:
+            # one head product, one top-k launch and one read-back for the whole pass (greedy, compact and full-row rows)
+            chosen = eng.choose_many([r.seq for r in rows_of], h, [len(r.seq.tokens) for r in rows_of])
+        for i, r in enumerate(rows_of):
             r.seq.last_x = x[i:i + 1]
-            if greedy is not None:
-                r.next_token = greedy[i]
-            else:
-                r.next_token = eng.choose(r.seq, h[i:i + 1], len(r.seq.tokens))
+            r.next_token = chosen[i]
         return True
 
     def _draft_cycle(self, r: Request) -> None:
