@@ -129,3 +129,26 @@ def test_scheduler_replays_captured_steps_and_matches_eager():
     assert s.pool is not None and s.pool.replays > 0, "the decode passes did not use the captured steps"
     assert pooled == eager
     eng.model.ops.check_status()
+
+
+def test_packed_prompt_pass_matches_one_prompt_per_pass_on_gpu():
+    """Slices of several prompts in one prompt-class pass (tcgen05 grouped products, per-sequence attention tiles and
+    scans) give each chat the ids it gets when every pass holds one prompt."""
+    from vade_b200.runtime.scheduler import Request, Scheduler, SchedulerConfig
+    eng = build_engine(small_gpu_config(), device="cuda", seed=0, slots=8, max_seq=1024, prefill_chunk=512, synth_on_device=True)
+    lens = [300, 64, 450, 129, 511, 200]
+
+    def run(pack):
+        s = Scheduler(eng, SchedulerConfig(reserve_foreground=0, prefill_slice=256, prefill_pack=pack))
+        reqs = [s.submit(Request(prompt=_prompt(n, seed=60 + i), max_tokens=8, ignore_eos=True)) for i, n in enumerate(lens)]
+        before = eng.steps
+        while any(r.state != "done" for r in reqs):
+            if not s.tick():
+                s._reap()
+        return [list(r.output) for r in reqs], eng.steps - before
+
+    alone, n_alone = run(1)
+    packed, n_packed = run(2048)
+    assert packed == alone
+    assert n_packed < n_alone
+    eng.model.ops.check_status()

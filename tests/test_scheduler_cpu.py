@@ -85,3 +85,20 @@ def test_serving_load_benchmark_reproduces_solo_runs_on_the_tiny_model():
     res = run(eng, 8, 20, 80, 8, 0.7, 0.95, 3, 4, out=lines.append)
     assert res["incomplete"] == 0 and res["solo_identical"] == res["solo_checked"] == 3
     assert res["output_tokens"] == 64 and res["ttft_p99_s"] >= res["ttft_p50_s"] > 0
+
+
+def test_packed_prompt_pass_gives_the_ids_of_one_prompt_per_pass_in_fewer_passes():
+    eng = build_engine(tiny_config(), device="cpu", seed=0, slots=4, max_seq=256, prefill_chunk=128)
+    prompts = [_ids(100, 70), _ids(90, 71), _ids(120, 72), _ids(33, 73)]
+
+    def serve(pack):
+        s = Scheduler(eng, SchedulerConfig(reserve_foreground=0, max_active=4, prefill_slice=64, prefill_pack=pack))
+        reqs = [s.submit(Request(prompt=p, max_tokens=5, ignore_eos=True)) for p in prompts]
+        before = eng.steps
+        _drain(s, reqs)
+        return [list(r.output) for r in reqs], eng.steps - before
+
+    alone, passes_alone = serve(1)          # a pass never holds a second prompt
+    packed, passes_packed = serve(256)      # up to 256 prompt rows per pass
+    assert packed == alone
+    assert passes_packed < passes_alone

@@ -102,6 +102,40 @@ class Engine:
             return None, None
         return x[-1:], h[-1:]
 
+    def prefill_many(self, items: list) -> list:
+        """Prompt slices of several sequences in ONE prompt-class pass: ``items`` = [(seq, ids, mtp)], result = the
+        (x, h) of each slice's last row, in order.  A prompt pass costs one expansion of every routed expert it
+        touches however few rows it has, so packing the slices of waiting prompts divides that cost among them.  Every
+        row's arithmetic is that of the slice run alone (row-independent products, per-sequence attention and scan).
+        A slice that crosses this engine's tile grid, or that feeds the draft block, takes the one-sequence path."""
+        outs = [None] * len(items)
+        packed = []
+        for i, (seq, ids, mtp) in enumerate(items):
+            pos = len(seq.tokens)
+            one_tile = pos // self.prefill_chunk == (pos + len(ids) - 1) // self.prefill_chunk
+            if self.pp is not None or mtp or not one_tile or len(items) == 1:
+                outs[i] = self.prefill(seq, ids, mtp=mtp)
+            else:
+                packed.append(i)
+        if len(packed) == 1:
+            seq, ids, mtp = items[packed[0]]
+            outs[packed[0]] = self.prefill(seq, ids)
+        elif packed:
+            rows = []
+            for i in packed:
+                seq, ids, _ = items[i]
+                self.cache.ensure(seq.slot, len(seq.tokens) + len(ids))
+                rows.append((seq.slot, len(seq.tokens), list(ids)))
+            batch = Batch.make(rows, self.device, "prefill")
+            x, h = self._run(batch)
+            for i, s, e in zip(packed, batch.seq_start, batch.seq_start[1:]):
+                seq, ids, _ = items[i]
+                seq.last_x = x[e - 1:e].clone()
+                seq.tokens += list(ids)
+                self.cache.length[seq.slot] = len(seq.tokens)
+                outs[i] = (x[e - 1:e], h[e - 1:e])
+        return outs
+
     # ------------------------------------------------------------------ decode rows
     def step(self, seqs: list, rows: list):
         """Decode-class pass: ``rows[i]`` are the tokens sequence i appends (1 for a plain step,

@@ -38,6 +38,7 @@ from .sampler import Sampling, sample
 class SchedulerConfig:
     max_active: int = 16                 # decoding chats per pass
     prefill_slice: int = 2048            # rows one prompt advances per tick (multiple of 64)
+    prefill_pack: int = 8192             # rows of one prompt pass over all waiting prompts (their next slices, in admission order)
     reserve_foreground: int = 1          # slots only priority-255 requests may take
     prefix_cache_entries: int = 16
     prefix_cache_min_tokens: int = 64
@@ -275,30 +276,52 @@ class Scheduler:
         self.active.append(r)
         events.note("request_admitted")
 
-    # ---- 3. one prompt slice
+    # ---- 3. one prompt pass: the next slice of every waiting prompt that fits the pass
+    def _slice_end(self, r: Request) -> int:
+        """End of the request's next slice: cut at the slice grid and at the last 64-boundary below the prompt end
+        (the prefix checkpoint)."""
+        pos, total = r.done_prompt, len(r.prompt)
+        boundary = (total - 1) // PAGE * PAGE
+        end = min(total, (pos // self.cfg.prefill_slice + 1) * self.cfg.prefill_slice)
+        if pos < boundary < end:
+            end = boundary
+        return end
+
     def _prefill_one(self) -> bool:
+        picks, rows = [], 0
         for r in self.active:
             if r.state != "prefill":
                 continue
-            eng = self.engine
-            pos = r.done_prompt
+            end = self._slice_end(r)
+            if picks and rows + end - r.done_prompt > self.cfg.prefill_pack:
+                break                                   # admission order is kept: nobody overtakes a waiting prompt
+            picks.append((r, end))
+            rows += end - r.done_prompt
+        if not picks:
+            return False
+        eng = self.engine
+        outs = eng.prefill_many([(r.seq, r.prompt[r.done_prompt:end], r.draft == "strict") for r, end in picks])
+        finished = []
+        for (r, end), (x, h) in zip(picks, outs):
             total = len(r.prompt)
-            # cut at the slice grid and at the last 64-boundary below the prompt end (the checkpoint)
             boundary = (total - 1) // PAGE * PAGE
-            end = min(total, (pos // self.cfg.prefill_slice + 1) * self.cfg.prefill_slice)
-            if pos < boundary < end:
-                end = boundary
-            ids = r.prompt[pos:end]
-            x, h = eng.prefill(r.seq, ids, mtp=(r.draft == "strict"))
             r.done_prompt = end
             if end == boundary and r.cache and boundary >= self.cfg.prefix_cache_min_tokens and r.cached_tokens < boundary:
                 self._checkpoint(r, boundary)
             if end == total:
-                r.next_token = eng.choose(r.seq, h, total)
-                r.state = "decode"
-                r.first_token_at = time.monotonic()
-            return True
-        return False
+                finished.append((r, h))
+        if len(finished) == 1:
+            r, h = finished[0]
+            r.next_token = eng.choose(r.seq, h, len(r.prompt))
+        elif finished:
+            first = eng.choose_many([r.seq for r, _ in finished], torch.cat([h for _, h in finished], 0), [len(r.prompt) for r, _ in finished])
+            for (r, _), tok in zip(finished, first):
+                r.next_token = tok
+        now = time.monotonic()
+        for r, _ in finished:
+            r.state = "decode"
+            r.first_token_at = now
+        return True
 
     def _checkpoint(self, r: Request, boundary: int) -> None:
         """Keep the prompt prefix [0, boundary): a retained donor slot shares the KV pages, the
