@@ -95,9 +95,10 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="tensor/expert-parallel exchanges: fused into the kernels over peer memory, or NCCL collectives (baseline)")
-    ap.add_argument("--parallel", default="pp", choices=["pp", "tp"],
+    ap.add_argument("--parallel", default="pp", choices=["pp", "tp", "cp"],
                     help="how N > 1 GPUs serve the one chat: pp = layer pipeline (residual rows hop between stages, prompt tiles "
-                         "overlap across stages), tp = tensor + expert parallel with the exchanges named by --comm")
+                         "overlap across stages), tp = tensor + expert parallel with the exchanges named by --comm, cp = whole-model "
+                         "replicas that split the prompt by tokens and hand each layer's cache state on (rank 0 then decodes alone)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -124,11 +125,15 @@ def main() -> None:
         os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
         dist.init_process_group("nccl", device_id=torch.device(dev))
     use_pp = world > 1 and args.parallel == "pp"
+    use_cp = world > 1 and args.parallel == "cp"
     if args.prefill_chunk <= 0:
         args.prefill_chunk = (2048 if world <= 4 else 1024) if use_pp else min(8192, -(-args.prompt_len // 64) * 64)
     if use_pp and args.no_graph:
         raise SystemExit("--parallel pp runs the captured step only")
-    par = make_parallel(tp=1 if use_pp else world, pp=world if use_pp else 1, int_device=dev, fused=(args.comm == "fused"))
+    if use_cp:
+        par = make_parallel(tp=1, pp=1)                 # every rank is a one-GPU engine over the whole model
+    else:
+        par = make_parallel(tp=1 if use_pp else world, pp=world if use_pp else 1, int_device=dev, fused=(args.comm == "fused"))
 
     cfg = NAMED_CONFIGS[args.model]("nvfp4")
     total_len = args.prompt_len + args.warmup + 2 * args.steps + 16
@@ -158,17 +163,34 @@ def main() -> None:
     w = Sequence(eng.cache.new_slot())
     eng.prefill(w, prompt[:256])
     eng.cache.free_slot(w.slot)
+    split = None
+    if use_cp:
+        from vade_b200.parallel.context import ContextSplit
+        split = ContextSplit()
+        w = Sequence(eng.cache.new_slot())
+        split.prefill(eng, w, prompt[:128 * world])                      # opens the point-to-point connections
+        eng.cache.free_slot(w.slot)
     barrier()
     seq = Sequence(eng.cache.new_slot())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    _, h_last = eng.prefill(seq, prompt)
-    first = eng.model.greedy(h_last) if h_last is not None else None       # the last pipeline stage owns the head
+    _, h_last = split.prefill(eng, seq, prompt) if use_cp else eng.prefill(seq, prompt)
+    first = eng.model.greedy(h_last) if h_last is not None else None       # the last pipeline stage / the finishing replica owns the head
     e1.record()
     barrier()
     ttft_s = max_over_ranks(e0.elapsed_time(e1) / 1e3)
-    first = eng._bcast([int(first[0])] if first is not None else [])[0]
     ops.check_status()
+    if use_cp and rank != 0:
+        # the prompt's state now lives on rank 0, which decodes alone; this rank only keeps the job's barriers
+        eng.cache.free_slot(seq.slot)
+        barrier(); barrier(); max_over_ranks(0.0)
+        if not args.no_graph:
+            barrier()
+        barrier(); barrier(); max_over_ranks(0.0)
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+    first = int(first[0]) if use_cp else eng._bcast([int(first[0])] if first is not None else [])[0]
 
     # ---- decode: captured step at position prompt_len
     eng.cache.ensure(seq.slot, total_len)
@@ -273,8 +295,9 @@ def main() -> None:
             "scaling": "strong", "vs_baseline": round(tok_s / BASELINE_TOK_S.get(n, 41.8), 2), "dtype": "bf16 activations, NVFP4 weights",
             "data": "synthetic: random-init weights generated on device, uniform-random prompt ids (seed 1)",
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
-                       "parallelism": ("single" if n == 1 else f"pp{n}" if use_pp else f"tp{n}+ep{n}"), "cuda_graph": graph is not None, "prompt_tile_rows": args.prefill_chunk,
-                       "exchanges": ("none" if n == 1 else "nccl send/recv of residual rows between stages" if use_pp else args.comm),
+                       "parallelism": ("single" if n == 1 else f"pp{n}" if use_pp else f"cp{n} (prompt split by tokens over replicas, rank 0 decodes)" if use_cp else f"tp{n}+ep{n}"), "cuda_graph": graph is not None, "prompt_tile_rows": args.prefill_chunk,
+                       "exchanges": ("none" if n == 1 else "nccl send/recv of residual rows between stages" if use_pp
+                                     else "nccl send/recv of each layer's cache state during the prompt, none in decode" if use_cp else args.comm),
                        "l2": "each step streams >2 GB of weights, larger than the 126 MB L2"},
             "ttft_s": round(ttft_s, 4), "ttft_vs_baseline": round(BASELINE_TTFT_S.get(n, 1.933) / ttft_s, 2),
             "e2e": {"value": round(args.steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 8},

@@ -1,0 +1,109 @@
+"""Token split of one prompt over replicas (gloo on CPU): the finishing rank continues with the ids of the
+one-process run; cut points; a short prompt leaves ranks idle."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from vade_b200.config import tiny_config
+from vade_b200.parallel.context import ContextSplit, cut_points
+from vade_b200.runtime.build import build_engine
+from vade_b200.runtime.engine import Sequence
+
+
+def _prompt(n, vocab=4096, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab - 8, (n,), generator=g).tolist()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _continue(eng, seq, h, n_new):
+    """Greedy decode steps after a finished prompt."""
+    out = []
+    nxt = eng.choose(seq, h, len(seq.tokens))
+    for _ in range(n_new):
+        out.append(nxt)
+        x, h = eng.step([seq], [[nxt]])
+        seq.tokens.append(nxt)
+        eng.cache.length[seq.slot] = len(seq.tokens)
+        nxt = eng.choose(seq, h, len(seq.tokens))
+    return out
+
+
+def _worker(rank, world, port, n_prompt, n_new, chunk, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = build_engine(tiny_config(), seed=0, max_seq=1024, prefill_chunk=chunk)
+    cs = ContextSplit()
+    seq = Sequence(eng.cache.new_slot())
+    x, h = cs.prefill(eng, seq, _prompt(n_prompt))
+    if cs.finisher:
+        q.put((rank, _continue(eng, seq, h, n_new), dict(cs.stats)))
+    else:
+        eng.cache.free_slot(seq.slot)
+        q.put((rank, None, dict(cs.stats)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _launch(world, n_prompt, n_new=12, chunk=512):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_prompt, n_new, chunk, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = {}
+    for _ in range(world):
+        r, ids, stats = q.get(timeout=300)
+        outs[r] = (ids, stats)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    return outs
+
+
+def _single(n_prompt, n_new=12):
+    eng = build_engine(tiny_config(), seed=0, max_seq=1024, prefill_chunk=512)
+    seq = Sequence(eng.cache.new_slot())
+    x, h = eng.prefill(seq, _prompt(n_prompt))
+    return _continue(eng, seq, h, n_new)
+
+
+def test_cut_points_are_aligned_and_cover_the_prompt():
+    assert cut_points(8192, 2) == [0, 4096, 8192]
+    assert cut_points(8192, 8) == [0, 1024, 2048, 3072, 4096, 5120, 6144, 7168, 8192]
+    c = cut_points(1000, 3)
+    assert c[0] == 0 and c[-1] == 1000 and all(a <= b for a, b in zip(c, c[1:])) and all(v % 128 == 0 for v in c[:-1])
+    assert cut_points(200, 4) == [0, 0, 0, 0, 200]            # too short to split: one rank works
+    assert cut_points(300, 4) == [0, 0, 0, 256, 300]
+
+
+def test_two_rank_token_split_continues_with_the_single_process_ids():
+    ref = _single(700)
+    outs = _launch(2, 700)
+    assert outs[0][0] == ref
+    assert outs[1][0] is None and outs[1][1]["messages"] == 4          # one hand-over per layer of the tiny model
+
+
+def test_three_rank_chain_with_tiles_smaller_than_a_slice():
+    ref = _single(900)
+    outs = _launch(3, 900, chunk=128)                                  # every slice runs as several 128-row tiles
+    assert outs[0][0] == ref
+
+
+def test_short_prompt_leaves_far_ranks_idle():
+    ref = _single(150)
+    outs = _launch(2, 150)
+    assert outs[0][0] == ref and outs[1][1]["messages"] == 0

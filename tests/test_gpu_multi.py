@@ -154,3 +154,60 @@ def test_pipeline_stages_match_single_gpu():
         assert out == ref, f"stage {rank}: eager tokens differ from the single-GPU run"
         if rank in (0, world - 1):
             assert toks == ref, f"stage {rank}: captured-step tokens differ from the single-GPU run"
+
+
+def _cp_worker(rank, world, port, n_prompt, n_new, q):
+    """Whole-model replicas split one prompt by tokens; each layer's cache state hops to the next slice's GPU over
+    NCCL point-to-point; rank 0 finishes the prompt and decodes with its captured step."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    from vade_b200.parallel.context import ContextSplit
+    from vade_b200.runtime.graphs import DecodeGraph
+    from vade_b200.runtime.engine import Sequence
+    eng = build_engine(small_gpu_config(), device=f"cuda:{rank}", seed=0, max_seq=2048, prefill_chunk=512, synth_on_device=True)
+    cs = ContextSplit()
+    seq = Sequence(eng.cache.new_slot())
+    _, h = cs.prefill(eng, seq, _prompt(n_prompt, seed=5))
+    toks = None
+    if cs.finisher:
+        first = int(eng.model.greedy(h)[0])
+        eng.cache.ensure(seq.slot, n_prompt + n_new + 8)
+        g = DecodeGraph(eng, [seq.slot], n_prompt + n_new + 8)
+        g.capture([first], [len(seq.tokens)])
+        toks = [first]
+        for _ in range(n_new - 1):
+            g.replay()
+            toks.append(int(g.tokens[0]))
+    else:
+        eng.cache.free_slot(seq.slot)
+    eng.model.ops.check_status()
+    q.put((rank, toks, dict(cs.stats)))
+    dist.barrier()
+    torch.cuda.synchronize()
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_token_split_of_a_prompt_over_replicas_matches_single_gpu():
+    world = _world()
+    n_prompt, n_new = 1300, 12
+    eng = build_engine(small_gpu_config(), device="cuda:0", seed=0, max_seq=2048, prefill_chunk=512, synth_on_device=True)
+    ref = eng.generate(_prompt(n_prompt, seed=5), n_new).generated
+    del eng
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cp_worker, args=(r, world, port, n_prompt, n_new, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = {r: (t, s) for r, t, s in (q.get(timeout=240) for _ in range(world))}
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert outs[0][0] == ref, "the finishing replica's tokens differ from the single-GPU run"
+    assert all(outs[r][1]["messages"] == 4 for r in range(1, world)), "one hand-over per layer and sending rank"

@@ -46,9 +46,11 @@ class HybridModel:
         return ops.combine_add_norm(pair_out, routing, x, next_norm)
 
     # ------------------------------------------------------------------ trunk
-    def forward(self, batch: Batch, cache, hidden_in: torch.Tensor | None = None):
+    def forward(self, batch: Batch, cache, hidden_in: torch.Tensor | None = None, hook=None):
         """Runs this stage's layers.  Returns (x, h): the fp32 residual rows and, on the last stage,
-        their final-norm rows; on other stages h is None and x goes to the next stage."""
+        their final-norm rows; on other stages h is None and x goes to the next stage.  ``hook`` (optional) has
+        ``before(i)`` / ``after(i)``, called around layer i: the place where a token-split prompt receives and
+        hands on the layer's cache state (parallel/context.py)."""
         ops, plan = self.ops, self.plan
         x = ops.embed(self.w.embed, batch.tokens) if plan.first_stage else hidden_in
         layers = list(range(*plan.layers))
@@ -58,7 +60,11 @@ class HybridModel:
                 nxt = self.w.layers[layers[n + 1]].input_norm
             else:
                 nxt = self.w.final_norm if plan.last_stage else None
+            if hook is not None:
+                hook.before(i)
             x, h = self._layer(self.w.layers[i], i, x, h, batch, cache, nxt)
+            if hook is not None:
+                hook.after(i)
         return x, h
 
     # ------------------------------------------------------------------ heads

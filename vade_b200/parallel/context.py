@@ -1,0 +1,140 @@
+"""Context-parallel prompt processing: one long prompt split by tokens over R replicas of the model.
+
+Every rank of the group holds the whole model (the data-parallel layout) and takes one contiguous slice of the
+prompt.  Slice j needs, for every layer, the cache state that slices 0..j-1 leave behind: the Gated-DeltaNet
+matrix and the three convolution rows (O(1) in the prompt length), and the K/V pages of all earlier positions.
+The rank of slice j therefore receives layer i's state right before it runs layer i and hands its own on right
+after, so the ranks work one layer apart: rank of slice j runs layer i while the rank of slice j+1 runs layer
+i-1.  A prompt of N rows on R ranks costs about (L + R - 1) / L of one slice instead of R slices.
+
+Token ids do not change: a slice is a prompt tile that starts on a multiple of 128 tokens, and a tile's rows see
+exactly the state that the rows before it produced, whichever GPU produced it; only raw cache words move.
+
+The LAST slice goes to group rank 0, which ends up holding the complete state of the prompt and serves the chat
+from there (decode, sampling, drafting) as a one-GPU engine; the other ranks release their slot.
+
+On GPUs the transfers are NCCL point-to-point operations over NVLink, ordered on the compute stream; on CPU gloo.
+Parity: the reference's long-prompt token split and its chained form over more ranks: per-layer export of the
+GDN state and the KV rows at the cut, the importing rank one layer behind
+(engine/crates/engine/src/flash/next_tp_seq.rs:122-201, tp_switch.rs:44-60,120-133), and the sequence-parallel
+prefill with forward K/V exchange (engine/crates/seqpar/src/prefill.rs:59-100, partition.rs:9-60).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops.api import Batch
+from ..runtime.cache import PAGE
+
+ALIGN = 128
+
+
+def cut_points(n_tokens: int, ranks: int, align: int = ALIGN, min_rows: int = ALIGN) -> list:
+    """Cuts [c0 = 0, c1, ..., cR = n_tokens]: equal slices rounded to ``align``; a prompt too short to give every
+    rank ``min_rows`` rows uses fewer ranks (the leading slices are empty: c_j == c_{j+1} == 0)."""
+    use = max(1, min(ranks, n_tokens // max(min_rows, 1)))
+    per = -(-n_tokens // use)
+    per = -(-per // align) * align
+    cuts = [min(n_tokens, j * per) for j in range(use + 1)]
+    cuts[-1] = n_tokens
+    return [0] * (ranks - use) + cuts
+
+
+class _Handoff:
+    """Layer hook of one slice: ``before(i)`` receives layer i's state from the rank of the previous slice,
+    ``after(i)`` sends this rank's state of layer i to the rank of the next slice."""
+
+    def __init__(self, cache, slot: int, start: int, end: int, src: int | None, dst: int | None, group, stats: dict):
+        self.cache, self.slot, self.start, self.end = cache, slot, start, end
+        self.src, self.dst, self.group, self.stats = src, dst, group, stats
+        self.recv_on = self.send_on = False
+
+    def _pages(self, upto: int) -> torch.Tensor:
+        ids = self.cache._table_host[self.slot][:upto // PAGE]
+        return torch.tensor(ids, dtype=torch.int64, device=self.cache.device)
+
+    def before(self, i) -> None:
+        if not self.recv_on or self.src is None or self.start == 0:
+            return
+        c = self.cache
+        if i in c.gdn_state:
+            dist.recv(c.gdn_state[i][self.slot], self.src, group=self.group)
+            dist.recv(c.conv_hist[i][self.slot], self.src, group=self.group)
+        else:
+            kp, vp = c.k_pages[i], c.v_pages[i]
+            pages = self._pages(self.start)
+            buf = torch.empty(2, pages.numel(), *kp.shape[1:], dtype=kp.dtype, device=kp.device)
+            dist.recv(buf, self.src, group=self.group)
+            kp[pages] = buf[0]
+            vp[pages] = buf[1]
+
+    def after(self, i) -> None:
+        if not self.send_on or self.dst is None:
+            return
+        c = self.cache
+        if i in c.gdn_state:
+            for t in (c.gdn_state[i][self.slot], c.conv_hist[i][self.slot]):
+                dist.send(t, self.dst, group=self.group)
+                self.stats["bytes"] += t.numel() * t.element_size()
+        else:
+            pages = self._pages(self.end)
+            buf = torch.stack([c.k_pages[i][pages], c.v_pages[i][pages]], 0)
+            dist.send(buf, self.dst, group=self.group)
+            self.stats["bytes"] += buf.numel() * buf.element_size()
+        self.stats["messages"] += 1
+
+
+class ContextSplit:
+    """Token split of prompts over the ranks of ``group`` (all ranks of the job when None).  ``ranks`` lists the
+    global ranks of the group in group order; rank ``ranks[0]`` finishes every prompt."""
+
+    def __init__(self, group=None, ranks: list | None = None):
+        self.group = group
+        self.ranks = list(ranks) if ranks is not None else list(range(dist.get_world_size()))
+        self.me = self.ranks.index(dist.get_rank())
+        self.stats = {"bytes": 0, "messages": 0, "prompts": 0}
+
+    @property
+    def world(self) -> int:
+        return len(self.ranks)
+
+    @property
+    def finisher(self) -> bool:
+        return self.me == 0
+
+    def prefill(self, engine, seq, ids: list):
+        """Every rank of the group calls this with the same ``ids`` and a fresh sequence of its own cache.  Returns
+        (x, h) of the prompt's last row on the finishing rank and (None, None) on the others, whose slot holds only
+        their slice's state afterwards and should be freed."""
+        if engine.pp is not None or engine.model.plan.tp != 1:
+            raise RuntimeError("a token split runs over whole-model replicas")
+        if seq.tokens:
+            raise ValueError("a token split starts at position 0")
+        R = self.world
+        j = R - 1 - self.me                                   # my slice; slice R-1 (the last) is rank 0's
+        cuts = cut_points(len(ids), R)
+        start, end = cuts[j], cuts[j + 1]
+        self.stats["prompts"] += 1
+        if end == start:
+            return None, None                                  # a short prompt leaves the far ranks idle
+        src = self.ranks[self.me + 1] if self.me + 1 < R and start > 0 else None
+        dst = self.ranks[self.me - 1] if self.me > 0 else None
+        cache = engine.cache
+        cache.ensure(seq.slot, end)
+        hook = _Handoff(cache, seq.slot, start, end, src, dst, self.group, self.stats)
+        pos, x, h = start, None, None
+        while pos < end:
+            n = min(engine.prefill_chunk - pos % engine.prefill_chunk, end - pos)
+            hook.recv_on = pos == start
+            hook.send_on = pos + n == end
+            batch = Batch.make([(seq.slot, pos, ids[pos:pos + n])], engine.device, "prefill")
+            x, h = engine._run(batch, hook)
+            pos += n
+        seq.tokens = list(ids[:end])
+        seq.n_prompt = len(ids)
+        cache.length[seq.slot] = end
+        if not self.finisher:
+            return None, None
+        seq.last_x = x[-1:].clone()
+        return x[-1:], h[-1:]

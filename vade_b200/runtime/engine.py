@@ -57,13 +57,13 @@ class Engine:
         self.steps = 0
 
     # ------------------------------------------------------------------ stage plumbing
-    def _run(self, batch: Batch):
+    def _run(self, batch: Batch, hook=None):
         """One pass over this rank's layers, with pipeline hand-over when pp > 1."""
         plan = self.model.plan
         hidden = None
         if self.pp is not None and not plan.first_stage:
             hidden = self.pp.recv_rows(batch.rows, self.cfg.hidden_size, self.device)
-        x, h = self.model.forward(batch, self.cache, hidden)
+        x, h = self.model.forward(batch, self.cache, hidden, hook)
         if self.pp is not None and not plan.last_stage:
             self.pp.send_rows(x)
         self.steps += 1
