@@ -87,19 +87,46 @@ def cmd_inspect(a) -> int:
 
 
 def cmd_serve(a) -> int:
+    """One process per GPU.  With ``--tp N`` (launched as N ranks, e.g. ``python -m torch.distributed.run --nproc-per-node N
+    --master-addr 127.0.0.1 -m vade_b200.cli.main serve MODEL --tp N``) the model is sharded tensor + expert parallel, rank 0
+    owns the HTTP front end and every rank runs the same scheduler turns (runtime/mirror.py)."""
     import torch
     from ..runtime.build import load_engine
     from ..runtime.scheduler import Scheduler, SchedulerConfig
     from ..serve.http import ApiServer
     from ..ops import _ext
-    device = a.device or ("cuda:0" if torch.cuda.is_available() else "cpu")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    on_gpu = torch.cuda.is_available() and (a.device or "cuda").startswith("cuda")
+    device = a.device or (f"cuda:{local}" if on_gpu else "cpu")
+    kw, mirror, leader = {}, None, True
+    if a.tp > 1:
+        import torch.distributed as dist
+        from ..parallel.groups import make_parallel
+        from ..runtime.mirror import Mirror
+        if world != a.tp:
+            raise SystemExit(f"--tp {a.tp} needs {a.tp} ranks (WORLD_SIZE is {world}): launch with torch.distributed.run")
+        if on_gpu:
+            device = f"cuda:{local}"
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device(device))
+        else:
+            dist.init_process_group("gloo")
+        par = make_parallel(tp=a.tp, pp=1, int_device=device, fused=on_gpu and a.comm == "fused")
+        mirror = Mirror()
+        leader = mirror.leader
+        kw = dict(tp=a.tp, tp_rank=par.tp_rank, comm=par.comm)
     eng, tok, receipt = load_engine(a.model, device=device, slots=a.slots + 1 + a.cache_entries, max_seq=a.context,
-                                    prefill_chunk=a.prefill_chunk)
+                                    prefill_chunk=a.prefill_chunk, **kw)
     sched = Scheduler(eng, SchedulerConfig(max_active=a.slots, prefill_slice=a.prefill_chunk, prefix_cache_entries=a.cache_entries),
-                      eos_id=tok.eos_id, detokenize=tok.decode)
+                      eos_id=tok.eos_id, detokenize=tok.decode, mirror=mirror)
+    if not leader:
+        sched.run_forever()          # follows the leader's turns until it publishes stop
+        return 0
     key = open(a.api_key_file).read().strip() if a.api_key_file else None
-    info = {"checkpoint": {"sha256": receipt.get("fingerprint")}, "world": 1, "device": device,
+    info = {"checkpoint": {"sha256": receipt.get("fingerprint")}, "world": max(a.tp, 1), "device": device,
             "numerics": {"path": eng.model.ops.name, "weights": eng.cfg.quant.method},
+            "parallel": {"tp": a.tp, "ep": a.tp, "exchanges": (a.comm if on_gpu else "gloo") if a.tp > 1 else "none"},
             "build": {"extension": os.path.basename(_ext.so_path()) if device != "cpu" else None}}
     api = ApiServer(sched, tok, os.path.basename(os.path.abspath(a.model)), info, max_output=a.max_output, api_key=key)
     port = api.start(a.host, a.port, allow_remote=a.allow_remote, run_engine=False)
@@ -107,7 +134,9 @@ def cmd_serve(a) -> int:
     try:
         sched.run_forever()          # the engine loop owns the main thread
     except KeyboardInterrupt:
-        pass
+        sched.stop()
+        if mirror is not None:
+            sched.run_forever()      # publishes stop to the followers
     finally:
         api.stop()
     return 0
@@ -283,7 +312,8 @@ def main(argv=None) -> int:
     p.add_argument("--device", default=None); p.add_argument("--slots", type=int, default=16); p.add_argument("--context", type=int, default=32768)
     p.add_argument("--prefill-chunk", type=int, default=2048); p.add_argument("--cache-entries", type=int, default=16)
     p.add_argument("--max-output", type=int, default=16384); p.add_argument("--allow-remote", action="store_true")
-    p.add_argument("--api-key-file", default=None); p.set_defaults(fn=cmd_serve)
+    p.add_argument("--api-key-file", default=None); p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--comm", default="fused", choices=["fused", "nccl"]); p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("verify"); p.add_argument("--url", default="http://127.0.0.1:8000"); p.add_argument("--runs", type=int, default=2)
     p.add_argument("--max-tokens", type=int, default=128); p.add_argument("--prompt", default="Write a short story about a lighthouse keeper.")
     p.add_argument("--receipt", default=None); p.add_argument("--api-key", default=None); p.add_argument("--allow-undrafted", action="store_true")

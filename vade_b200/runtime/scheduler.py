@@ -23,7 +23,7 @@ import itertools
 import threading
 import time
 from collections import OrderedDict, deque
-from dataclasses import dataclass, field
+from dataclasses import asdict, dataclass, field
 
 import torch
 
@@ -131,9 +131,26 @@ class PrefixCache:
         return {"entries": len(self.items), "hits": self.hits, "misses": self.misses}
 
 
+_SPEC_FIELDS = ("prompt", "max_tokens", "stop_ids", "stop_strings", "ignore_eos", "draft", "mtp_depth", "cache", "cache_salt",
+                "priority", "id")
+
+
+def _spec(r: Request) -> dict:
+    """What a follower needs to build its own copy of a request: everything that can influence a pass."""
+    d = {k: getattr(r, k) for k in _SPEC_FIELDS}
+    d["sampling"] = Sampling(**asdict(r.sampling))
+    return d
+
+
 class Scheduler:
-    def __init__(self, engine: Engine, config: SchedulerConfig | None = None, eos_id: int | None = None, detokenize=None):
+    def __init__(self, engine: Engine, config: SchedulerConfig | None = None, eos_id: int | None = None, detokenize=None,
+                 mirror=None):
+        """``mirror`` (runtime/mirror.py): the scheduler runs replicated on every serving rank; the leader publishes each
+        turn's intake and the followers apply it, so all ranks run the same passes."""
         self.engine = engine
+        self.mirror = mirror
+        self.inbox: deque = deque()                       # mirrored leader: submitted, not yet published
+        self.release_cache = False
         self.cfg = config or SchedulerConfig()
         assert self.cfg.prefill_slice % PAGE == 0
         self.eos_id = eos_id
@@ -156,17 +173,19 @@ class Scheduler:
             raise ValueError("empty prompt")
         if len(req.prompt) + req.max_tokens > limit:
             raise ValueError(f"prompt ({len(req.prompt)}) plus max_tokens ({req.max_tokens}) exceeds the context limit {limit}")
+        if self.mirror is not None and not self.mirror.leader:
+            raise RuntimeError("requests enter at the leader rank")
         with self.lock:
-            if len(self.queue) >= self.cfg.max_queue:
+            if len(self.queue) + len(self.inbox) >= self.cfg.max_queue:
                 raise OverflowError("server overloaded: request queue is full")
             req.id = next(self.ids)
-            self.queue.append(req)
+            (self.queue if self.mirror is None else self.inbox).append(req)
         events.note("request_queued")
         return req
 
     def cancel(self, req_id: int) -> bool:
         with self.lock:
-            for r in list(self.queue) + self.active:
+            for r in list(self.inbox) + list(self.queue) + self.active:
                 if r.id == req_id:
                     r.cancelled = True
                     return True
@@ -174,20 +193,23 @@ class Scheduler:
 
     def snapshot(self) -> dict:
         c = self.engine.cache
-        return {"active": len(self.active), "queued": len(self.queue), "free_slots": len(c.free_slots),
+        return {"active": len(self.active), "queued": len(self.queue) + len(self.inbox), "free_slots": len(c.free_slots),
                 "free_pages": c.alloc.available, "total_pages": c.alloc.total, "prefix_cache": self.prefix.stats(),
                 "ticks": self.ticks}
 
     # ------------------------------------------------------------------ engine thread
     def run_forever(self, idle_sleep: float = 0.001) -> None:
+        follower = self.mirror is not None and not self.mirror.leader
         try:
             while not self.stop_flag:
-                if not self.tick():
+                if not self.tick() and not follower:        # a follower's turn blocks on the leader's message instead
                     time.sleep(idle_sleep)
+            if self.mirror is not None and self.mirror.leader:
+                self.mirror.publish({"new": [], "cancel": [], "deadline": [], "release_cache": False, "stop": True})
         except Exception as e:                              # a failed pass invalidates every participant
             self.fatal = f"{type(e).__name__}: {e}"
             events.note("engine_fatal", self.fatal)
-            for r in list(self.active) + list(self.queue):
+            for r in list(self.active) + list(self.queue) + list(self.inbox):
                 r.error = self.fatal
                 r.push(("error", self.fatal))
             raise
@@ -195,29 +217,75 @@ class Scheduler:
     def stop(self) -> None:
         self.stop_flag = True
 
+    def drop_prefix_cache(self) -> None:
+        """Releases every retained prefix at the start of the next turn (on every rank when mirrored)."""
+        self.release_cache = True
+
     def tick(self) -> bool:
+        msg = self._intake()
+        if msg is None:                                     # mirrored leader with nothing to do and nothing to tell
+            return False
+        if msg["stop"]:
+            self.stop_flag = True
+            return False
         self.ticks += 1
-        self._reap()
+        self._apply(msg)
         self._admit()
         worked = self._prefill_one()
         worked = self._decode_pass() or worked
         return worked
 
-    # ---- 1. cancellations and deadlines
-    def _reap(self) -> None:
+    # ---- 1. intake: new requests, cancellations, deadlines (collected on the leader, applied on every rank)
+    def _collect(self) -> dict:
         now = time.monotonic()
+        with self.lock:
+            new = list(self.inbox)
+            self.inbox.clear()
+            cancel = [r.id for r in new + list(self.queue) + self.active if r.cancelled]
+            release, self.release_cache = self.release_cache, False
+        deadline = [r.id for r in self.active if not r.cancelled and now - r.created > self.cfg.request_timeout_s]
+        return {"new": new, "cancel": cancel, "deadline": deadline, "release_cache": release, "stop": self.stop_flag}
+
+    def _intake(self):
+        m = self.mirror
+        if m is None:
+            return self._collect()
+        if not m.leader:
+            msg = m.receive()
+            msg["new"] = [Request(**spec) for spec in msg["new"]]
+            return msg
+        msg = self._collect()
+        busy = bool(self.active or self.queue or msg["new"] or msg["cancel"] or msg["deadline"] or msg["release_cache"] or msg["stop"])
+        if not busy and not m.keepalive_due():
+            return None
+        m.publish({**msg, "new": [_spec(r) for r in msg["new"]]})
+        return msg
+
+    def _apply(self, msg: dict) -> None:
+        with self.lock:
+            if self.mirror is not None:
+                self.queue.extend(msg["new"])
+        cancel, deadline = set(msg["cancel"]), set(msg["deadline"])
         for r in list(self.active):
-            if r.cancelled:
+            if r.id in cancel:
                 self._finish(r, "cancelled")
-            elif now - r.created > self.cfg.request_timeout_s:
+            elif r.id in deadline:
                 self._finish(r, "deadline")
         with self.lock:
             for r in list(self.queue):
-                if r.cancelled:
+                if r.id in cancel:
                     self.queue.remove(r)
                     r.finish_reason = "cancelled"
                     r.state = "done"
                     r.push(("done", "cancelled"))
+        if msg["release_cache"]:
+            while self.prefix.items and self.prefix.evict_one():
+                pass
+
+    def _reap(self) -> None:
+        """Applies pending cancellations and deadlines outside a turn (single-process use: drain loops, tests)."""
+        if self.mirror is None:
+            self._apply(self._collect())
 
     # ---- 2. admission
     def _pages_for(self, r: Request) -> int:

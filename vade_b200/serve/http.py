@@ -124,9 +124,8 @@ class ApiServer:
                 rid = json.loads(body or b"{}").get("id")
                 return self._send(h, 200, {"cancelled": bool(rid is not None and self.sched.cancel(int(rid)))})
             if path == "/v1/kv/release":
-                freed = 0
-                while self.sched.prefix.items and self.sched.prefix.evict_one():
-                    freed += 1
+                freed = len(self.sched.prefix.items)
+                self.sched.drop_prefix_cache()           # applied by the engine thread at its next turn (on every rank)
                 return self._send(h, 200, {"released": freed})
             if path == "/v1/admission":
                 obj = json.loads(body or b"{}")
