@@ -35,6 +35,7 @@ namespace vade {
 
 constexpr int kRowsThreads = 128;
 constexpr int kChunk = 8;                                  // K blocks kept in flight per thread
+constexpr int kMaxXParts = 4;                              // fp32 partials of a fused SwiGLU token operand
 constexpr int kXStride = kChunk * 128 + 64;                // bytes per staged token row (odd multiple of 64: conflict-free 16-byte reads)
 
 // Four bytes (eight e2m1 values, low nibble first) -> four f16x2 of value * scale (exact), `mult` = f16x2(scale, scale).
@@ -102,6 +103,9 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
         orow0 = row0;
     }
 
+    // groups of eight token rows that hold a row of this task: a 16-row block of the small-pass layout usually
+    // holds one or two rows, and the other groups are neither staged nor multiplied
+    const int nt_used = active ? min(NT, (nrows + 7) >> 3) : 0;
     float acc[NT][4], tot[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -135,7 +139,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
             if (threadIdx.x < NT * 8) row_max[threadIdx.x] = 0u;
             __syncthreads();
             const int pieces = nc * 8;                     // 16-byte pieces per staged token row
-            for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRowsThreads) {
+            for (int p = threadIdx.x; p < nt_used * 8 * pieces; p += kRowsThreads) {
                 const int j = p / pieces;
                 const int q = p - j * pieces;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -148,17 +152,33 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                         // columns): ascending sums, bf16 roundings of gate and up, bf16(silu(gate) * up)
                         const float4* src = reinterpret_cast<const float4*>(xparts + (static_cast<long long>(row0 + j) * a.kb_total * kTileK + col) * 2);
                         uint32_t o[4];
-#pragma unroll 1
-                        for (int u = 0; u < 4; ++u) {                  // one float4 = gate, up, gate, up of two columns
-                            float4 sum = __ldcg(src + u);
-                            for (int pp = 1; pp < x_nparts; ++pp) {
-                                const float4 nx = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + pp * xpart_stride) + u);
-                                sum.x += nx.x; sum.y += nx.y; sum.z += nx.z; sum.w += nx.w;
+                        // all partials of two float4s are requested before the first is used (up to 8 loads in
+                        // flight per thread); the sums keep the ascending order of the partials
+#pragma unroll
+                        for (int uh = 0; uh < 2; ++uh) {
+                            float4 pv[2][kMaxXParts];
+#pragma unroll
+                            for (int u2 = 0; u2 < 2; ++u2) {
+#pragma unroll
+                                for (int pp = 0; pp < kMaxXParts; ++pp) {
+                                    if (pp < x_nparts)
+                                        pv[u2][pp] = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + pp * xpart_stride) + uh * 2 + u2);
+                                }
                             }
-                            const float m0 = siluf_(bf16_round(sum.x)) * bf16_round(sum.y);
-                            const float m1 = siluf_(bf16_round(sum.z)) * bf16_round(sum.w);
-                            const __nv_bfloat162 pk = __floats2bfloat162_rn(m0, m1);
-                            o[u] = *reinterpret_cast<const uint32_t*>(&pk);
+#pragma unroll
+                            for (int u2 = 0; u2 < 2; ++u2) {           // one float4 = gate, up, gate, up of two columns
+                                float4 sum = pv[u2][0];
+#pragma unroll
+                                for (int pp = 1; pp < kMaxXParts; ++pp) {
+                                    if (pp < x_nparts) {
+                                        sum.x += pv[u2][pp].x; sum.y += pv[u2][pp].y; sum.z += pv[u2][pp].z; sum.w += pv[u2][pp].w;
+                                    }
+                                }
+                                const float m0 = siluf_(bf16_round(sum.x)) * bf16_round(sum.y);
+                                const float m1 = siluf_(bf16_round(sum.z)) * bf16_round(sum.w);
+                                const __nv_bfloat162 pk = __floats2bfloat162_rn(m0, m1);
+                                o[uh * 2 + u2] = *reinterpret_cast<const uint32_t*>(&pk);
+                            }
                         }
                         v = make_uint4(o[0], o[1], o[2], o[3]);
                     }
@@ -172,7 +192,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
             }
             __syncthreads();
             // second pass: bf16 -> f16 of x * 2^s, s = 13 - exponent of the row's maximum (clamped), in place
-            for (int p = threadIdx.x; p < NT * 8 * pieces; p += kRowsThreads) {
+            for (int p = threadIdx.x; p < nt_used * 8 * pieces; p += kRowsThreads) {
                 const int j = p / pieces;
                 const int q = p - j * pieces;
                 const int e = static_cast<int>(row_max[j] >> 7) - 127;             // floor(log2(max)) of a normal bf16
@@ -206,6 +226,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                         expand_word(w1, m1[h], A1);
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
+                            if (n >= nt_used) continue;    // the task has no token row in this group of eight (same for the whole CTA)
                             const uint4 bx = *reinterpret_cast<const uint4*>(xs + (n * 8 + g) * kXStride + i * 128 + h * 64 + t * 16);
                             mma_f16(acc[n], A0[0], A1[0], A0[1], A1[1], bx.x, bx.y);
                             mma_f16(acc[n], A0[2], A1[2], A0[3], A1[3], bx.z, bx.w);
@@ -216,6 +237,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
             // the chunk's sums leave the scaled domain (2^-s is exact) and join the row totals
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
+                if (n >= nt_used) continue;
                 const float i0 = row_inv[n * 8 + 2 * t], i1 = row_inv[n * 8 + 2 * t + 1];
                 tot[n][0] += acc[n][0] * i0; tot[n][1] += acc[n][1] * i1;
                 tot[n][2] += acc[n][2] * i0; tot[n][3] += acc[n][3] * i1;
@@ -282,6 +304,7 @@ static const char* launch_rows(const GemmArgs& h, const GemmDev& d, dim3 grid, c
 const char* rows_mma_gemm(const GemmArgs& h, const GemmDev& d, cudaStream_t stream) {
     const int group = h.tasks != nullptr ? h.bn : (h.tokens < 64 ? h.tokens : 64);   // token rows per CTA
     if (group < 1 || group > 64) return "the decode-class kernel takes 1..64 token rows per task";
+    if (h.x_parts != nullptr && (h.x_n_parts < 1 || h.x_n_parts > kMaxXParts)) return "a fused token operand has 1..4 partials";
     const int nt = group <= 8 ? 1 : group <= 16 ? 2 : group <= 32 ? 4 : 8;
     const int m_tiles = (h.n_out + kTileM - 1) / kTileM;
     const int y = h.tasks != nullptr ? h.max_tasks : (h.tokens + nt * 8 - 1) / (nt * 8);
