@@ -35,7 +35,7 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
           c10::optional<torch::Tensor> tasks, c10::optional<torch::Tensor> meta, int64_t max_tasks,
           c10::optional<torch::Tensor> status, std::vector<int64_t> peer_out, std::vector<int64_t> peer_flags, int64_t peer_local,
           int64_t peer_half_stride, int64_t peer_self, int64_t peer_local_only_from, bool rows_kernel,
-          c10::optional<torch::Tensor> x_parts) {
+          c10::optional<torch::Tensor> x_parts, c10::optional<torch::Tensor> x_row_index) {
     need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be bf16 rows on the GPU");
     need(w.is_cuda() && w.is_contiguous() && row_scale.is_cuda() && row_scale.scalar_type() == torch::kFloat32, "bad weights");
     need(out.is_cuda(), "bad output");
@@ -50,6 +50,10 @@ void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor row_scale, torch::Tens
         need(x_parts->is_cuda() && x_parts->scalar_type() == torch::kFloat32 && x_parts->is_contiguous() && x_parts->dim() == 3 &&
              x_parts->size(2) == 2 * k, "x_parts must be fp32 [parts, rows, 2k]");
         a.x_parts = x_parts->data_ptr<float>(); a.x_part_stride = x_parts->stride(0); a.x_n_parts = static_cast<int>(x_parts->size(0));
+    }
+    if (x_row_index.has_value()) {
+        need(x_row_index->is_cuda() && x_row_index->scalar_type() == torch::kInt32 && x_row_index->is_contiguous(), "x_row_index must be int32 on the GPU");
+        a.x_row_index = x_row_index->data_ptr<int>();
     }
     if (tasks.has_value()) {
         need(meta.has_value(), "grouped GEMM needs the task count");
@@ -193,23 +197,25 @@ void moe_route(torch::Tensor logits, int64_t n_parts, int64_t E, int64_t k, bool
 
 void moe_route_small(torch::Tensor logits, int64_t n_parts, int64_t E, int64_t k, bool renorm, int64_t e0, int64_t n_local, int64_t ns,
                      torch::Tensor ids, torch::Tensor wts, torch::Tensor sg, torch::Tensor tasks_up, torch::Tensor tasks_down,
-                     torch::Tensor meta, torch::Tensor slot_row) {
+                     torch::Tensor meta, torch::Tensor slot_row, c10::optional<torch::Tensor> row_token) {
     need(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous(), "route arguments");
+    need(!row_token.has_value() || (row_token->is_cuda() && row_token->scalar_type() == torch::kInt32), "row_token must be int32 on the GPU");
     c10::cuda::CUDAGuard guard(logits.device());
     const int64_t T = logits.size(-2), ld = logits.size(-1);
     check(vade::moe_route_small(logits.data_ptr<float>(), T * ld, static_cast<int>(n_parts), static_cast<int>(ld), static_cast<int>(T),
                                 static_cast<int>(E), static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local),
                                 static_cast<int>(ns), ids.data_ptr<int>(), wts.data_ptr<float>(), sg.data_ptr<float>(),
                                 tasks_up.data_ptr<int>(), tasks_down.data_ptr<int>(), meta.data_ptr<int>(), slot_row.data_ptr<int>(),
-                                stream_of(logits)));
+                                ptr<int>(row_token), stream_of(logits)));
 }
 
 // Decode-class router (logits as 8 K-range partials) with, optionally, the small-pass routing fused in.
 void router_rows(torch::Tensor w, torch::Tensor x, torch::Tensor logits, c10::optional<torch::Tensor> ticket, int64_t E, int64_t k,
                  bool renorm, int64_t e0, int64_t n_local, int64_t ns, c10::optional<torch::Tensor> ids, c10::optional<torch::Tensor> wts,
                  c10::optional<torch::Tensor> sg, c10::optional<torch::Tensor> tasks_up, c10::optional<torch::Tensor> tasks_down,
-                 c10::optional<torch::Tensor> meta, c10::optional<torch::Tensor> slot_row) {
+                 c10::optional<torch::Tensor> meta, c10::optional<torch::Tensor> slot_row, c10::optional<torch::Tensor> row_token) {
     need(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 2, "router rows must be bf16");
+    need(!row_token.has_value() || (row_token->is_cuda() && row_token->scalar_type() == torch::kInt32), "row_token must be int32 on the GPU");
     need(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) == w.size(1), "router input");
     need(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous() && logits.dim() == 3 && logits.size(0) == 8 &&
          logits.size(1) == x.size(0) && logits.size(2) >= w.size(0), "router logits must be fp32 [8, T, ld]");
@@ -223,7 +229,7 @@ void router_rows(torch::Tensor w, torch::Tensor x, torch::Tensor logits, c10::op
                             ticket.has_value() ? reinterpret_cast<unsigned int*>(ticket->data_ptr<int>()) : nullptr, static_cast<int>(E),
                             static_cast<int>(k), renorm, static_cast<int>(e0), static_cast<int>(n_local), static_cast<int>(ns),
                             ptr<int>(ids), ptr<float>(wts), ptr<float>(sg), ptr<int>(tasks_up), ptr<int>(tasks_down), ptr<int>(meta),
-                            ptr<int>(slot_row), stream_of(x)));
+                            ptr<int>(slot_row), ptr<int>(row_token), stream_of(x)));
 }
 
 // Runs the bounded consumer wait of an exchange on `flags` (int32 [n]); returns after at most limit_ms.

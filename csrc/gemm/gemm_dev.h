@@ -18,6 +18,7 @@ struct GemmDev {
     void* out;
     const int4* tasks;
     const int* num_tasks;
+    const int* row_index;           // decode-class kernel: optional indirection of a task's token rows
     uint32_t* status;
     long long w_expert_stride;      // bytes between stacked matrices (NVFP4 tiles)
     long long out_range_stride;     // elements between range partials

@@ -146,7 +146,8 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
                 if (j < nrows) {
                     const int col = (kb0 + c0) * kTileK + q * 8;
                     if (!XP) {
-                        v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row0 + j) * ldx + col);
+                        const long long xr = a.row_index != nullptr ? __ldg(a.row_index + row0 + j) : row0 + j;
+                        v = *reinterpret_cast<const uint4*>(x + xr * ldx + col);
                     } else {
                         // token operand = SwiGLU of the previous product's fp32 K-range partials (interleaved gate/up
                         // columns): ascending sums, bf16 roundings of gate and up, bf16(silu(gate) * up)

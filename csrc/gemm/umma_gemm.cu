@@ -331,6 +331,7 @@ const char* fill_gemm_dev(const GemmArgs& h, GemmDev* dp) {
     d.out = h.out;
     d.tasks = reinterpret_cast<const int4*>(h.tasks);
     d.num_tasks = h.num_tasks;
+    d.row_index = h.x_row_index;
     d.status = h.status;
     d.w_expert_stride = static_cast<long long>(m_tiles) * (h.k / kTileK) * kWBlockBytes;
     d.out_range_stride = h.out_range_stride;
@@ -362,6 +363,7 @@ const char* umma_gemm(const GemmArgs& h, cudaStream_t stream) {
     if (h.ranges < 1 || (h.k / kTileK) % h.ranges != 0) return "K blocks must divide evenly into ranges";
     if (h.ranges > 1 && h.epilogue != 1) return "range partials are fp32";
     if (h.x_parts != nullptr && !h.rows_kernel) return "a token operand from partials needs the decode-class kernel";
+    if (h.x_row_index != nullptr && (!h.rows_kernel || h.tasks == nullptr || h.x_parts != nullptr)) return "a token row index needs grouped tasks of the decode-class kernel over bf16 rows";
     if (h.x_parts == nullptr && (reinterpret_cast<uintptr_t>(h.x) & 15) != 0) return "activation rows must be 16-byte aligned";
     if (h.x_parts != nullptr && ((reinterpret_cast<uintptr_t>(h.x_parts) & 15) != 0 || h.x_part_stride % 4 != 0 || h.x_n_parts < 1))
         return "partials of the token operand must be 16-byte aligned";

@@ -30,6 +30,9 @@ struct GemmArgs {
     const float* x_parts = nullptr;
     long long x_part_stride = 0;
     int x_n_parts = 0;
+    // rows_kernel only: token row j of a task is x[x_row_index[first x row + j]] instead of x[first x row + j]
+    // (a task's rows need not be contiguous, so a small pass multiplies each expert by its own tokens without a gather)
+    const int* x_row_index = nullptr;
     // block-scaled FP8 (fp8_gemm.cu): x and w are e4m3 bytes [rows][k]; scales per (row, 128-column block)
     const float* w_scale = nullptr;         // [experts?][n_out][k / 128]
     const float* x_scale = nullptr;         // [x_rows][k / 128]

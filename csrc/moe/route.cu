@@ -211,14 +211,18 @@ template <int PER>
 __device__ void route_small_body(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k,
                                  int renorm, int e0, int n_local, int ns, int* __restrict__ ids, float* __restrict__ wts,
                                  float* __restrict__ sg, int4* __restrict__ tasks_up, int4* __restrict__ tasks_down,
-                                 int* __restrict__ meta, int* __restrict__ slot_row, float* lg) {
+                                 int* __restrict__ meta, int* __restrict__ slot_row, int* __restrict__ row_token, float* lg) {
+    // row_token == nullptr: every task multiplies all T rows and keeps row t of its 16-row block for token t.
+    // row_token != nullptr (compact): a task multiplies only the tokens routed to its expert; block row p holds the
+    // p-th such token in ascending token order and row_token[block * 16 + p] names it.
+    __shared__ unsigned int tokmask[1024];
     __shared__ unsigned char present[1024];
     __shared__ short index_of[1024];
     __shared__ int sa[32], sb[32];
     __shared__ int sel[16 * 32];
     const int nthr = blockDim.x, nwarps = nthr >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < 1024; i += nthr) present[i] = 0;
+    for (int i = threadIdx.x; i < 1024; i += nthr) { present[i] = 0; tokmask[i] = 0u; }
     // all partial loads of an element are issued together, then added in ascending part order
     for (int i = threadIdx.x; i < T * (E + 1); i += nthr) {
         const int t = i / (E + 1), e = i % (E + 1);
@@ -247,6 +251,7 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
             wts[row * k + lane] = w;
             sel[row * 32 + lane] = e;
             present[e] = 1;
+            atomicOr(&tokmask[e], 1u << row);               // a set of token rows: the order of arrival does not matter
         }
         if (lane == 0) sg[row] = sigmoidf_(gl);
     }
@@ -272,8 +277,16 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
         if (e < E && present[e]) {
             index_of[e] = static_cast<short>(idx);
             if (e >= e0 && e < e0 + n_local) {
-                tasks_up[li] = make_int4(e - e0, 0, T, idx * 16);
-                tasks_down[li] = make_int4(e - e0, idx * 16, T, idx * 16);
+                if (row_token == nullptr) {
+                    tasks_up[li] = make_int4(e - e0, 0, T, idx * 16);
+                    tasks_down[li] = make_int4(e - e0, idx * 16, T, idx * 16);
+                } else {
+                    unsigned int m = tokmask[e];
+                    const int n = __popc(m);
+                    tasks_up[li] = make_int4(e - e0, idx * 16, n, idx * 16);
+                    tasks_down[li] = make_int4(e - e0, idx * 16, n, idx * 16);
+                    for (int p = 0; m != 0u; ++p, m &= m - 1u) row_token[idx * 16 + p] = __ffs(m) - 1;
+                }
                 ++li;
             }
             ++idx;
@@ -281,8 +294,10 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
     }
     for (int i = threadIdx.x; i < ns; i += nthr) {
         const int lt = n_active_local + i, blk = n_active + i;
-        tasks_up[lt] = make_int4(n_local + i, 0, T, blk * 16);
+        tasks_up[lt] = make_int4(n_local + i, row_token == nullptr ? 0 : blk * 16, T, blk * 16);
         tasks_down[lt] = make_int4(n_local + i, blk * 16, T, blk * 16);
+        if (row_token != nullptr)
+            for (int t = 0; t < T; ++t) row_token[blk * 16 + t] = t;
     }
     if (threadIdx.x < 8) {
         int v = 0;
@@ -294,7 +309,12 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
     const int slots = k + ns;
     for (int i = threadIdx.x; i < T * slots; i += nthr) {
         const int t = i / slots, j = i % slots;
-        slot_row[i] = (j < k ? index_of[sel[t * 32 + j]] : n_active + (j - k)) * 16 + t;
+        int row = (j < k ? index_of[sel[t * 32 + j]] : n_active + (j - k)) * 16 + t;
+        if (row_token != nullptr && j < k) {
+            const int e = sel[t * 32 + j];
+            row = index_of[e] * 16 + __popc(tokmask[e] & ((1u << t) - 1u));
+        }
+        slot_row[i] = row;
     }
 }
 
@@ -302,12 +322,13 @@ template <int PER>
 __global__ void __launch_bounds__(1024, 1)
 route_small_kernel(const float* __restrict__ logits, long long part_stride, int n_parts, int ld, int T, int E, int k, int renorm,
                    int e0, int n_local, int ns, int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sg,
-                   int4* __restrict__ tasks_up, int4* __restrict__ tasks_down, int* __restrict__ meta, int* __restrict__ slot_row) {
+                   int4* __restrict__ tasks_up, int4* __restrict__ tasks_down, int* __restrict__ meta, int* __restrict__ slot_row,
+                   int* __restrict__ row_token) {
     chain_release();
     chain_wait();
     extern __shared__ float lg[];              // [T][E + 1] logits with their K-range partials added
     route_small_body<PER>(logits, part_stride, n_parts, ld, T, E, k, renorm, e0, n_local, ns, ids, wts, sg, tasks_up, tasks_down,
-                          meta, slot_row, lg);
+                          meta, slot_row, row_token, lg);
 }
 
 // ------------------------------------------------------------------ decode-class router
@@ -324,7 +345,7 @@ constexpr int kRouterChunks = 8;               // 32-column chunks kept in fligh
 struct RouterFuse {                            // routing by the last CTA (T <= 16); ticket == nullptr: logits only
     unsigned int* ticket;
     int E, k, renorm, e0, n_local, ns;
-    int* ids; float* wts; float* sg; int4* tasks_up; int4* tasks_down; int* meta; int* slot_row;
+    int* ids; float* wts; float* sg; int4* tasks_up; int4* tasks_down; int* meta; int* slot_row; int* row_token;
 };
 
 template <int NT, int PER>
@@ -411,7 +432,7 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ w, int n_rows, int K, const
     __threadfence();
     if (threadIdx.x == 0) *f.ticket = 0u;
     route_small_body<PER>(logits, part_stride, 8, ld, T, f.E, f.k, f.renorm, f.e0, f.n_local, f.ns, f.ids, f.wts, f.sg, f.tasks_up,
-                          f.tasks_down, f.meta, f.slot_row, reinterpret_cast<float*>(dyn));
+                          f.tasks_down, f.meta, f.slot_row, f.row_token, reinterpret_cast<float*>(dyn));
 }
 
 template <int PER>
@@ -437,7 +458,7 @@ const char* moe_route(const float* logits, long long part_stride, int n_parts, i
 
 const char* moe_route_small(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
                             int n_local, int ns, int* ids, float* wts, float* sg, int* tasks_up, int* tasks_down, int* meta,
-                            int* slot_row, cudaStream_t s) {
+                            int* slot_row, int* row_token, cudaStream_t s) {
     if (T > 16 || n_local > 1024 || E > 1024 || k > 32 || ns > 32) return "route_small handles up to 16 rows and 1024 experts";
     int4* tu = reinterpret_cast<int4*>(tasks_up);
     int4* td = reinterpret_cast<int4*>(tasks_down);
@@ -450,9 +471,9 @@ const char* moe_route_small(const float* logits, long long part_stride, int n_pa
         cudaFuncSetAttribute(route_small_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1025 * 4);
         configured = true;
     }
-    if (E <= 128) launch_chained(route_small_kernel<4>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
-    else if (E <= 512) launch_chained(route_small_kernel<16>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
-    else launch_chained(route_small_kernel<32>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row);
+    if (E <= 128) launch_chained(route_small_kernel<4>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row, row_token);
+    else if (E <= 512) launch_chained(route_small_kernel<16>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row, row_token);
+    else launch_chained(route_small_kernel<32>, dim3(1), dim3(1024), sm, s, logits, part_stride, n_parts, ld, T, E, k, rn, e0, n_local, ns, ids, wts, sg, tu, td, meta, slot_row, row_token);
     return cudaGetLastError() == cudaSuccess ? nullptr : "route_small launch failed";
 }
 
@@ -483,7 +504,7 @@ static const char* launch_router(const void* w, int n_rows, int K, const void* x
 
 const char* router_rows(const void* w, int n_rows, int K, const void* x, int ldx, int T, float* logits, long long part_stride, int ld,
                         unsigned int* ticket, int E, int k, bool renorm, int e0, int n_local, int ns, int* ids, float* wts, float* sg,
-                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, cudaStream_t s) {
+                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, int* row_token, cudaStream_t s) {
     if (K % 512 != 0) return "router columns must be a multiple of 512";
     if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || ldx % 8 != 0)
         return "router operands must be 16-byte aligned";
@@ -492,7 +513,7 @@ const char* router_rows(const void* w, int n_rows, int K, const void* x, int ldx
         if (T > 16 || E > 1024 || k > 32 || ns > 32 || n_rows != E + 1) return "fused routing handles up to 16 rows and 1024 experts";
         f.ticket = ticket; f.E = E; f.k = k; f.renorm = renorm ? 1 : 0; f.e0 = e0; f.n_local = n_local; f.ns = ns;
         f.ids = ids; f.wts = wts; f.sg = sg; f.tasks_up = reinterpret_cast<int4*>(tasks_up); f.tasks_down = reinterpret_cast<int4*>(tasks_down);
-        f.meta = meta; f.slot_row = slot_row;
+        f.meta = meta; f.slot_row = slot_row; f.row_token = row_token;
     }
     if (T <= 8) return launch_router<1>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);
     if (T <= 16) return launch_router<2>(w, n_rows, K, x, ldx, T, logits, part_stride, ld, f, E, s);

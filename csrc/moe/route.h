@@ -19,7 +19,7 @@ const char* moe_route(const float* logits, long long part_stride, int n_parts, i
 // tasks_down reads the 16-row block its gate/up task wrote; both write output block i * 16.
 const char* moe_route_small(const float* logits, long long part_stride, int n_parts, int ld, int T, int E, int k, bool renorm, int e0,
                             int n_local, int ns, int* ids, float* wts, float* sg, int* tasks_up, int* tasks_down, int* meta,
-                            int* slot_row, cudaStream_t s);
+                            int* slot_row, int* row_token, cudaStream_t s);
 
 // Decode-class router: logits[8][T][ld] = K-range partials of x [T][K] (bf16) against the plain bf16
 // router rows w [n_rows][K] by warp-level mma.  With a ticket word (zero before the first call; the
@@ -27,6 +27,6 @@ const char* moe_route_small(const float* logits, long long part_stride, int n_pa
 // moe_route_small, n_rows == E + 1).
 const char* router_rows(const void* w, int n_rows, int K, const void* x, int ldx, int T, float* logits, long long part_stride, int ld,
                         unsigned int* ticket, int E, int k, bool renorm, int e0, int n_local, int ns, int* ids, float* wts, float* sg,
-                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, cudaStream_t s);
+                        int* tasks_up, int* tasks_down, int* meta, int* slot_row, int* row_token, cudaStream_t s);
 
 }  // namespace vade

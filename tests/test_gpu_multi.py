@@ -211,3 +211,78 @@ def test_token_split_of_a_prompt_over_replicas_matches_single_gpu():
         assert p.exitcode == 0
     assert outs[0][0] == ref, "the finishing replica's tokens differ from the single-GPU run"
     assert all(outs[r][1]["messages"] == 4 for r in range(1, world)), "one hand-over per layer and sending rank"
+
+
+def _serve_requests():
+    from vade_b200.runtime.sampler import Sampling
+    from vade_b200.runtime.scheduler import Request
+    return [Request(prompt=_prompt(90, seed=31), max_tokens=10, ignore_eos=True),
+            Request(prompt=_prompt(200, seed=32), max_tokens=8, ignore_eos=True, sampling=Sampling(temperature=0.8, top_p=0.9, top_k=20, seed=3)),
+            Request(prompt=_prompt(140, seed=33), max_tokens=12, ignore_eos=True)]
+
+
+def _mirror_worker(rank, world, port, q):
+    """Tensor + expert parallel serving: the scheduler runs on every rank, rank 0 takes the requests and publishes each
+    turn's intake; decode passes replay the captured per-width steps with the exchanges fused into the kernels."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    import threading
+    import time
+    from vade_b200.parallel.groups import make_parallel
+    from vade_b200.runtime.mirror import Mirror
+    from vade_b200.runtime.scheduler import Scheduler, SchedulerConfig
+    par = make_parallel(tp=world, pp=1, int_device=f"cuda:{rank}", fused=True)
+    eng = build_engine(small_gpu_config(), device=f"cuda:{rank}", seed=0, tp=world, tp_rank=par.tp_rank, comm=par.comm,
+                       slots=6, max_seq=512, prefill_chunk=128, synth_on_device=True)
+    sched = Scheduler(eng, SchedulerConfig(reserve_foreground=0, prefill_slice=128), mirror=Mirror(keepalive_s=0.5))
+    res = None
+    if rank != 0:
+        sched.run_forever()
+    else:
+        loop = threading.Thread(target=sched.run_forever, daemon=True)
+        loop.start()
+        reqs = _serve_requests()
+        for r in reqs:
+            sched.submit(r)
+        t0 = time.monotonic()
+        while any(r.state != "done" for r in reqs) and time.monotonic() - t0 < 120 and sched.fatal is None:
+            time.sleep(0.005)
+        sched.stop()
+        loop.join(60)
+        res = [list(r.output) for r in reqs]
+    eng.model.ops.check_status()
+    q.put((rank, res, sched.ticks, sched.pool.replays if sched.pool is not None else 0))
+    dist.barrier()
+    torch.cuda.synchronize()
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_mirrored_serving_on_tensor_parallel_gpus_matches_single_gpu():
+    from vade_b200.runtime.scheduler import Scheduler, SchedulerConfig
+    world = _world()
+    eng = build_engine(small_gpu_config(), device="cuda:0", seed=0, slots=6, max_seq=512, prefill_chunk=128, synth_on_device=True)
+    s = Scheduler(eng, SchedulerConfig(reserve_foreground=0, prefill_slice=128))
+    reqs = [s.submit(r) for r in _serve_requests()]
+    while any(r.state != "done" for r in reqs):
+        if not s.tick():
+            s._reap()
+    ref = [list(r.output) for r in reqs]
+    del s, eng
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mirror_worker, args=(r, world, port, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = {r: (res, ticks, replays) for r, res, ticks, replays in (q.get(timeout=240) for _ in range(world))}
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert outs[0][0] == ref, "served tokens differ from the single-GPU scheduler"
+    assert len({outs[r][1] for r in outs}) == 1, "the ranks ran different numbers of turns"
+    assert outs[0][2] > 0, "decode passes did not replay the captured steps"

@@ -56,13 +56,13 @@ class CudaOps:
         return batch.dev
 
     def _gemm(self, x, q, out, epilogue, bn, ranges, tokens, ldo, range_stride, tasks=None, meta=None, max_tasks=0,
-              ex=None, ex_offset: int = 0, local_only_from: int = -1, rows: bool = False, x_parts=None):
+              ex=None, ex_offset: int = 0, local_only_from: int = -1, rows: bool = False, x_parts=None, row_index=None):
         """ex: parallel.symm.Exchange -> the epilogue stores into every rank's buffer (+ ex_offset bytes).
         rows: decode class -> the register-dataflow kernel (NVFP4 weights, epilogue 0/1, <= 64 rows per task)."""
         nv = q.kind == "nvfp4"
         rows = bool(rows and nv and epilogue != 2 and (tasks is None or bn <= 64))
-        if x_parts is not None and not rows:
-            raise ValueError("a token operand from partials needs the decode-class kernel")
+        if (x_parts is not None or row_index is not None) and not rows:
+            raise ValueError("a token operand from partials or through a row index needs the decode-class kernel")
         self.launches += 1
         peers = ([], [], 0, 0, 0, -1) if ex is None else ([p + ex_offset for p in ex.out], ex.flags, ex.local, ex.half_stride,
                                                          ex.self_rank, local_only_from)
@@ -76,7 +76,7 @@ class CudaOps:
                               tasks, meta, max_tasks, self.status, *peers)
             return
         self.ext.gemm(x, q.tiles if nv else q.w, q.row_scale, out, q.k, q.n, nv, epilogue, bn, ranges, tokens, ldo,
-                      range_stride, tasks, meta, max_tasks, self.status, *peers, rows, x_parts)
+                      range_stride, tasks, meta, max_tasks, self.status, *peers, rows, x_parts, row_index)
 
     # ---- basic
     def embed(self, w, tokens):
@@ -205,14 +205,19 @@ class CudaOps:
         if phase == "decode" and q.kind == "plain" and q.k % 512 == 0:
             logits = torch.empty(8, T, q.n, dtype=torch.float32, device=self.device)
             self.launches += 1
+            compact = self._rows_moe(mw)
             if T <= 16 and q.n == self.cfg.num_experts + 1:
-                r = self._route_small_alloc(T, mw)
+                r = self._route_small_alloc(T, mw, compact)
                 self.ext.router_rows(q.w, h, logits, self.ticket, r.E, r.k, self.cfg.norm_topk_prob, mw.expert0, mw.n_local, r.ns,
-                                     r.ids, r.wts, r.sg, r.tasks, r.tasks_down, r.meta, r.slot_row)
+                                     r.ids, r.wts, r.sg, r.tasks, r.tasks_down, r.meta, r.slot_row, r.row_token)
                 return r
-            self.ext.router_rows(q.w, h, logits, None, 0, 0, False, 0, 0, 0, None, None, None, None, None, None, None)
-            return self.route_logits(logits, mw, 8)
-        return self.route_logits(self.linear(h, mw.router, out_fp32=True), mw, 1)
+            self.ext.router_rows(q.w, h, logits, None, 0, 0, False, 0, 0, 0, None, None, None, None, None, None, None, None)
+            return self.route_logits(logits, mw, 8, compact)
+        return self.route_logits(self.linear(h, mw.router, out_fp32=True), mw, 1, phase == "decode" and self._rows_moe(mw))
+
+    def _rows_moe(self, mw) -> bool:
+        """Both expert products of a decode-class pass run in the register-dataflow kernel (packed weights)."""
+        return mw.gate_up.kind == "nvfp4" and mw.down.kind == "nvfp4" and mw.gate_up.k % (self.DECODE_PARTS * 64) == 0
 
     def _route_base(self, T, mw, zero_meta: bool):
         cfg = self.cfg
@@ -224,26 +229,28 @@ class CudaOps:
             sg=torch.empty(T, dtype=torch.float32, device=dev), meta=meta,
             slot_row=torch.empty(T, k + ns, dtype=i32, device=dev), T=T, k=k, ns=ns, E=E, n_local=mw.n_local)
 
-    def _route_small_alloc(self, T, mw):
+    def _route_small_alloc(self, T, mw, compact: bool = False):
         """Small pass: a 16-row block per active expert of the whole model, tasks for the experts held here,
-        no gather.  The routing kernel writes all eight meta words."""
+        no gather.  The routing kernel writes all eight meta words.  compact (decode class on packed weights): a task
+        holds only the tokens routed to its expert, named by ``row_token``; otherwise every task multiplies all T rows."""
         r = self._route_base(T, mw, zero_meta=False)
         i32 = torch.int32
         r.small, r.bn = True, 16
+        r.row_token = torch.empty((min(r.E, T * r.k) + r.ns) * 16, dtype=i32, device=self.device) if compact else None
         r.max_tasks = min(mw.n_local, T * r.k) + r.ns
         r.max_rows = (min(r.E, T * r.k) + r.ns) * 16
         r.tasks = torch.empty(r.max_tasks, 4, dtype=i32, device=self.device)
         r.tasks_down = torch.empty(r.max_tasks, 4, dtype=i32, device=self.device)
         return r
 
-    def route_logits(self, logits, mw, n_parts: int = 1):
+    def route_logits(self, logits, mw, n_parts: int = 1, compact: bool = False):
         cfg = self.cfg
         T = logits.shape[-2]
         if T <= 16:
-            r = self._route_small_alloc(T, mw)
+            r = self._route_small_alloc(T, mw, compact)
             self.launches += 1
             self.ext.moe_route_small(logits, n_parts, r.E, r.k, cfg.norm_topk_prob, mw.expert0, mw.n_local, r.ns, r.ids, r.wts, r.sg,
-                                     r.tasks, r.tasks_down, r.meta, r.slot_row)
+                                     r.tasks, r.tasks_down, r.meta, r.slot_row, r.row_token)
             return r
         r = self._route_base(T, mw, zero_meta=True)
         k, ns, E = r.k, r.ns, r.E
@@ -288,7 +295,8 @@ class CudaOps:
         gu = mid = None
         if dec and mw.gate_up.k % (P * 64) == 0:
             gu = torch.empty(P, r.max_rows, I2, dtype=torch.float32, device=self.device)
-            self._gemm(xs, mw.gate_up, gu, 1, bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks, rows=True)
+            self._gemm(xs, mw.gate_up, gu, 1, bn, P, r.max_rows, I2, r.max_rows * I2, r.tasks, r.meta, r.max_tasks, rows=True,
+                       row_index=getattr(r, "row_token", None) if r.small else None)
             if not fused:
                 mid = torch.empty(r.max_rows, I2 // 2, dtype=torch.bfloat16, device=self.device)
                 self.launches += 1

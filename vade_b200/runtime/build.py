@@ -51,7 +51,10 @@ def build_engine(cfg: ModelConfig, source=None, *, device="cpu", act: torch.dtyp
     if pages is None:
         pages = slots * (-(-max_seq // 64))
     cache = Cache(cfg, plan, slots, pages, max_seq, act, dev, mtp=with_mtp)
-    return Engine(model, cache, prefill_chunk, pp_comm)
+    eng = Engine(model, cache, prefill_chunk, pp_comm)
+    if symm is not None:
+        eng.max_pass_rows = max(prefill_chunk, 64)       # the exchange buffers are sized for one prompt tile
+    return eng
 
 
 def load_engine(root: str, **kw) -> tuple:

@@ -53,6 +53,7 @@ class Engine:
         self.prefill_chunk = prefill_chunk
         self.pp = pp_comm
         self._pool = None
+        self.max_pass_rows = None        # rows one pass may hold when buffers were sized for it (fused exchanges); None = no limit
         self.device = cache.device
         self.steps = 0
 

@@ -357,11 +357,12 @@ class Scheduler:
 
     def _prefill_one(self) -> bool:
         picks, rows = [], 0
+        room = min(self.cfg.prefill_pack, self.engine.max_pass_rows or self.cfg.prefill_pack)
         for r in self.active:
             if r.state != "prefill":
                 continue
             end = self._slice_end(r)
-            if picks and rows + end - r.done_prompt > self.cfg.prefill_pack:
+            if picks and rows + end - r.done_prompt > room:
                 break                                   # admission order is kept: nobody overtakes a waiting prompt
             picks.append((r, end))
             rows += end - r.done_prompt
