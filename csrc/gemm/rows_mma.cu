@@ -94,9 +94,11 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
     if (a.tasks != nullptr) {
         chain_wait();                                      // the task list is the routing kernel's output
         waited = true;
-        active = static_cast<int>(blockIdx.y) < *a.num_tasks;
-        const int4 task = active ? a.tasks[blockIdx.y] : make_int4(0, 0, 0, 0);
-        expert = task.x; row0 = task.y; nrows = task.z; orow0 = task.w;
+        // both words are requested at once: the task array has an entry for every blockIdx.y (unused ones hold
+        // whatever the allocation held and are never acted on)
+        const int4 task = __ldg(a.tasks + blockIdx.y);
+        active = static_cast<int>(blockIdx.y) < __ldg(a.num_tasks);
+        expert = active ? task.x : 0; row0 = task.y; nrows = active ? task.z : 0; orow0 = task.w;
     } else {
         row0 = blockIdx.y * (NT * 8);
         nrows = min(NT * 8, a.tokens - row0);
@@ -116,6 +118,12 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
     if (active) {
         const uint8_t* wb = a.w_tiles + static_cast<long long>(expert) * a.w_expert_stride
                           + (static_cast<long long>(mtile) * a.kb_total + kb0) * kWBlockBytes;
+        float rs2[2];                                      // row scales of this thread's two rows, requested with the weights
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int m = mtile * kTileM + rit + 8 * r;
+            rs2[r] = m < a.n_out ? __ldg(a.row_scale + static_cast<long long>(expert) * a.rs_expert_stride + m) : 0.f;
+        }
         for (int c0 = 0; c0 < nkb; c0 += kChunk) {
             const int nc = min(kChunk, nkb - c0);
             uint32_t wq[kChunk][4], ws[kChunk][2];
@@ -253,7 +261,7 @@ rows_mma_kernel(const GemmDev a, const __nv_bfloat16* __restrict__ x, int ldx, c
         for (int r = 0; r < 2; ++r) {
             const int m = mtile * kTileM + rit + 8 * r;
             if (m >= a.n_out) continue;
-            const float rs = a.row_scale[static_cast<long long>(expert) * a.rs_expert_stride + m];
+            const float rs = rs2[r];
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
 #pragma unroll

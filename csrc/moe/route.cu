@@ -271,7 +271,9 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
     int inc = cnt, inc_local = cnt_local;
     block_scan2(inc, inc_local, sa, sb);
     const int n_active = sa[nwarps - 1], n_active_local = sb[nwarps - 1];
-    int idx = inc - cnt, li = inc_local - cnt_local;
+    // task order: the shared experts first (they hold every row of the pass, the longest tasks, so they start with
+    // the first wave of CTAs instead of forming the tail), then this rank's active routed experts by ascending id
+    int idx = inc - cnt, li = ns + inc_local - cnt_local;
     for (int j = 0; j < ept; ++j) {
         const int e = first + j;
         if (e < E && present[e]) {
@@ -293,7 +295,7 @@ __device__ void route_small_body(const float* __restrict__ logits, long long par
         }
     }
     for (int i = threadIdx.x; i < ns; i += nthr) {
-        const int lt = n_active_local + i, blk = n_active + i;
+        const int lt = i, blk = n_active + i;
         tasks_up[lt] = make_int4(n_local + i, row_token == nullptr ? 0 : blk * 16, T, blk * 16);
         tasks_down[lt] = make_int4(n_local + i, blk * 16, T, blk * 16);
         if (row_token != nullptr)

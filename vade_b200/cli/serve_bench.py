@@ -3,6 +3,7 @@ aggregate output tokens per second, TTFT percentiles, and a check that sampled r
 
     python -m vade_b200.cli.serve_bench [--config qwen3-next-80b-a3b] [--requests 64] [--min-prompt 512] [--max-prompt 4096]
                                         [--output 256] [--temperature 0.7] [--top-p 0.95] [--top-k 0] [--check 4] [--max-active 16]
+    python -m vade_b200.cli.serve_bench --step-times          # device time of the pooled decode step at widths 1..16
 
 Prompt lengths are uniform on [min, max] from seed 2, token ids uniform-random, every request carries its own sampler
 seed.  All requests are submitted at time zero; TTFT is measured from submission to the first emitted token, so it
@@ -66,6 +67,38 @@ def run(engine, n_requests: int, min_prompt: int, max_prompt: int, n_out: int, t
     return res
 
 
+def step_times(engine, out=print, rows: int = 16, prompt: int = 1024) -> dict:
+    """Device time of the pooled decode step at every captured width (CUDA events over 20 replays after 3 warm-up
+    replays), on ``rows`` sequences prefilled with prompts of ``prompt`` + 64 i tokens."""
+    from ..runtime.engine import Sequence
+    V = engine.model.cfg.vocab_size
+    g = torch.Generator().manual_seed(3)
+    seqs = [Sequence(engine.cache.new_slot()) for _ in range(rows)]
+    items = [(s, torch.randint(0, V, (prompt + 64 * i,), generator=g).tolist(), False) for i, s in enumerate(seqs)]
+    for k in range(0, rows, 4):
+        engine.prefill_many(items[k:k + 4])
+    pool = engine.decode_pool()
+    res = {}
+    for w in pool.WIDTHS:
+        if w > rows:
+            break
+        sl, pos, tok = [s.slot for s in seqs[:w]], [len(s.tokens) for s in seqs[:w]], [5 + i for i in range(w)]
+        for _ in range(3):
+            pool.step(sl, tok, pos)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(20):
+            pool.step(sl, tok, [p + i + 1 for p in pos])
+        e1.record()
+        torch.cuda.synchronize()
+        res[w] = round(e0.elapsed_time(e1) / 20, 3)
+    for s in seqs:
+        engine.cache.free_slot(s.slot)
+    out(json.dumps({"decode_step_ms_by_width": res}))
+    return res
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--config", default="qwen3-next-80b-a3b")
@@ -79,6 +112,7 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=0, help="1..64 takes the compact device top-k path; 0 reads the whole logits row per sampled token")
     ap.add_argument("--check", type=int, default=4)
     ap.add_argument("--max-active", type=int, default=16)
+    ap.add_argument("--step-times", action="store_true", help="GPU: only time the pooled decode step at every captured width")
     a = ap.parse_args(argv)
     from ..config import NAMED_CONFIGS
     from ..runtime.build import build_engine
@@ -86,6 +120,10 @@ def main(argv=None) -> int:
     on_gpu = a.device.startswith("cuda")
     eng = build_engine(cfg, device=a.device, slots=a.max_active + 2, max_seq=a.max_prompt + a.output + 64, synth_on_device=on_gpu,
                        with_mtp=False, prefill_chunk=2048 if on_gpu else 64)
+    if a.step_times:
+        step_times(eng, rows=a.max_active)
+        eng.model.ops.check_status()
+        return 0
     res = run(eng, a.requests, a.min_prompt, a.max_prompt, a.output, a.temperature, a.top_p, a.check, a.max_active, top_k=a.top_k)
     if on_gpu:
         eng.model.ops.check_status()
