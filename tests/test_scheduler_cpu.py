@@ -102,3 +102,31 @@ def test_packed_prompt_pass_gives_the_ids_of_one_prompt_per_pass_in_fewer_passes
     packed, passes_packed = serve(256)      # up to 256 prompt rows per pass
     assert packed == alone
     assert passes_packed < passes_alone
+
+
+def test_lookup_drafting_keeps_the_ids_whether_the_copied_run_is_right_or_wrong(engine):
+    prompt = _ids(50, 90)
+    plain = Scheduler(engine, SchedulerConfig(reserve_foreground=0))
+    a = plain.submit(Request(prompt=list(prompt), max_tokens=20, ignore_eos=True))
+    _drain(plain, [a])
+    full = list(prompt) + list(a.output)
+
+    class Copy:                                             # stands in for a text that repeats: proposes from a fixed continuation
+        def __init__(self, text):
+            self.text = text
+
+        def propose(self, tokens, depth):
+            return list(self.text[len(tokens):len(tokens) + depth])
+
+    for text, all_kept in ((full, True), (full[:55] + [(t + 1) % 4000 for t in full[55:]], False)):
+        s = Scheduler(engine, SchedulerConfig(reserve_foreground=0))
+        b = s.submit(Request(prompt=list(prompt), max_tokens=20, ignore_eos=True, draft="lookup", mtp_depth=4, lookup=Copy(text)))
+        _drain(s, [b])
+        assert list(b.output) == list(a.output)
+        assert b.drafted > 0
+        assert (b.accepted == b.drafted) == all_kept, "a right copy is kept whole, a wrong one is rolled back"
+    # the real index on a text without repetition proposes nothing and the chat decodes plainly
+    s = Scheduler(engine, SchedulerConfig(reserve_foreground=0))
+    c = s.submit(Request(prompt=list(prompt), max_tokens=20, ignore_eos=True, draft="lookup"))
+    _drain(s, [c])
+    assert list(c.output) == list(a.output)

@@ -368,3 +368,14 @@ def test_adaptive_draft_depth_follows_acceptance_and_is_a_cost_decision_only():
         d = c.choose() or 1
         c.record(d, min(d, 2))                           # the third drafted token always misses
     assert c.choose() == 2
+
+
+def test_prompt_lookup_proposes_the_continuation_of_the_longest_earlier_suffix():
+    from vade_b200.runtime.draft import PromptLookup
+    lk = PromptLookup()
+    text = [1, 2, 3, 4, 5, 6, 7, 9, 9, 2, 3, 4]
+    assert lk.propose(text, 3) == [5, 6, 7]                 # "2 3 4" occurred before, followed by 5 6 7
+    assert lk.propose(text + [5], 2) == [6, 7]              # the index grows with the text; now "2 3 4 5" matches
+    assert lk.propose([1, 2, 3], 4) == []                   # nothing earlier to copy from
+    assert lk.propose(text[:10], 2) == []                   # after a truncation the index is rebuilt: "9 2" has no earlier match
+    assert lk.propose([7, 8, 7, 8, 7, 8], 5) == [7, 8]      # the latest earlier occurrence wins and the copy stops at the end of the text

@@ -12,6 +12,7 @@ that could change its arithmetic if a rule of the exactness contract were broken
     slices S          prompt processed in tiles of S rows instead of the default
     prefix cache      second turn resumes from a 64-token checkpoint of the first turn
     draft D           exact speculative decoding with D drafted tokens per cycle (accept and rollback happen)
+    lookup draft      drafts copied from the chat's own earlier text (n-gram continuation), verified the same way
     sampled           seeded sampling (temperature / top-p / top-k): same seed -> same ids alone and batched
     cancelled peer    a neighbour is cancelled in the middle of the batch (the host-side "poison" case): the
                       survivors' ids are unchanged
@@ -133,6 +134,11 @@ def run_gate(engine, tokens: int = 24, prompt_len: int = 150, out=print, graph: 
             r = one(s, draft="strict", mtp_depth=depth)
             _drain(s, [r])
             check(f"draft {depth or 'auto'} ({r.accepted}/{r.drafted} kept)", r.output, ref)
+
+    s = sched()
+    r = one(s, draft="lookup")
+    _drain(s, [r])
+    check(f"lookup draft ({r.accepted}/{r.drafted} kept)", r.output, ref)
 
     samp = dict(temperature=0.8, top_p=0.9, top_k=40, seed=1234)
     s = sched()

@@ -79,3 +79,38 @@ class DepthChooser:
                 self.tried[i] += 1.0
                 if i < accepted:
                     self.kept[i] += 1.0
+
+
+class PromptLookup:
+    """Draft tokens copied from the chat's own text: if the last n tokens (n = 4..2) occurred earlier, propose what
+    followed them then.  Summaries, code edits and quoted passages repeat long runs of their prompt, and a proposed
+    run costs no model pass at all.  Like every draft it is only a proposal: the trunk verifies each row itself.
+    The index maps every n-gram to the position after its LATEST earlier occurrence and grows as tokens are appended.
+    Parity: engine/crates/engine/src/flash/next_lookup.rs:29-60 (suffix hashes over the session's tokens)."""
+
+    def __init__(self, max_ngram: int = 4, min_ngram: int = 2):
+        self.max_n, self.min_n = max_ngram, min_ngram
+        self.after: dict = {}               # n-gram -> index of the token after its latest indexed occurrence
+        self.indexed = 0                    # tokens[:indexed] have been entered as n-gram ENDS
+
+    def _grow(self, tokens: list, upto: int) -> None:
+        for end in range(self.indexed, upto):                 # n-grams ending at tokens[end]
+            for n in range(self.min_n, self.max_n + 1):
+                if end + 1 >= n:
+                    self.after[tuple(tokens[end + 1 - n:end + 1])] = end + 1
+        self.indexed = max(self.indexed, upto)
+
+    def propose(self, tokens: list, depth: int) -> list:
+        """Up to ``depth`` tokens that followed the longest earlier occurrence of the current suffix of ``tokens``."""
+        n_tok = len(tokens)
+        if depth <= 0 or n_tok < self.min_n + 1:
+            return []
+        if self.indexed > n_tok - 1:                          # the text was truncated (rollback): start over
+            self.after.clear()
+            self.indexed = 0
+        self._grow(tokens, n_tok - 1)                          # every n-gram that ends before the last token
+        for n in range(min(self.max_n, n_tok), self.min_n - 1, -1):
+            at = self.after.get(tuple(tokens[n_tok - n:]))
+            if at is not None and at < n_tok:
+                return list(tokens[at:at + depth])
+        return []

@@ -30,7 +30,7 @@ import torch
 from ..utils import events
 from .cache import PAGE, OutOfPages
 from .engine import Engine, Sequence
-from .draft import MAX_DEPTH, DepthChooser
+from .draft import MAX_DEPTH, DepthChooser, PromptLookup
 from .sampler import Sampling, sample
 
 
@@ -56,7 +56,7 @@ class Request:
     stop_ids: tuple = ()
     stop_strings: tuple = ()
     ignore_eos: bool = False
-    draft: str = "plain"                 # plain | strict (exact greedy drafting)
+    draft: str = "plain"                 # plain | strict (exact greedy drafting with the MTP block) | lookup (drafts copied from the chat's own text)
     mtp_depth: int = 0
     cache: bool = False                  # opt in to the prefix cache (read and write)
     cache_salt: str = ""
@@ -81,6 +81,7 @@ class Request:
     pages_reserved: int = 0
     text_tail: str = ""
     chooser: DepthChooser = field(default_factory=DepthChooser)      # adaptive draft depth (runtime/draft.py)
+    lookup: PromptLookup = field(default_factory=PromptLookup)       # n-gram index of the chat's tokens (draft == "lookup")
 
     def push(self, ev) -> None:
         self.events.append(ev)
@@ -418,8 +419,9 @@ class Scheduler:
                 rows_of.remove(r)
         if not rows_of:
             return True
-        solo_draft = (len(rows_of) == 1 and rows_of[0].draft == "strict" and rows_of[0].sampling.plain_greedy
-                      and eng.model.w.mtp is not None)
+        lone = rows_of[0] if len(rows_of) == 1 else None
+        solo_draft = lone is not None and lone.sampling.plain_greedy and (
+            (lone.draft == "strict" and eng.model.w.mtp is not None) or lone.draft == "lookup")
         if solo_draft:
             self._draft_cycle(rows_of[0])
             return True
@@ -446,20 +448,24 @@ class Scheduler:
         return True
 
     def _draft_cycle(self, r: Request) -> None:
-        """Exact greedy drafting for a lone chat: MTP proposes, the trunk verifies, the longest
-        matching prefix is kept (engine/crates/engine/src/draft.rs:822-828)."""
+        """Exact greedy drafting for a lone chat: the MTP block (or the chat's own text, draft == "lookup") proposes,
+        the trunk verifies, the longest matching prefix is kept (engine/crates/engine/src/draft.rs:822-828)."""
         eng = self.engine
         seq = r.seq
         remaining = r.max_tokens - len(r.output)
-        if r.mtp_depth:
-            depth = max(0, min(r.mtp_depth, remaining - 1))                      # the client fixed the depth
+        by_lookup = r.draft == "lookup"
+        if by_lookup:
+            drafts = r.lookup.propose(seq.tokens + [r.next_token], max(0, min(r.mtp_depth or MAX_DEPTH, remaining - 1)))
         else:
-            depth = r.chooser.choose(max(0, min(MAX_DEPTH, remaining - 1)))       # adaptive: a cost decision, never a token decision
-        drafts = eng.propose(seq, r.next_token, depth) if depth > 0 else []
+            if r.mtp_depth:
+                depth = max(0, min(r.mtp_depth, remaining - 1))                      # the client fixed the depth
+            else:
+                depth = r.chooser.choose(max(0, min(MAX_DEPTH, remaining - 1)))       # adaptive: a cost decision, never a token decision
+            drafts = eng.propose(seq, r.next_token, depth) if depth > 0 else []
         rows = [r.next_token] + drafts
         snap = eng.cache.snapshot(seq.slot) if drafts else None
         x, h = eng.step([seq], [rows])
-        targets = [int(t) for t in eng.model.greedy(h)]
+        targets = eng.read_ints(eng.model.greedy(h))
         keep = 1
         while keep < len(rows) and rows[keep] == targets[keep - 1]:
             keep += 1
@@ -469,11 +475,12 @@ class Scheduler:
         prev_x = seq.last_x
         seq.tokens += rows[:keep]
         eng.cache.length[seq.slot] = len(seq.tokens)
-        eng._mtp_catch_up(seq, rows[:keep], prev_x, x[:keep])
+        if not by_lookup:
+            eng._mtp_catch_up(seq, rows[:keep], prev_x, x[:keep])
         seq.last_x = x[keep - 1:keep].clone()
         r.drafted += len(drafts)
         r.accepted += keep - 1
-        if not r.mtp_depth and drafts:
+        if not by_lookup and not r.mtp_depth and drafts:
             r.chooser.record(len(drafts), keep - 1)
         for t in rows[1:keep]:
             if self._emit(r, t):

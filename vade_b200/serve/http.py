@@ -108,7 +108,7 @@ class ApiServer:
                 if path == "/v1/models":
                     return self._send(h, 200, {"object": "list", "data": [{"id": self.model_name, "object": "model", "owned_by": "vade-b200"}]})
                 if path == "/v1/capabilities":
-                    return self._send(h, 200, {"apis": ["chat", "completions", "responses", "messages"], "draft": ["plain", "strict"],
+                    return self._send(h, 200, {"apis": ["chat", "completions", "responses", "messages"], "draft": ["plain", "strict", "lookup"],
                                                "context": self.sched.engine.cache.max_pages * 64, "max_output": self.max_output,
                                                "prefix_cache": True, "token_ids": True})
                 if path == "/v1/events":
@@ -173,7 +173,7 @@ class ApiServer:
         draft = req.draft
         if draft == "auto":
             draft = "strict" if (req.sampling.plain_greedy and self.sched.engine.model.w.mtp is not None) else "plain"
-        if draft == "strict" and not req.sampling.plain_greedy:
+        if draft in ("strict", "lookup") and not req.sampling.plain_greedy:
             draft = "plain"
         sr = Request(prompt=ids, max_tokens=req.max_tokens, sampling=req.sampling, stop_strings=req.stop,
                      ignore_eos=req.ignore_eos, draft=draft, mtp_depth=req.mtp_depth, cache=req.cache,

@@ -46,7 +46,7 @@ class GenRequest:
     stop: tuple = ()
     sampling: Sampling = field(default_factory=Sampling)
     sampled: bool = False                  # the client named a sampling field
-    draft: str = "auto"                    # auto | plain | strict
+    draft: str = "auto"                    # auto | plain | strict | lookup
     mtp_depth: int = 0
     cache: bool = False
     cache_salt: str = ""
@@ -102,7 +102,7 @@ def _common(obj: dict, req: GenRequest, defaults: Sampling, max_output: int) -> 
     so = obj.get("stream_options") or {}
     req.include_usage = bool(so.get("include_usage", False)) if isinstance(so, dict) else False
     draft = obj.get("draft", "auto")
-    _need(draft in ("auto", "plain", "strict", "sampled"), "draft must be plain, strict, sampled or auto")
+    _need(draft in ("auto", "plain", "strict", "sampled", "lookup"), "draft must be plain, strict, lookup, sampled or auto")
     req.draft = "strict" if draft == "sampled" else draft
     depth = obj.get("mtp_depth", 0)
     _need(isinstance(depth, int) and 0 <= depth <= 7, "mtp_depth must be 0..7")
