@@ -1,6 +1,8 @@
 #!/usr/bin/env python
 """Headline benchmark: batch-1 greedy decode tokens/s (and 8192-token TTFT) of the
-Qwen3-Next-80B-A3B-shaped hybrid MoE in NVFP4 on N B200s of one node (tensor + expert parallel).
+Qwen3-Next-80B-A3B-shaped hybrid MoE in NVFP4 on N B200s of one node.  With N > 1 the prompt is split by tokens
+over whole-model replicas and rank 0 decodes (--parallel cp); --parallel pp / tp run the layer pipeline and the
+tensor + expert parallel layouts.
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -95,10 +97,10 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="tensor/expert-parallel exchanges: fused into the kernels over peer memory, or NCCL collectives (baseline)")
-    ap.add_argument("--parallel", default="pp", choices=["pp", "tp", "cp"],
-                    help="how N > 1 GPUs serve the one chat: pp = layer pipeline (residual rows hop between stages, prompt tiles "
-                         "overlap across stages), tp = tensor + expert parallel with the exchanges named by --comm, cp = whole-model "
-                         "replicas that split the prompt by tokens and hand each layer's cache state on (rank 0 then decodes alone)")
+    ap.add_argument("--parallel", default="cp", choices=["cp", "pp", "tp"],
+                    help="how N > 1 GPUs serve the one chat: cp = whole-model replicas that split the prompt by tokens and hand each "
+                         "layer's cache state on (rank 0 then decodes alone), pp = layer pipeline (residual rows hop between stages, "
+                         "prompt tiles overlap across stages), tp = tensor + expert parallel with the exchanges named by --comm")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
