@@ -46,6 +46,14 @@ def _worker(rank, world, port, q):
     par = make_parallel(tp=world, pp=1)
     eng = build_engine(tiny_config(), seed=0, tp=world, tp_rank=par.tp_rank, comm=par.comm, slots=4, max_seq=512, prefill_chunk=64)
     mirror = Mirror(keepalive_s=0.2)
+    from vade_b200.runtime.mirror import AgreementError, startup_agreement
+    agreed = startup_agreement(mirror.group, same={"config": "tiny", "draft_block": True}, least={"slots": 3 + rank, "pages": 100 - rank})
+    assert agreed == {"slots": 3, "pages": 99}
+    try:
+        startup_agreement(mirror.group, same={"checkpoint": f"sha-{rank}"})
+        raise SystemExit("ranks with different checkpoints were allowed to start")
+    except AgreementError as e:
+        assert "checkpoint" in str(e) and "rank 1" in str(e)
     sched = Scheduler(eng, SchedulerConfig(reserve_foreground=0, max_active=3, prefix_cache_entries=4), mirror=mirror)
     if rank != 0:
         sched.run_forever()                                  # returns when the leader publishes stop

@@ -1,0 +1,79 @@
+"""`serve --tp 2` as two real processes (gloo, CPU): rank 0 answers HTTP, rank 1 follows its turns; replies carry the
+ids of the one-process server and the receipt names the layout."""
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+
+import torch
+
+from vade_b200.checkpoint.synth import write_checkpoint
+from vade_b200.config import tiny_config
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _post(port, obj):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", json.dumps(obj).encode(), {"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        return json.loads(r.read().decode())
+
+
+def _wait_ready(port, proc, limit=120.0):
+    t0 = time.monotonic()
+    while time.monotonic() - t0 < limit:
+        if proc.poll() is not None:
+            raise AssertionError("the server exited during start-up")
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                if r.status == 200:
+                    return
+        except Exception:
+            time.sleep(0.3)
+    raise AssertionError("the server did not come up")
+
+
+def _ids(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 4000, (n,), generator=g).tolist()
+
+
+def _serve(cmd, port, bodies):
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, start_new_session=True)
+    try:
+        _wait_ready(port, proc)
+        return [_post(port, b) for b in bodies]
+    finally:
+        os.killpg(proc.pid, signal.SIGTERM)                  # exactly the process group this test started
+        try:
+            proc.wait(20)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+
+
+def test_two_rank_server_answers_like_the_one_process_server(tmp_path):
+    root = str(tmp_path / "ckpt")
+    write_checkpoint(tiny_config(), root, seed=0, dtype=torch.float32)
+    bodies = [{"prompt": _ids(70, 1), "max_tokens": 10, "ignore_eos": True, "draft": "plain"},
+              {"prompt": _ids(33, 2), "max_tokens": 6, "ignore_eos": True, "temperature": 0.7, "top_k": 20, "seed": 5}]
+    common = ["--device", "cpu", "--slots", "4", "--context", "512", "--prefill-chunk", "64", "--cache-entries", "2"]
+    p1 = _free_port()
+    one = _serve([sys.executable, "-m", "vade_b200.cli.main", "serve", root, "--port", str(p1)] + common, p1, bodies)
+    p2 = _free_port()
+    two = _serve([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                  "--master-port", str(_free_port()), "-m", "vade_b200.cli.main", "serve", root, "--port", str(p2), "--tp", "2"] + common,
+                 p2, bodies)
+    for a, b in zip(one, two):
+        assert a["choices"][0]["token_ids"] == b["choices"][0]["token_ids"]
+    assert two[0]["vade"]["world"] == 2 and two[0]["vade"]["parallel"]["tp"] == 2

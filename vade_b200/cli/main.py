@@ -118,7 +118,21 @@ def cmd_serve(a) -> int:
         kw = dict(tp=a.tp, tp_rank=par.tp_rank, comm=par.comm)
     eng, tok, receipt = load_engine(a.model, device=device, slots=a.slots + 1 + a.cache_entries, max_seq=a.context,
                                     prefill_chunk=a.prefill_chunk, **kw)
-    sched = Scheduler(eng, SchedulerConfig(max_active=a.slots, prefill_slice=a.prefill_chunk, prefix_cache_entries=a.cache_entries),
+    slots = a.slots
+    if mirror is not None:
+        from dataclasses import asdict
+        from ..runtime.mirror import startup_agreement
+        from ..utils.env import flag
+        cfgd = asdict(eng.cfg)
+        agreed = startup_agreement(mirror.group,
+                                   same={"checkpoint": receipt.get("fingerprint"), "config": json.dumps(cfgd, sort_keys=True, default=str),
+                                         "draft_block": eng.model.w.mtp is not None, "ops": eng.model.ops.name,
+                                         "build": _ext.source_stamp() if on_gpu else None, "tp": a.tp, "comm": a.comm,
+                                         "prefill_chunk": a.prefill_chunk, "cache_entries": a.cache_entries,
+                                         "decode_graphs": flag("VADE_DECODE_GRAPHS", True), "eos": tok.eos_id},
+                                   least={"slots": a.slots, "pages": eng.cache.alloc.total, "context": eng.cache.max_pages * 64})
+        slots = agreed["slots"]
+    sched = Scheduler(eng, SchedulerConfig(max_active=slots, prefill_slice=a.prefill_chunk, prefix_cache_entries=a.cache_entries),
                       eos_id=tok.eos_id, detokenize=tok.decode, mirror=mirror)
     if not leader:
         sched.run_forever()          # follows the leader's turns until it publishes stop

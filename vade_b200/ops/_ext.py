@@ -76,5 +76,10 @@ def load():
     return build()
 
 
+def source_stamp() -> str:
+    """Digest of the kernel sources the loaded object was built from (equal on ranks that run the same kernels)."""
+    return _stamp()
+
+
 def so_path() -> str:
     return os.path.join(_OUT, _NAME + ".so")

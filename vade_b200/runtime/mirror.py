@@ -43,3 +43,28 @@ class Mirror:
         box = [None]
         dist.broadcast_object_list(box, src=self.leader_rank, group=self.group)
         return box[0]
+
+
+class AgreementError(RuntimeError):
+    pass
+
+
+def startup_agreement(group, same: dict, least: dict | None = None) -> dict:
+    """Every serving rank publishes what it loaded before the first pass; the job starts only if they agree.
+
+    ``same``: values that must be equal on every rank (checkpoint fingerprint, model dimensions, weight format, draft
+    block present, kernel build stamp, switches that change arithmetic).  ``least``: capacities of which the job takes
+    the minimum over ranks (sequence slots, KV pages, context), so that every rank admits exactly the same requests.
+    Returns the agreed capacities.  A mismatch raises the same error on every rank, naming the key and the ranks.
+    Parity: engine/crates/tp/src/bin/flash-serve.rs:385-390,416-424,460-477 (precision / MTP bytes, residency flags
+    and limits gathered at start-up), engine/crates/tp/src/startup_pool.rs (`agree`: least session count and pool)."""
+    least = least or {}
+    box = [None] * dist.get_world_size(group)
+    dist.all_gather_object(box, {"same": same, "least": least}, group=group)
+    for key in sorted(box[0]["same"]):
+        vals = [b["same"].get(key) for b in box]
+        if any(v != vals[0] for v in vals):
+            raise AgreementError(f"ranks disagree on {key}: " + ", ".join(f"rank {i}: {v!r}" for i, v in enumerate(vals)))
+    if any(set(b["same"]) != set(box[0]["same"]) or set(b["least"]) != set(box[0]["least"]) for b in box):
+        raise AgreementError("ranks published different sets of start-up keys")
+    return {key: min(b["least"][key] for b in box) for key in box[0]["least"]}
