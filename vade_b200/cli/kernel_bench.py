@@ -257,6 +257,7 @@ CASES = {
     "attn_decode_8192": lambda ops: case_attn_decode(ops),
     "moe_prefill_2048": lambda ops: case_moe(ops, 2048, "prefill"),
     "moe_decode_1": lambda ops: case_moe(ops, 1, "decode"),
+    "moe_decode_16": lambda ops: case_moe(ops, 16, "decode"),
     "gemm_gdn_in_proj_decode": lambda ops: case_gemm(ops, "NVFP4 12352x2048, 1 row, decode class", 12352, 2048, 1, phase="decode"),
     "gemm_gdn_in_proj_verify8": lambda ops: case_gemm(ops, "NVFP4 12352x2048, 8 rows, decode class", 12352, 2048, 8, phase="decode"),
     "gemm_qkv_decode": lambda ops: case_gemm(ops, "NVFP4 9216x2048, 1 row, decode class", 9216, 2048, 1, phase="decode"),
