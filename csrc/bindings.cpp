@@ -275,6 +275,35 @@ void gdn_prefill(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, t
                             static_cast<int>(kd), static_cast<int>(vd), static_cast<float>(eps), gate_silu, stream_of(proj)));
 }
 
+// The prompt-class GDN with full 64-row chunks in the chunk form.  ranges: int32 [4][n_seq] = head_start, head_end, tail_start,
+// tail_end (row ranges of the token scan before the first and after the last chunk boundary of each sequence).
+void gdn_prefill_chunked(torch::Tensor proj, torch::Tensor conv_w, torch::Tensor hist, torch::Tensor state, torch::Tensor a_log,
+                         torch::Tensor dt_bias, torch::Tensor norm_w, torch::Tensor row_seq, torch::Tensor seq_slot, torch::Tensor seq_start,
+                         int64_t n_seq, torch::Tensor scratch, torch::Tensor out, int64_t kh, int64_t vh, int64_t kd, int64_t vd, double eps,
+                         bool gate_silu, torch::Tensor ranges, bool any_head, bool any_tail, torch::Tensor chunk_row0, torch::Tensor seq_chunk,
+                         int64_t n_chunks, torch::Tensor W, torch::Tensor U, torch::Tensor P, torch::Tensor CL) {
+    const int64_t rows = proj.size(0);
+    need(proj.dim() == 2 && proj.scalar_type() == torch::kBFloat16 && proj.stride(1) == 1 && scratch.scalar_type() == torch::kFloat32 &&
+         scratch.numel() >= rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh && out.scalar_type() == torch::kBFloat16 && out.is_contiguous(),
+         "gdn_prefill arguments");
+    need(ranges.is_cuda() && ranges.scalar_type() == torch::kInt32 && ranges.is_contiguous() && ranges.dim() == 2 && ranges.size(0) == 4 &&
+         ranges.size(1) == n_seq && chunk_row0.scalar_type() == torch::kInt32 && chunk_row0.numel() >= n_chunks &&
+         seq_chunk.scalar_type() == torch::kInt32 && seq_chunk.numel() == n_seq + 1, "chunk tables");
+    need(W.scalar_type() == torch::kFloat32 && W.is_contiguous() && W.numel() >= n_chunks * vh * 64 * 128 && U.scalar_type() == torch::kFloat32 &&
+         U.is_contiguous() && U.numel() >= n_chunks * vh * 64 * 128 && P.scalar_type() == torch::kFloat32 && P.is_contiguous() &&
+         P.numel() >= n_chunks * vh * 64 * 64 && CL.scalar_type() == torch::kFloat32 && CL.numel() >= n_chunks * vh * 64, "chunk scratch");
+    c10::cuda::CUDAGuard guard(proj.device());
+    const int* rg = ranges.data_ptr<int>();
+    check(vade::gdn_prefill_chunked(proj.data_ptr(), static_cast<int>(proj.stride(0)), static_cast<int>(rows), conv_w.data_ptr<float>(),
+                                    hist.data_ptr<float>(), state.data_ptr<float>(), a_log.data_ptr<float>(), dt_bias.data_ptr<float>(),
+                                    norm_w.data_ptr<float>(), row_seq.data_ptr<int>(), seq_slot.data_ptr<int>(), seq_start.data_ptr<int>(),
+                                    static_cast<int>(n_seq), scratch.data_ptr<float>(), out.data_ptr(), static_cast<int>(kh),
+                                    static_cast<int>(vh), static_cast<int>(kd), static_cast<int>(vd), static_cast<float>(eps), gate_silu,
+                                    rg, rg + n_seq, any_head, rg + 2 * n_seq, rg + 3 * n_seq, any_tail, chunk_row0.data_ptr<int>(),
+                                    seq_chunk.data_ptr<int>(), static_cast<int>(n_chunks), W.data_ptr<float>(), U.data_ptr<float>(),
+                                    P.data_ptr<float>(), CL.data_ptr<float>(), stream_of(proj)));
+}
+
 void attn_prep(torch::Tensor qkv, int64_t nq, int64_t nkv, int64_t hd, torch::Tensor q_norm, torch::Tensor k_norm,
                torch::Tensor positions, torch::Tensor row_slot, torch::Tensor block_table, torch::Tensor q_out, torch::Tensor gate_out,
                torch::Tensor k_pages, torch::Tensor v_pages, int64_t rot, double theta, double eps) {
@@ -412,6 +441,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("act_quant_fp8", &act_quant_fp8);
     m.def("gdn_scan", &gdn_scan);
     m.def("gdn_prefill", &gdn_prefill);
+    m.def("gdn_prefill_chunked", &gdn_prefill_chunked);
     m.def("attn_prep", &attn_prep);
     m.def("attn_rows", &attn_rows);
     m.def("attn_prefill", &attn_prefill);

@@ -232,7 +232,9 @@ __device__ __forceinline__ void cp_async_f(void* dst, const void* src, int bytes
 __global__ void __launch_bounds__(kLeanCols * kLeanParts)
 gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                      const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
-                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, float* __restrict__ o_out, int kh, int vh) {
+                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ seq_end,
+                     float* __restrict__ o_out, int kh, int vh) {
+    // rows [seq_start[b], seq_end[b]) of sequence b (seq_end == nullptr: up to seq_start[b + 1])
     chain_release();
     chain_wait();
     __shared__ __align__(16) float qk[kLeanRing][2 * kD];          // [slot][q(128) | k(128)]
@@ -247,7 +249,7 @@ gdn_scan_lean_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
     // thread `part` owns state rows 4 * (part + 16 * jj) + c (jj in 0..1, c in 0..3): the sixteen lanes of a column
     // read sixteen consecutive float4 of k / q, which is bank-conflict free (the other half warp reads the same words)
     const int slot = seq_slot[b];
-    const int r0 = seq_start[b], r1 = seq_start[b + 1];
+    const int r0 = seq_start[b], r1 = seq_end != nullptr ? seq_end[b] : seq_start[b + 1];
     if (r0 >= r1) return;
     float S[kLeanRows];
     float* sp = state + ((static_cast<long long>(slot) * vh + vhead) * kD) * kD + col;
@@ -337,6 +339,289 @@ gdn_post_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ p
     out[(static_cast<long long>(row) * vh + h) * kD + j] = __float2bfloat16_rn(x * rsqrtf(tot / kD + eps) * norm_w[j] * gz);
 }
 
+// ---------------------------------------------------------------- chunk form of the prompt class (64-row chunks)
+// With d_i the decay of row i, cl_i = sum_{l <= i} log d_l inside the chunk, S_0 the state before the chunk:
+//   L_ij = beta_i e^(cl_i - cl_j) (k_i . k_j)  (j < i),   T = (I + L)^-1,
+//   W = T diag(beta e^cl) K,   U_v = T diag(beta) V,   P_ij = e^(cl_i - cl_j) (q_i . k_j)  (j <= i)      [no state needed]
+//   U = U_v - W S_0,   O = diag(e^cl) Q S_0 + P U,   S_64 = e^(cl_63) S_0 + (diag(e^(cl_63 - cl)) K)^T U   [64 rows per step]
+// which is the token recurrence S_i = d_i S_(i-1) + k_i u_i^T, u_i = beta_i (v_i - (d_i S_(i-1))^T k_i), o_i = S_i^T q_i
+// written for 64 rows at once.  Chunks start at absolute multiples of 64 tokens, every sum has a fixed order, and a
+// chunk's arithmetic depends only on its own rows and S_0: the bits do not depend on how a prompt is cut into calls.
+constexpr int kC = 64;
+constexpr int kPadD = kD + 4;          // row stride of [64][128] tiles in shared memory (conflict-free float4 rows)
+constexpr int kPadC = kC + 4;
+
+// grid = (chunks, value heads), 256 threads.  W, U_v: [chunk][vh][64][128]; P: [chunk][vh][64][64]; CL: [chunk][vh][64].
+__global__ void __launch_bounds__(256)
+gdn_chunk_prepare_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                         const float* __restrict__ beta, const float* __restrict__ decay, const int* __restrict__ chunk_row0,
+                         int kh, int vh, float* __restrict__ Wg, float* __restrict__ Ug, float* __restrict__ Pg, float* __restrict__ CLg) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(16) float csm[];
+    float* Ks = csm;                         // [64][132]
+    float* Qs = Ks + kC * kPadD;             // [64][132] q rows, later the v rows
+    float* Ls = Qs + kC * kPadD;             // [64][68]
+    float* Ts = Ls + kC * kPadC;             // [64][68]
+    float* cl = Ts + kC * kPadC;             // [64]
+    float* bt = cl + kC;                     // [64]
+    float* eg = bt + kC;                     // [64] e^cl
+    const int c = blockIdx.x, h = blockIdx.y, khd = h / (vh / kh);
+    const int row0 = chunk_row0[c];
+    const int t = threadIdx.x;
+    for (int p = t; p < kC * (kD / 4); p += 256) {
+        const int r = p / (kD / 4), q4 = p % (kD / 4);
+        const long long src = (static_cast<long long>(row0 + r) * kh + khd) * kD + q4 * 4;
+        *reinterpret_cast<float4*>(Ks + r * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(kn + src);
+        *reinterpret_cast<float4*>(Qs + r * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(qn + src);
+    }
+    if (t < kC) {
+        bt[t] = beta[static_cast<long long>(row0 + t) * vh + h];
+        cl[t] = fmaxf(logf(decay[static_cast<long long>(row0 + t) * vh + h]), -80.f);
+    }
+    __syncthreads();
+    if (t == 0) {
+        float a = 0.f;
+        for (int i = 0; i < kC; ++i) { a += cl[i]; cl[i] = a; }
+    }
+    __syncthreads();
+    if (t < kC) eg[t] = expf(cl[t]);
+    const int i = t >> 2;
+    {
+        float am[16], ap[16];
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) { am[jj] = 0.f; ap[jj] = 0.f; }
+        for (int k4 = 0; k4 < kD; k4 += 4) {
+            const float4 ki = *reinterpret_cast<const float4*>(Ks + i * kPadD + k4);
+            const float4 qi = *reinterpret_cast<const float4*>(Qs + i * kPadD + k4);
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+                const float4 kj = *reinterpret_cast<const float4*>(Ks + ((t & 3) + 4 * jj) * kPadD + k4);
+                am[jj] += ki.x * kj.x; am[jj] += ki.y * kj.y; am[jj] += ki.z * kj.z; am[jj] += ki.w * kj.w;
+                ap[jj] += qi.x * kj.x; ap[jj] += qi.y * kj.y; ap[jj] += qi.z * kj.z; ap[jj] += qi.w * kj.w;
+            }
+        }
+        float* pg = Pg + ((static_cast<long long>(c) * vh + h) * kC + i) * kC;
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            const int j = (t & 3) + 4 * jj;
+            const float ratio = j <= i ? expf(cl[i] - cl[j]) : 0.f;
+            Ls[i * kPadC + j] = j < i ? bt[i] * ratio * am[jj] : 0.f;
+            pg[j] = ratio * ap[jj];
+        }
+    }
+    __syncthreads();                         // L complete; nobody reads the q rows any more
+    for (int p = t; p < kC * (kD / 4); p += 256) {
+        const int r = p / (kD / 4), q4 = p % (kD / 4);
+        *reinterpret_cast<float4*>(Qs + r * kPadD + q4 * 4) =
+            *reinterpret_cast<const float4*>(vv + (static_cast<long long>(row0 + r) * vh + h) * kD + q4 * 4);
+    }
+    if (t < kC) {
+        // column t of T = (I + L)^-1 by forward substitution (zero above the diagonal); columns are independent
+        for (int r = 0; r < kC; ++r) {
+            float acc = r == t ? 1.f : 0.f;
+            for (int j = t; j < r; ++j) acc -= Ls[r * kPadC + j] * Ts[j * kPadC + t];
+            Ts[r * kPadC + t] = r < t ? 0.f : acc;
+        }
+        CLg[(static_cast<long long>(c) * vh + h) * kC + t] = cl[t];
+    }
+    __syncthreads();
+    {
+        // row i, columns 16 q + 4 (t & 3) + e  (q = 0..7, e = 0..3)
+        float w[32], u[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) { w[e] = 0.f; u[e] = 0.f; }
+        const int cb = 4 * (t & 3);
+        for (int j = 0; j <= i; ++j) {
+            const float tb = Ts[i * kPadC + j] * bt[j];
+            const float tg = tb * eg[j];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 kk = *reinterpret_cast<const float4*>(Ks + j * kPadD + 16 * q + cb);
+                const float4 v4 = *reinterpret_cast<const float4*>(Qs + j * kPadD + 16 * q + cb);
+                w[4 * q] += tg * kk.x; w[4 * q + 1] += tg * kk.y; w[4 * q + 2] += tg * kk.z; w[4 * q + 3] += tg * kk.w;
+                u[4 * q] += tb * v4.x; u[4 * q + 1] += tb * v4.y; u[4 * q + 2] += tb * v4.z; u[4 * q + 3] += tb * v4.w;
+            }
+        }
+        const long long base = ((static_cast<long long>(c) * vh + h) * kC + i) * kD;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            *reinterpret_cast<float4*>(Wg + base + 16 * q + cb) = make_float4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            *reinterpret_cast<float4*>(Ug + base + 16 * q + cb) = make_float4(u[4 * q], u[4 * q + 1], u[4 * q + 2], u[4 * q + 3]);
+        }
+    }
+}
+
+constexpr int kScanCols = 32;            // state columns per CTA of the chunk scan
+
+// grid = (value heads x 4 column groups, sequences), 256 threads.  Walks the chunks [seq_chunk[b], seq_chunk[b + 1]) of
+// sequence b in order with the state columns of its group in shared memory.
+__global__ void __launch_bounds__(256)
+gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ Wg,
+                      const float* __restrict__ Ug, const float* __restrict__ Pg, const float* __restrict__ CLg,
+                      const int* __restrict__ chunk_row0, const int* __restrict__ seq_chunk, const int* __restrict__ seq_slot,
+                      float* __restrict__ state, float* __restrict__ o_out, int kh, int vh) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(16) float csm[];
+    float* Ws = csm;                         // [64][132]
+    float* Qs = Ws + kC * kPadD;             // [64][132]
+    float* Ks = Qs + kC * kPadD;             // [64][132]
+    float* Ps = Ks + kC * kPadD;             // [64][68]
+    float* Us = Ps + kC * kPadC;             // [64][32]
+    float* Ss = Us + kC * kScanCols;         // [128][32]
+    float* cl = Ss + kD * kScanCols;         // [64]
+    float* sc = cl + kC;                     // [64] e^(cl_63 - cl_j)
+    const int groups = kD / kScanCols;
+    const int h = blockIdx.x / groups, col0 = (blockIdx.x % groups) * kScanCols, b = blockIdx.y;
+    const int khd = h / (vh / kh);
+    const int c_begin = seq_chunk[b], c_end = seq_chunk[b + 1];
+    if (c_begin >= c_end) return;
+    const int t = threadIdx.x;
+    float* sp = state + ((static_cast<long long>(seq_slot[b]) * vh + h) * kD) * kD + col0;
+    for (int p = t; p < kD * (kScanCols / 4); p += 256) {
+        const int k = p / (kScanCols / 4), q4 = p % (kScanCols / 4);
+        *reinterpret_cast<float4*>(Ss + k * kScanCols + q4 * 4) = *reinterpret_cast<const float4*>(sp + static_cast<long long>(k) * kD + q4 * 4);
+    }
+    const int r = t >> 2, cg = (t & 3) * 8;              // products with 64 output rows: row r, columns cg .. cg + 7
+    const int sk = t >> 1, sh = (t & 1) * 16;            // state update: state row sk, columns sh .. sh + 15
+    for (int c = c_begin; c < c_end; ++c) {
+        const int row0 = chunk_row0[c];
+        const long long cb = static_cast<long long>(c) * vh + h;
+        __syncthreads();                                 // the previous chunk is done with every tile (and the state is loaded)
+        for (int p = t; p < kC * (kD / 4); p += 256) {
+            const int rr = p / (kD / 4), q4 = p % (kD / 4);
+            const long long src = (static_cast<long long>(row0 + rr) * kh + khd) * kD + q4 * 4;
+            *reinterpret_cast<float4*>(Ws + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(Wg + (cb * kC + rr) * kD + q4 * 4);
+            *reinterpret_cast<float4*>(Qs + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(qn + src);
+            *reinterpret_cast<float4*>(Ks + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(kn + src);
+        }
+        for (int p = t; p < kC * (kC / 4); p += 256) {
+            const int rr = p / (kC / 4), q4 = p % (kC / 4);
+            *reinterpret_cast<float4*>(Ps + rr * kPadC + q4 * 4) = *reinterpret_cast<const float4*>(Pg + (cb * kC + rr) * kC + q4 * 4);
+        }
+        if (t < kC) cl[t] = CLg[cb * kC + t];
+        __syncthreads();
+        if (t < kC) sc[t] = expf(cl[kC - 1] - cl[t]);
+        // U = U_v - W S_0
+        float a[8];
+        {
+            const float* ug = Ug + (cb * kC + r) * kD + col0 + cg;
+            const float4 u0 = *reinterpret_cast<const float4*>(ug), u1 = *reinterpret_cast<const float4*>(ug + 4);
+            a[0] = u0.x; a[1] = u0.y; a[2] = u0.z; a[3] = u0.w; a[4] = u1.x; a[5] = u1.y; a[6] = u1.z; a[7] = u1.w;
+        }
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = 0.f;
+        for (int k4 = 0; k4 < kD; k4 += 4) {
+            const float4 w4 = *reinterpret_cast<const float4*>(Ws + r * kPadD + k4);
+            const float4 q4 = *reinterpret_cast<const float4*>(Qs + r * kPadD + k4);
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const float4 s0 = *reinterpret_cast<const float4*>(Ss + (k4 + kk) * kScanCols + cg);
+                const float4 s1 = *reinterpret_cast<const float4*>(Ss + (k4 + kk) * kScanCols + cg + 4);
+                a[0] -= wv[kk] * s0.x; a[1] -= wv[kk] * s0.y; a[2] -= wv[kk] * s0.z; a[3] -= wv[kk] * s0.w;
+                a[4] -= wv[kk] * s1.x; a[5] -= wv[kk] * s1.y; a[6] -= wv[kk] * s1.z; a[7] -= wv[kk] * s1.w;
+                o[0] += qv[kk] * s0.x; o[1] += qv[kk] * s0.y; o[2] += qv[kk] * s0.z; o[3] += qv[kk] * s0.w;
+                o[4] += qv[kk] * s1.x; o[5] += qv[kk] * s1.y; o[6] += qv[kk] * s1.z; o[7] += qv[kk] * s1.w;
+            }
+        }
+        *reinterpret_cast<float4*>(Us + r * kScanCols + cg) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(Us + r * kScanCols + cg + 4) = make_float4(a[4], a[5], a[6], a[7]);
+        __syncthreads();                                 // U complete (sc too)
+        // O = diag(e^cl) Q S_0 + P U
+        {
+            const float g = expf(cl[r]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] *= g;
+            for (int j = 0; j <= r; ++j) {
+                const float pj = Ps[r * kPadC + j];
+                const float4 u0 = *reinterpret_cast<const float4*>(Us + j * kScanCols + cg);
+                const float4 u1 = *reinterpret_cast<const float4*>(Us + j * kScanCols + cg + 4);
+                o[0] += pj * u0.x; o[1] += pj * u0.y; o[2] += pj * u0.z; o[3] += pj * u0.w;
+                o[4] += pj * u1.x; o[5] += pj * u1.y; o[6] += pj * u1.z; o[7] += pj * u1.w;
+            }
+            float* og = o_out + (static_cast<long long>(row0 + r) * vh + h) * kD + col0 + cg;
+            *reinterpret_cast<float4*>(og) = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(og + 4) = make_float4(o[4], o[5], o[6], o[7]);
+        }
+        __syncthreads();                                 // every read of S_0 is done
+        // S = e^(cl_63) S_0 + (diag(e^(cl_63 - cl)) K)^T U
+        {
+            float sv[16];
+            const float gc = expf(cl[kC - 1]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 s4 = *reinterpret_cast<const float4*>(Ss + sk * kScanCols + sh + 4 * q);
+                sv[4 * q] = s4.x * gc; sv[4 * q + 1] = s4.y * gc; sv[4 * q + 2] = s4.z * gc; sv[4 * q + 3] = s4.w * gc;
+            }
+            for (int j = 0; j < kC; ++j) {
+                const float kj = Ks[j * kPadD + sk] * sc[j];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kScanCols + sh + 4 * q);
+                    sv[4 * q] += kj * u4.x; sv[4 * q + 1] += kj * u4.y; sv[4 * q + 2] += kj * u4.z; sv[4 * q + 3] += kj * u4.w;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<float4*>(Ss + sk * kScanCols + sh + 4 * q) = make_float4(sv[4 * q], sv[4 * q + 1], sv[4 * q + 2], sv[4 * q + 3]);
+        }
+    }
+    __syncthreads();
+    for (int p = t; p < kD * (kScanCols / 4); p += 256) {
+        const int k = p / (kScanCols / 4), q4 = p % (kScanCols / 4);
+        *reinterpret_cast<float4*>(sp + static_cast<long long>(k) * kD + q4 * 4) = *reinterpret_cast<const float4*>(Ss + k * kScanCols + q4 * 4);
+    }
+}
+
+constexpr int kPrepareSmem = (2 * kC * kPadD + 2 * kC * kPadC + 3 * kC) * static_cast<int>(sizeof(float));
+constexpr int kScanSmem = (3 * kC * kPadD + kC * kPadC + kC * kScanCols + kD * kScanCols + 2 * kC) * static_cast<int>(sizeof(float));
+
+// Prompt-class entry with the chunk form: rows [head_start, head_end) of every sequence (up to its first absolute
+// multiple of 64) and [tail_start, tail_end) (after its last one) run the token scan, the full chunks between them
+// the chunk kernels.  chunk_row0[c] = first row of chunk c; chunks [seq_chunk[b], seq_chunk[b + 1]) belong to sequence b.
+const char* gdn_prefill_chunked(const void* proj, int ld, int rows, const float* conv_w, float* hist, float* state, const float* a_log,
+                                const float* dt_bias, const float* norm_w, const int* row_seq, const int* seq_slot, const int* seq_start,
+                                int n_seq, float* scratch, void* out, int kh, int vh, int kd, int vd, float eps, bool gate_silu,
+                                const int* head_start, const int* head_end, bool any_head, const int* tail_start, const int* tail_end,
+                                bool any_tail, const int* chunk_row0, const int* seq_chunk, int n_chunks, float* W, float* U, float* P,
+                                float* CL, cudaStream_t s) {
+    if (kd != kD || vd != kD) return "gdn kernels handle head dimension 128";
+    if (vh % kh != 0) return "value heads must be a multiple of key heads";
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepareSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem) != cudaSuccess)
+            return "cannot raise the shared memory limit of the chunk kernels";
+        configured = true;
+    }
+    const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
+    float* qn = scratch;
+    float* kn = qn + static_cast<long long>(rows) * kh * kD;
+    float* vv = kn + static_cast<long long>(rows) * kh * kD;
+    float* oo = vv + static_cast<long long>(rows) * vh * kD;
+    float* bt = oo + static_cast<long long>(rows) * vh * kD;
+    float* dc = bt + static_cast<long long>(rows) * vh;
+    launch_chained(gdn_prep_kernel, dim3(dim3(rows, 2 * kh + vh)), dim3(kD), 0, s, pj, ld, conv_w, hist, a_log, dt_bias, row_seq, seq_slot, seq_start,
+                   qn, kn, vv, bt, dc, kh, vh);
+    const int C = 2 * kh * kD + vh * kD;
+    launch_chained(gdn_hist_kernel, dim3(dim3((C + 255) / 256, n_seq)), dim3(256), 0, s, pj, ld, hist, seq_slot, seq_start, C);
+    const dim3 lean_grid(vh * (kD / kLeanCols), n_seq);
+    if (any_head)
+        launch_chained(gdn_scan_lean_kernel, lean_grid, dim3(kLeanCols * kLeanParts), 0, s, qn, kn, vv, bt, dc, state, seq_slot, head_start, head_end, oo, kh, vh);
+    if (n_chunks > 0) {
+        launch_chained(gdn_chunk_prepare_kernel, dim3(n_chunks, vh), dim3(256), kPrepareSmem, s, qn, kn, vv, bt, dc, chunk_row0, kh, vh, W, U, P, CL);
+        launch_chained(gdn_chunk_scan_kernel, dim3(vh * (kD / kScanCols), n_seq), dim3(256), kScanSmem, s, qn, kn, W, U, P, CL, chunk_row0, seq_chunk,
+                       seq_slot, state, oo, kh, vh);
+    }
+    if (any_tail)
+        launch_chained(gdn_scan_lean_kernel, lean_grid, dim3(kLeanCols * kLeanParts), 0, s, qn, kn, vv, bt, dc, state, seq_slot, tail_start, tail_end, oo, kh, vh);
+    launch_chained(gdn_post_kernel, dim3(dim3(rows, vh)), dim3(kD), 0, s, oo, pj, ld, norm_w, static_cast<__nv_bfloat16*>(out), kh, vh, eps, gate_silu ? 1 : 0);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_prefill_chunked launch failed";
+}
+
 // Prompt-class entry: scratch = fp32 [rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh] (q, k, v, o, beta, decay).
 const char* gdn_prefill(const void* proj, int ld, int rows, const float* conv_w, float* hist, float* state, const float* a_log,
                         const float* dt_bias, const float* norm_w, const int* row_seq, const int* seq_slot, const int* seq_start,
@@ -356,7 +641,7 @@ const char* gdn_prefill(const void* proj, int ld, int rows, const float* conv_w,
     const int C = 2 * kh * kD + vh * kD;
     launch_chained(gdn_hist_kernel, dim3(dim3((C + 255) / 256, n_seq)), dim3(256), 0, s, pj, ld, hist, seq_slot, seq_start, C);
     launch_chained(gdn_scan_lean_kernel, dim3(dim3(vh * (kD / kLeanCols), n_seq)), dim3(kLeanCols * kLeanParts), 0, s, qn, kn, vv, bt, dc, state, seq_slot,
-                                                                                              seq_start, oo, kh, vh);
+                                                                                              seq_start, static_cast<const int*>(nullptr), oo, kh, vh);
     launch_chained(gdn_post_kernel, dim3(dim3(rows, vh)), dim3(kD), 0, s, oo, pj, ld, norm_w, static_cast<__nv_bfloat16*>(out), kh, vh, eps, gate_silu ? 1 : 0);
     return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_prefill launch failed";
 }

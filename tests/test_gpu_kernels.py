@@ -396,3 +396,37 @@ def test_grouped_gemm_is_bitwise_repeatable_under_skewed_routing():
             bad += 1
     ops.check_status()
     assert bad == 0, f"{bad} of 149 repeated launches differ from the first"
+
+
+def test_gdn_chunk_form_matches_the_token_scan_and_does_not_depend_on_the_cut():
+    """Prompt-class GDN with full 64-row chunks in the chunk form (heads and tails of sequences by the token scan): close to
+    the token scan and to the reference, and bitwise the same whether a prompt arrives in one call or in two."""
+    cfg = small_gpu_config()
+    seqs = [(0, 0, list(range(200))), (1, 40, list(range(150))), (2, 128, list(range(64))), (3, 10, list(range(20)))]
+    mw, (c1, c2), batch = _layer_setup(cfg, seqs, "prefill")
+    c3 = Cache(cfg, make_plan(cfg), 4, 64, 1024, torch.bfloat16, DEV, mtp=False)
+    lw = mw.layers[0]
+    chunked, scan, ref = _ops(cfg), _ops(cfg), RefOps(cfg, torch.bfloat16)
+    chunked.gdn_chunked, scan.gdn_chunked = True, False
+    rows = sum(len(s[2]) for s in seqs)
+    g = torch.Generator().manual_seed(14)
+    for step in range(2):                     # the second pass starts from carried state and convolution rows
+        proj = (torch.randn(rows, lw.in_proj.n, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+        a = chunked.gdn_mix(lw, proj, batch(), c1, 0)
+        b = scan.gdn_mix(lw, proj, batch(), c3, 0)
+        r = ref.gdn_mix(lw, proj, batch(), c2, 0)
+        assert bool(torch.isfinite(a.float()).all())
+        _close(a, b, rtol=2e-2, atol=6e-3)
+        _close(a, r, rtol=3e-2, atol=1e-2)
+        _close(c1.gdn_state[0], c3.gdn_state[0], rtol=1e-3, atol=1e-4)
+        _close(c1.conv_hist[0], c3.conv_hist[0], rtol=0, atol=0)
+    # one call of 256 rows against two calls of 128 rows: same bits
+    ids = list(range(256))
+    whole, halves = [Cache(cfg, make_plan(cfg), 2, 16, 512, torch.bfloat16, DEV, mtp=False) for _ in range(2)]
+    whole.ensure(0, 256), halves.ensure(0, 256)
+    proj = (torch.randn(256, lw.in_proj.n, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    y = chunked.gdn_mix(lw, proj, Batch.make([(0, 0, ids)], DEV, "prefill"), whole, 0)
+    y1 = chunked.gdn_mix(lw, proj[:128].contiguous(), Batch.make([(0, 0, ids[:128])], DEV, "prefill"), halves, 0)
+    y2 = chunked.gdn_mix(lw, proj[128:].contiguous(), Batch.make([(0, 128, ids[128:])], DEV, "prefill"), halves, 0)
+    assert torch.equal(y, torch.cat([y1, y2], 0))
+    assert torch.equal(whole.gdn_state[0], halves.gdn_state[0])

@@ -14,6 +14,7 @@ import torch
 from ..config import ModelConfig
 from . import _ext
 from .api import Batch
+from ..utils.env import flag
 
 
 def _bn_for(rows: int) -> int:
@@ -39,6 +40,7 @@ class CudaOps:
         self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)   # last-CTA ticket of the fused router
         self.launches = 0
         self._moe_ws = {}
+        self.gdn_chunked = flag("VADE_GDN_CHUNK", False)     # prompt-class GDN: full 64-row chunks in the chunk form
 
     # ---- helpers
     def check_status(self) -> None:
@@ -154,6 +156,19 @@ class CudaOps:
                 counts = torch.tensor([e - s for s, e in zip(batch.seq_start, batch.seq_start[1:])], device=self.device)
                 d["row_seq"] = torch.repeat_interleave(torch.arange(len(batch.seq_slots), device=self.device), counts).to(torch.int32)
             scratch = torch.empty(rows * (2 * kh + 2 * vh) * 128 + 2 * rows * vh, dtype=torch.float32, device=self.device)
+            ck = self._gdn_chunks(batch, d) if self.gdn_chunked else None
+            if ck is not None:
+                # full 64-row chunks (absolute multiples of 64 tokens) in the chunk form, the rows around them by the token scan
+                nc = ck["n"]
+                W = torch.empty(2, nc, vh, 64, 128, dtype=torch.float32, device=self.device)
+                P = torch.empty(nc, vh, 64, 64, dtype=torch.float32, device=self.device)
+                CL = torch.empty(nc, vh, 64, dtype=torch.float32, device=self.device)
+                self.launches += 4 + int(ck["head"]) + int(ck["tail"])
+                self.ext.gdn_prefill_chunked(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
+                                             d["row_seq"], d["seq_slot"], d["seq_start"], len(batch.seq_slots), scratch, out, kh, vh,
+                                             cfg.linear_key_head_dim, cfg.linear_value_head_dim, cfg.rms_norm_eps, False, ck["ranges"],
+                                             ck["head"], ck["tail"], ck["row0"], ck["seq_chunk"], nc, W[0], W[1], P, CL)
+                return out
             self.launches += 4
             self.ext.gdn_prefill(proj, lw.conv_w, cache.conv_hist[layer], cache.gdn_state[layer], lw.a_log, lw.dt_bias, lw.gdn_norm,
                                  d["row_seq"], d["seq_slot"], d["seq_start"], len(batch.seq_slots), scratch, out, kh, vh,
@@ -164,6 +179,26 @@ class CudaOps:
                           d["seq_slot"], d["seq_start"], len(batch.seq_slots), out, kh, vh, cfg.linear_key_head_dim,
                           cfg.linear_value_head_dim, cfg.rms_norm_eps, False)
         return out
+
+    def _gdn_chunks(self, batch: Batch, d: dict):
+        """Chunk tables of a prompt pass (built once per pass, shared by its layers): per sequence the rows before its first
+        absolute multiple of 64 tokens, its full 64-row chunks, and the rows after the last boundary.  None when the pass
+        holds no full chunk."""
+        if "gdn_chunks" not in d:
+            ranges, row0, seq_chunk = [[], [], [], []], [], [0]
+            for b, p0 in enumerate(batch.seq_pos0):
+                r0, r1 = batch.seq_start[b], batch.seq_start[b + 1]
+                head = min(r1 - r0, (-p0) % 64)
+                full = (r1 - r0 - head) // 64
+                row0 += [r0 + head + 64 * i for i in range(full)]
+                seq_chunk.append(len(row0))
+                for lst, v in zip(ranges, (r0, r0 + head, r0 + head + 64 * full, r1)):
+                    lst.append(v)
+            mk = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+            d["gdn_chunks"] = None if not row0 else {
+                "n": len(row0), "ranges": mk(ranges), "row0": mk(row0), "seq_chunk": mk(seq_chunk),
+                "head": any(e > s for s, e in zip(ranges[0], ranges[1])), "tail": any(e > s for s, e in zip(ranges[2], ranges[3]))}
+        return d["gdn_chunks"]
 
     def attn_mix(self, lw, qkv, batch: Batch, cache, layer):
         cfg = self.cfg
