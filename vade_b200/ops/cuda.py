@@ -40,7 +40,7 @@ class CudaOps:
         self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)   # last-CTA ticket of the fused router
         self.launches = 0
         self._moe_ws = {}
-        self.gdn_chunked = flag("VADE_GDN_CHUNK", False)     # prompt-class GDN: full 64-row chunks in the chunk form
+        self.gdn_chunked = flag("VADE_GDN_CHUNK", True)     # prompt-class GDN: full 64-row chunks in the chunk form
 
     # ---- helpers
     def check_status(self) -> None:
