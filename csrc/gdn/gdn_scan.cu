@@ -417,12 +417,24 @@ gdn_chunk_prepare_kernel(const float* __restrict__ qn, const float* __restrict__
             *reinterpret_cast<const float4*>(vv + (static_cast<long long>(row0 + r) * vh + h) * kD + q4 * 4);
     }
     if (t < kC) {
-        // column t of T = (I + L)^-1 by forward substitution (zero above the diagonal); columns are independent
+        // column t of T = (I + L)^-1 by forward substitution; columns are independent.  The column lives in registers
+        // (loops fully unrolled), so a row costs broadcast reads of L and one multiply-add chain, no shared-memory
+        // store -> load round trip.  L is zero on and above the diagonal, so whole float4 pieces can be used.
+        float colv[kC];
+#pragma unroll
+        for (int r = 0; r < kC; ++r) colv[r] = 0.f;
+#pragma unroll
         for (int r = 0; r < kC; ++r) {
             float acc = r == t ? 1.f : 0.f;
-            for (int j = t; j < r; ++j) acc -= Ls[r * kPadC + j] * Ts[j * kPadC + t];
-            Ts[r * kPadC + t] = r < t ? 0.f : acc;
+#pragma unroll
+            for (int j4 = 0; j4 < r; j4 += 4) {
+                const float4 l4 = *reinterpret_cast<const float4*>(Ls + r * kPadC + j4);
+                acc -= l4.x * colv[j4]; acc -= l4.y * colv[j4 + 1]; acc -= l4.z * colv[j4 + 2]; acc -= l4.w * colv[j4 + 3];
+            }
+            colv[r] = acc;
         }
+#pragma unroll
+        for (int r = 0; r < kC; ++r) Ts[r * kPadC + t] = colv[r];
         CLg[(static_cast<long long>(c) * vh + h) * kC + t] = cl[t];
     }
     __syncthreads();
@@ -456,7 +468,7 @@ constexpr int kScanCols = 32;            // state columns per CTA of the chunk s
 
 // grid = (value heads x 4 column groups, sequences), 256 threads.  Walks the chunks [seq_chunk[b], seq_chunk[b + 1]) of
 // sequence b in order with the state columns of its group in shared memory.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ Wg,
                       const float* __restrict__ Ug, const float* __restrict__ Pg, const float* __restrict__ CLg,
                       const int* __restrict__ chunk_row0, const int* __restrict__ seq_chunk, const int* __restrict__ seq_slot,
@@ -484,7 +496,7 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
         *reinterpret_cast<float4*>(Ss + k * kScanCols + q4 * 4) = *reinterpret_cast<const float4*>(sp + static_cast<long long>(k) * kD + q4 * 4);
     }
     const int r = t >> 2, cg = (t & 3) * 8;              // products with 64 output rows: row r, columns cg .. cg + 7
-    const int sk = t >> 1, sh = (t & 1) * 16;            // state update: state row sk, columns sh .. sh + 15
+    const int sk = (t >> 3) * 4, sh = (t & 7) * 4;       // state update: state rows sk .. sk + 3, columns sh .. sh + 3
     for (int c = c_begin; c < c_end; ++c) {
         const int row0 = chunk_row0[c];
         const long long cb = static_cast<long long>(c) * vh + h;
@@ -547,26 +559,29 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
             *reinterpret_cast<float4*>(og + 4) = make_float4(o[4], o[5], o[6], o[7]);
         }
         __syncthreads();                                 // every read of S_0 is done
-        // S = e^(cl_63) S_0 + (diag(e^(cl_63 - cl)) K)^T U
+        // S = e^(cl_63) S_0 + (diag(e^(cl_63 - cl)) K)^T U : a thread owns 4 state rows x 4 columns, so a chunk row costs it
+        // two 16-byte shared-memory reads (four k values, four u values) for sixteen multiply-adds
         {
-            float sv[16];
+            float sv[4][4];
             const float gc = expf(cl[kC - 1]);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float4 s4 = *reinterpret_cast<const float4*>(Ss + sk * kScanCols + sh + 4 * q);
-                sv[4 * q] = s4.x * gc; sv[4 * q + 1] = s4.y * gc; sv[4 * q + 2] = s4.z * gc; sv[4 * q + 3] = s4.w * gc;
+            for (int i = 0; i < 4; ++i) {
+                const float4 s4 = *reinterpret_cast<const float4*>(Ss + (sk + i) * kScanCols + sh);
+                sv[i][0] = s4.x * gc; sv[i][1] = s4.y * gc; sv[i][2] = s4.z * gc; sv[i][3] = s4.w * gc;
             }
             for (int j = 0; j < kC; ++j) {
-                const float kj = Ks[j * kPadD + sk] * sc[j];
+                const float4 k4 = *reinterpret_cast<const float4*>(Ks + j * kPadD + sk);
+                const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kScanCols + sh);
+                const float sj = sc[j];
+                const float kv[4] = {k4.x * sj, k4.y * sj, k4.z * sj, k4.w * sj};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 u4 = *reinterpret_cast<const float4*>(Us + j * kScanCols + sh + 4 * q);
-                    sv[4 * q] += kj * u4.x; sv[4 * q + 1] += kj * u4.y; sv[4 * q + 2] += kj * u4.z; sv[4 * q + 3] += kj * u4.w;
+                for (int i = 0; i < 4; ++i) {
+                    sv[i][0] += kv[i] * u4.x; sv[i][1] += kv[i] * u4.y; sv[i][2] += kv[i] * u4.z; sv[i][3] += kv[i] * u4.w;
                 }
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<float4*>(Ss + sk * kScanCols + sh + 4 * q) = make_float4(sv[4 * q], sv[4 * q + 1], sv[4 * q + 2], sv[4 * q + 3]);
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<float4*>(Ss + (sk + i) * kScanCols + sh) = make_float4(sv[i][0], sv[i][1], sv[i][2], sv[i][3]);
         }
     }
     __syncthreads();
