@@ -129,7 +129,8 @@ def cmd_serve(a) -> int:
                                          "draft_block": eng.model.w.mtp is not None, "ops": eng.model.ops.name,
                                          "build": _ext.source_stamp() if on_gpu else None, "tp": a.tp, "comm": a.comm,
                                          "prefill_chunk": a.prefill_chunk, "cache_entries": a.cache_entries,
-                                         "decode_graphs": flag("VADE_DECODE_GRAPHS", True), "eos": tok.eos_id},
+                                         "decode_graphs": flag("VADE_DECODE_GRAPHS", True), "gdn_chunk": flag("VADE_GDN_CHUNK", True),
+                                         "eos": tok.eos_id},
                                    least={"slots": a.slots, "pages": eng.cache.alloc.total, "context": eng.cache.max_pages * 64})
         slots = agreed["slots"]
     sched = Scheduler(eng, SchedulerConfig(max_active=slots, prefill_slice=a.prefill_chunk, prefix_cache_entries=a.cache_entries),
