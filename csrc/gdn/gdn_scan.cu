@@ -478,12 +478,12 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
     extern __shared__ __align__(16) float csm[];
     float* Ws = csm;                         // [64][132]
     float* Qs = Ws + kC * kPadD;             // [64][132]
-    float* Ks = Qs + kC * kPadD;             // [64][132]
-    float* Ps = Ks + kC * kPadD;             // [64][68]
+    float* Kb = Qs + kC * kPadD;             // 2 x [64][132]: the k rows of this chunk and of the next one
+    float* Ps = Kb + 2 * kC * kPadD;         // [64][68]
     float* Us = Ps + kC * kPadC;             // [64][32]
     float* Ss = Us + kC * kScanCols;         // [128][32]
-    float* cl = Ss + kD * kScanCols;         // [64]
-    float* sc = cl + kC;                     // [64] e^(cl_63 - cl_j)
+    float* clb = Ss + kD * kScanCols;        // 2 x [64]
+    float* sc = clb + 2 * kC;                // [64] e^(cl_63 - cl_j)
     const int groups = kD / kScanCols;
     const int h = blockIdx.x / groups, col0 = (blockIdx.x % groups) * kScanCols, b = blockIdx.y;
     const int khd = h / (vh / kh);
@@ -497,23 +497,33 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
     }
     const int r = t >> 2, cg = (t & 3) * 8;              // products with 64 output rows: row r, columns cg .. cg + 7
     const int sk = (t >> 3) * 4, sh = (t & 7) * 4;       // state update: state rows sk .. sk + 3, columns sh .. sh + 3
-    for (int c = c_begin; c < c_end; ++c) {
+    // asynchronous copies of a chunk's tiles (W, q, k, P, cl); the k rows and cl go to the buffer of the chunk's parity
+    auto fetch = [&](int c) {
         const int row0 = chunk_row0[c];
         const long long cb = static_cast<long long>(c) * vh + h;
-        __syncthreads();                                 // the previous chunk is done with every tile (and the state is loaded)
+        float* Kn = Kb + ((c - c_begin) & 1) * kC * kPadD;
         for (int p = t; p < kC * (kD / 4); p += 256) {
             const int rr = p / (kD / 4), q4 = p % (kD / 4);
             const long long src = (static_cast<long long>(row0 + rr) * kh + khd) * kD + q4 * 4;
-            *reinterpret_cast<float4*>(Ws + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(Wg + (cb * kC + rr) * kD + q4 * 4);
-            *reinterpret_cast<float4*>(Qs + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(qn + src);
-            *reinterpret_cast<float4*>(Ks + rr * kPadD + q4 * 4) = *reinterpret_cast<const float4*>(kn + src);
+            cp_async_f(Ws + rr * kPadD + q4 * 4, Wg + (cb * kC + rr) * kD + q4 * 4, 16);
+            cp_async_f(Qs + rr * kPadD + q4 * 4, qn + src, 16);
+            cp_async_f(Kn + rr * kPadD + q4 * 4, kn + src, 16);
         }
         for (int p = t; p < kC * (kC / 4); p += 256) {
             const int rr = p / (kC / 4), q4 = p % (kC / 4);
-            *reinterpret_cast<float4*>(Ps + rr * kPadC + q4 * 4) = *reinterpret_cast<const float4*>(Pg + (cb * kC + rr) * kC + q4 * 4);
+            cp_async_f(Ps + rr * kPadC + q4 * 4, Pg + (cb * kC + rr) * kC + q4 * 4, 16);
         }
-        if (t < kC) cl[t] = CLg[cb * kC + t];
-        __syncthreads();
+        if (t < kC / 4) cp_async_f(clb + ((c - c_begin) & 1) * kC + t * 4, CLg + cb * kC + t * 4, 16);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(c_begin);
+    for (int c = c_begin; c < c_end; ++c) {
+        const int row0 = chunk_row0[c];
+        const long long cb = static_cast<long long>(c) * vh + h;
+        const float* Ks = Kb + ((c - c_begin) & 1) * kC * kPadD;
+        const float* cl = clb + ((c - c_begin) & 1) * kC;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                 // this chunk's tiles have landed; the previous state update is complete
         if (t < kC) sc[t] = expf(cl[kC - 1] - cl[t]);
         // U = U_v - W S_0
         float a[8];
@@ -558,7 +568,8 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
             *reinterpret_cast<float4*>(og) = make_float4(o[0], o[1], o[2], o[3]);
             *reinterpret_cast<float4*>(og + 4) = make_float4(o[4], o[5], o[6], o[7]);
         }
-        __syncthreads();                                 // every read of S_0 is done
+        __syncthreads();                                 // every read of S_0, W, q and P is done
+        if (c + 1 < c_end) fetch(c + 1);                 // the next chunk's tiles arrive while the state is updated
         // S = e^(cl_63) S_0 + (diag(e^(cl_63 - cl)) K)^T U : a thread owns 4 state rows x 4 columns, so a chunk row costs it
         // two 16-byte shared-memory reads (four k values, four u values) for sixteen multiply-adds
         {
@@ -592,7 +603,7 @@ gdn_chunk_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
 }
 
 constexpr int kPrepareSmem = (2 * kC * kPadD + 2 * kC * kPadC + 3 * kC) * static_cast<int>(sizeof(float));
-constexpr int kScanSmem = (3 * kC * kPadD + kC * kPadC + kC * kScanCols + kD * kScanCols + 2 * kC) * static_cast<int>(sizeof(float));
+constexpr int kScanSmem = (4 * kC * kPadD + kC * kPadC + kC * kScanCols + kD * kScanCols + 3 * kC) * static_cast<int>(sizeof(float));
 
 // Prompt-class entry with the chunk form: rows [head_start, head_end) of every sequence (up to its first absolute
 // multiple of 64) and [tail_start, tail_end) (after its last one) run the token scan, the full chunks between them
